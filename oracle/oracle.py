@@ -1,0 +1,252 @@
+"""ctypes front end of the CPU oracle (``oracle/trigrad_oracle.cpp``).
+
+TEST INFRASTRUCTURE ONLY: imported by ``tests/``, by the smoke check and by the benchmark's
+``cpu_baseline`` / reference arm, never by the shipped render path.
+
+Two ways to the per-tile lists are offered and must agree (``tests/test_oracle.py``):
+
+* ``build_lists``            - native: per-tile counts, cumulative offsets, ``std::stable_sort``
+                               per tile, i.e. the reference's own objects (``render.cu:286-308``);
+* ``build_lists_staged``     - the new pipeline's objects restated with numpy: per-triangle counts,
+                               exclusive scan, 64-bit ``tile<<32 | ord(depth)`` keys in triangle
+                               order, one global stable sort, tile ranges.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import sys
+from dataclasses import dataclass
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+if HERE not in sys.path:
+    sys.path.insert(0, HERE)
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        import build as _build  # oracle/build.py
+
+        path = _build.LIB
+        if not os.path.exists(path) or os.path.getmtime(path) < os.path.getmtime(_build.SRC):
+            path = _build.build()
+        _lib = C.CDLL(path)
+        _lib.tgo_build_lists_f32.restype = C.c_longlong
+        _lib.tgo_build_lists_f64.restype = C.c_longlong
+        _lib.tgo_num_threads.restype = C.c_int
+    return _lib
+
+
+def num_threads() -> int:
+    return int(lib().tgo_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    lib().tgo_set_num_threads(C.c_int(n))
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _suf(dtype) -> str:
+    return "f32" if np.dtype(dtype) == np.float32 else "f64"
+
+
+def _fn(name: str, dtype):
+    return getattr(lib(), f"{name}_{_suf(dtype)}")
+
+
+def _sc(dtype, x):
+    return C.c_float(x) if np.dtype(dtype) == np.float32 else C.c_double(x)
+
+
+def float_to_ordered_u32(x: np.ndarray) -> np.ndarray:
+    """Order-preserving float32 -> uint32 map used in the 64-bit sort keys.
+
+    Negative floats have all bits flipped, non-negative ones the sign bit set; -0.0 is first
+    mapped to +0.0 so that the two zeros compare equal, as they do in a float comparison.
+    """
+    x = np.asarray(x, dtype=np.float32) + np.float32(0.0)  # -0.0 + 0.0 = +0.0
+    u = x.view(np.uint32)
+    neg = (u >> np.uint32(31)).astype(bool)
+    return np.where(neg, ~u, u | np.uint32(0x80000000)).astype(np.uint32)
+
+
+def ordered_u32_to_float(u: np.ndarray) -> np.ndarray:
+    u = np.asarray(u, dtype=np.uint32)
+    pos = (u >> np.uint32(31)).astype(bool)
+    return np.where(pos, u & np.uint32(0x7FFFFFFF), ~u).astype(np.uint32).view(np.float32)
+
+
+@dataclass
+class Lists:
+    offsets: np.ndarray   # [tiles+1] int32
+    ids: np.ndarray       # [K] int32, sorted per tile
+    keys: np.ndarray      # [K] float, sorted per tile
+
+
+@dataclass
+class Staged:
+    rects: np.ndarray        # [T,4] int32 (x0,y0,x1,y1), empty = (0,-1,0,-1)
+    counts: np.ndarray       # [T] int32
+    tri_offsets: np.ndarray  # [T+1] int64 exclusive scan of counts
+    keys_unsorted: np.ndarray  # [K] uint64 (float32 only)
+    ids_unsorted: np.ndarray   # [K] int32
+    keys_sorted: np.ndarray    # [K] uint64
+    ids_sorted: np.ndarray     # [K] int32
+    offsets: np.ndarray        # [tiles+1] int32
+    depth_keys_unsorted: np.ndarray  # [K] float
+
+
+def num_tiles(W, H, tw, th):
+    return ((W + tw - 1) // tw) * ((H + th - 1) // th)
+
+
+def tile_rects(verts, idx, W, H, tw, th):
+    verts = np.ascontiguousarray(verts)
+    idx = np.ascontiguousarray(idx, dtype=np.int32)
+    T = idx.shape[0]
+    rects = np.empty((T, 4), np.int32)
+    counts = np.empty(T, np.int32)
+    _fn("tgo_tile_rects", verts.dtype)(_p(verts), _p(idx), T, W, H, tw, th, _p(rects), _p(counts))
+    return rects, counts
+
+
+def build_lists_staged(verts, idx, W, H, tw, th) -> Staged:
+    verts = np.ascontiguousarray(verts)
+    idx = np.ascontiguousarray(idx, dtype=np.int32)
+    T = idx.shape[0]
+    rects, counts = tile_rects(verts, idx, W, H, tw, th)
+    tri_offsets = np.zeros(T + 1, np.int64)
+    np.cumsum(counts, out=tri_offsets[1:])
+    K = int(tri_offsets[-1])
+    depth = np.empty(K, verts.dtype)
+    tiles = np.empty(K, np.int32)
+    tris = np.empty(K, np.int32)
+    _fn("tgo_emit_keys", verts.dtype)(_p(verts), _p(idx), T, W, H, tw, th, _p(rects), _p(tri_offsets), _p(depth),
+                                      _p(tiles), _p(tris))
+    nt = num_tiles(W, H, tw, th)
+    if verts.dtype == np.float32:
+        keys = (tiles.astype(np.uint64) << np.uint64(32)) | float_to_ordered_u32(depth).astype(np.uint64)
+        order = np.argsort(keys, kind="stable")
+        keys_sorted = keys[order]
+    else:
+        keys = np.zeros(K, np.uint64)
+        order = np.lexsort((np.arange(K), depth, tiles))  # tile, then depth, then emission order
+        keys_sorted = keys
+    ids_sorted = tris[order]
+    tiles_sorted = tiles[order]
+    offsets = np.searchsorted(tiles_sorted, np.arange(nt + 1), side="left").astype(np.int32)
+    return Staged(rects, counts, tri_offsets, keys, tris, keys_sorted, np.ascontiguousarray(ids_sorted), offsets, depth)
+
+
+def build_lists(verts, idx, W, H, tw, th) -> Lists:
+    verts = np.ascontiguousarray(verts)
+    idx = np.ascontiguousarray(idx, dtype=np.int32)
+    T = idx.shape[0]
+    nt = num_tiles(W, H, tw, th)
+    offsets = np.empty(nt + 1, np.int32)
+    f = _fn("tgo_build_lists", verts.dtype)
+    K = f(_p(verts), _p(idx), T, W, H, tw, th, _p(offsets), None, None, C.c_longlong(0))
+    ids = np.empty(max(K, 1), np.int32)
+    keys = np.empty(max(K, 1), verts.dtype)
+    K2 = f(_p(verts), _p(idx), T, W, H, tw, th, _p(offsets), _p(ids), _p(keys), C.c_longlong(K))
+    assert K2 == K
+    return Lists(offsets, ids[:K], keys[:K])
+
+
+def bary_matrices(verts, idx):
+    verts = np.ascontiguousarray(verts)
+    idx = np.ascontiguousarray(idx, dtype=np.int32)
+    M = np.empty((idx.shape[0], 3, 3), verts.dtype)
+    _fn("tgo_bary_matrices", verts.dtype)(_p(verts), _p(idx), idx.shape[0], _p(M))
+    return M
+
+
+def depth_planes(verts, idx):
+    verts = np.ascontiguousarray(verts)
+    idx = np.ascontiguousarray(idx, dtype=np.int32)
+    P = np.empty((idx.shape[0], 3), verts.dtype)
+    _fn("tgo_depth_planes", verts.dtype)(_p(verts), _p(idx), idx.shape[0], _p(P))
+    return P
+
+
+@dataclass
+class ForwardOut:
+    image: np.ndarray
+    depthmap: np.ndarray
+    final_weights: np.ndarray
+    ends: np.ndarray
+    lists: Lists
+    M: np.ndarray
+
+
+def forward(verts, idx, colors, opac, W, H, tw=16, th=16, thr=1 / 256, per_pixel_sort=True, max_layers=32,
+            lists: Lists | None = None) -> ForwardOut:
+    dt = np.asarray(verts).dtype
+    verts = np.ascontiguousarray(verts, dtype=dt)
+    idx = np.ascontiguousarray(idx, dtype=np.int32)
+    colors = np.ascontiguousarray(colors, dtype=dt)
+    opac = np.ascontiguousarray(opac, dtype=dt)
+    T = idx.shape[0]
+    if max_layers <= 0:
+        max_layers = T + 1          # reference src/trigrad/wrapper.py:35-36
+    if lists is None:
+        lists = build_lists(verts, idx, W, H, tw, th)
+    M = bary_matrices(verts, idx)
+    image = np.zeros((H, W, 4), dt)
+    depth = np.zeros((H, W), dt)
+    fw = np.zeros((H, W), dt)
+    ends = np.zeros((H, W), np.int32)
+    ids = np.ascontiguousarray(lists.ids)
+    _fn("tgo_forward", dt)(_p(verts), _p(idx), _p(colors), _p(opac), T, W, H, tw, th, _p(ids), _p(lists.offsets), _p(M),
+                           _sc(dt, thr), int(bool(per_pixel_sort)), int(max_layers), _p(image), _p(depth), _p(fw),
+                           _p(ends))
+    return ForwardOut(image, depth, fw, ends, lists, M)
+
+
+def backward(verts, idx, colors, opac, W, H, fwd: ForwardOut, grad_image, grad_depth, tw=16, th=16,
+             per_pixel_sort=True, max_layers=32):
+    dt = np.asarray(verts).dtype
+    verts = np.ascontiguousarray(verts, dtype=dt)
+    idx = np.ascontiguousarray(idx, dtype=np.int32)
+    colors = np.ascontiguousarray(colors, dtype=dt)
+    opac = np.ascontiguousarray(opac, dtype=dt)
+    gi = np.ascontiguousarray(grad_image, dtype=dt)
+    gd = np.ascontiguousarray(grad_depth, dtype=dt)
+    T = idx.shape[0]
+    if max_layers <= 0:
+        max_layers = T + 1
+    gV = np.zeros_like(verts)
+    gC = np.zeros_like(colors)
+    gO = np.zeros_like(opac)
+    ids = np.ascontiguousarray(fwd.lists.ids)
+    _fn("tgo_backward", dt)(_p(verts), _p(idx), _p(colors), _p(opac), T, W, H, tw, th, _p(ids), _p(fwd.lists.offsets),
+                            _p(fwd.M), int(bool(per_pixel_sort)), int(max_layers), _p(gi), _p(gd), _p(fwd.image),
+                            _p(fwd.depthmap), _p(fwd.final_weights), _p(fwd.ends), _p(gV), _p(gC), _p(gO))
+    return gV, gC, gO
+
+
+def render_l2(scene, dtype=np.float32, per_pixel_sort=True, max_layers=32, thr=1 / 256, target=None):
+    """fwd + bwd of ``mean((image - target)**2)`` on a ``trigrad_b200.scenes.Scene``; the timed CPU step."""
+    v = scene.vertices.astype(dtype)
+    c = scene.colors.astype(dtype)
+    o = scene.opacities.astype(dtype)
+    if target is None:
+        target = scene.target()
+    target = target.astype(dtype)
+    f = forward(v, scene.indices, c, o, scene.width, scene.height, scene.tile_width, scene.tile_height, thr,
+                per_pixel_sort, max_layers)
+    diff = f.image - target
+    loss = float(np.mean(diff.astype(np.float64) ** 2))
+    gi = (diff * dtype(2.0 / diff.size)).astype(dtype)
+    gd = np.zeros((scene.height, scene.width), dtype)
+    g = backward(v, scene.indices, c, o, scene.width, scene.height, f, gi, gd, scene.tile_width, scene.tile_height,
+                 per_pixel_sort, max_layers)
+    return loss, f, g
