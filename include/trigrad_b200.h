@@ -1,0 +1,142 @@
+/*
+ * trigrad_b200 - C ABI of the B200 (sm_100a) differentiable triangle rasteriser.
+ *
+ * This is the drop-in boundary for the render path of Davidxdydz/trigrad.  In the reference
+ * that boundary is a pybind11 module taking torch::Tensor by value
+ * (src/trigrad/module.cu:8-10, src/trigrad/render.h:6-38); here it is plain C: raw device
+ * pointers, sizes, a CUDA stream and an int status.  The library never allocates or frees
+ * device memory: outputs, saved state and workspace belong to the caller.
+ *
+ * Conventions
+ *   vertices   [V,4] float32  (x, y, z, w), x/y in NDC, row 0 of the image is y = -1
+ *   indices    [T,3] int32
+ *   colors     [V,3] float32, opacities [V] float32
+ *   image      [H,W,4] float32 (rgb accumulated, a = remaining transmittance)
+ *   tiles      tiles_x = ceil(W/tile_w), tiles_y = ceil(H/tile_h), tile id = ty*tiles_x + tx
+ *   All pointers are device pointers unless named *_host.  `stream` is a cudaStream_t.
+ *   Every function returns TG_OK (0) or one of the TG_ERR_* codes; tg_last_error() gives text.
+ *   The number of (triangle, tile) pairs K must stay below 2^31.
+ */
+#ifndef TRIGRAD_B200_H
+#define TRIGRAD_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* tg_stream_t; /* cudaStream_t */
+
+enum {
+    TG_OK = 0,
+    TG_ERR_BAD_ARG = 1,     /* null pointer, non-positive size, tile_w*tile_h > 1024 ... */
+    TG_ERR_WORKSPACE = 2,   /* workspace / scratch smaller than tg_*_bytes() says */
+    TG_ERR_CAPACITY = 3,    /* K exceeds the caller's list capacity; K is reported back */
+    TG_ERR_DEVICE_FLAG = 4, /* a kernel raised its error word (a bounded wait ran out) */
+    TG_ERR_CUDA = 5         /* a CUDA runtime call or launch failed */
+};
+
+/* Words per packed per-triangle record (float32 words). */
+#define TG_GEO_WORDS 16  /* M[9] row-major, z[3], w[3], depth lower bound */
+#define TG_ATTR_WORDS 24 /* opacity[3], colour a/b/c [9], vertex ids [3] (as int bits), pad, xy of a/b/c [6], pad[2] */
+
+int tg_version(void);
+const char* tg_status_string(int status);
+/* Text of the last failure on the calling thread ("" if none). */
+const char* tg_last_error(void);
+
+/* ---- stage 1: per-triangle preprocess ------------------------------------------------------
+ * Tile rectangle of the bounding box, tile-overlap count, barycentric matrix and packed records.
+ * Replaces count_per_tile_kernel (src/trigrad/render.cu:90-121, rectangle rule :51-76) and
+ * cartesian_to_bary_kernel (src/trigrad/render.cu:310-337).
+ *   tri_counts [T] uint32      number of tiles in the rectangle, 0 for degenerate triangles
+ *   tri_rects  [T,4] int32     (x0,y0,x1,y1) or (0,-1,0,-1); may be NULL
+ *   tri_geo    [T,TG_GEO_WORDS], tri_attr [T,TG_ATTR_WORDS] float32, 16-byte aligned
+ */
+int tg_preprocess(const float* vertices, const int32_t* indices, const float* colors, const float* opacities,
+                  int T, int W, int H, int tile_w, int tile_h, uint32_t* tri_counts, int32_t* tri_rects,
+                  float* tri_geo, float* tri_attr, tg_stream_t stream);
+
+/* ---- stage 2: device-wide exclusive prefix scan ---------------------------------------------
+ * out[i] = sum(in[0..i)), out[n] = total.  Single pass, decoupled look-back with bounded waits.
+ * Replaces offsets.sum() + torch::cumsum_out (src/trigrad/render.cu:290-295).
+ * `status` is one device uint32 that the kernel sets non-zero if a wait ran out.
+ */
+size_t tg_scan_scratch_bytes(int n);
+int tg_scan(const uint32_t* in, uint32_t* out, int n, void* scratch, size_t scratch_bytes, uint32_t* status,
+            tg_stream_t stream);
+
+/* ---- stage 3: key emission --------------------------------------------------------------------
+ * For triangle t and every tile (tx outer, ty inner) of its rectangle, entry e = tri_offsets[t] + n:
+ *   keys[e] = (uint64)tile << 32 | ord(depth key),  ids[e] = t
+ * depth key = min plane depth over the triangle clipped to the tile, 1e30f if the clip is empty;
+ * ord() is the order-preserving float->uint32 map (-0 folded into +0).
+ * Replaces fill_per_tile_lists_kernel (src/trigrad/render.cu:140-270).
+ */
+int tg_emit_keys(const float* vertices, const int32_t* indices, int T, int W, int H, int tile_w, int tile_h,
+                 const uint32_t* tri_offsets, uint64_t* keys, uint32_t* ids, uint32_t capacity, tg_stream_t stream);
+
+/* ---- stage 4: onesweep LSD radix sort of (uint64 key, uint32 value) pairs --------------------
+ * Stable, ascending on key bits [begin_bit, end_bit), 8-bit digits.  Sorts n pairs from
+ * (keys_a, vals_a); the other pair of buffers is scratch.  *result_in_b_host tells where the
+ * sorted data ended up (0: a, 1: b).  Replaces cub::DeviceSegmentedSort::StableSortPairs
+ * (src/trigrad/render.cu:272-284): one global sort on tile<<32|depth equals a stable sort per tile.
+ */
+size_t tg_sort_scratch_bytes(uint32_t n);
+int tg_sort_pairs(uint64_t* keys_a, uint64_t* keys_b, uint32_t* vals_a, uint32_t* vals_b, uint32_t n,
+                  int begin_bit, int end_bit, void* scratch, size_t scratch_bytes, uint32_t* status,
+                  int* result_in_b_host, tg_stream_t stream);
+
+/* ---- stage 5: tile ranges ----------------------------------------------------------------------
+ * offsets[t] = first position in the sorted keys whose tile id is >= t; offsets[tiles] = n.
+ * Same object as the reference's `offsets` (src/trigrad/render.cu:292-295).
+ */
+int tg_tile_ranges(const uint64_t* sorted_keys, uint32_t n, int tiles, int32_t* offsets, tg_stream_t stream);
+
+/* ---- stage 6: forward compositing ---------------------------------------------------------------
+ * One CTA per tile, one thread per pixel.  Replaces render_forward_kernel
+ * (src/trigrad/render.cu:540-619 with :338-453).  max_layers must be >= 1.
+ */
+int tg_blend_forward(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids, const int32_t* offsets,
+                     int W, int H, int tile_w, int tile_h, float early_stopping_threshold, int per_pixel_sort,
+                     int max_layers, float* image, float* depthmap, float* final_weights, int32_t* ends,
+                     tg_stream_t stream);
+
+/* ---- stage 7: backward ------------------------------------------------------------------------
+ * Replaces render_backward_kernel (src/trigrad/render.cu:621-695 with :455-538).
+ * grad_vertices [V,4] (z column stays 0), grad_colors [V,3], grad_opacities [V].
+ * accumulate == 0: the three gradient buffers are zeroed first; != 0: added to.
+ */
+int tg_blend_backward(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids, const int32_t* offsets,
+                      int V, int W, int H, int tile_w, int tile_h, int per_pixel_sort, int max_layers,
+                      const float* grad_image, const float* grad_depthmap, const float* image, const float* depthmap,
+                      const float* final_weights, const int32_t* ends, float* grad_vertices, float* grad_colors,
+                      float* grad_opacities, int accumulate, tg_stream_t stream);
+
+/* ---- whole forward path -------------------------------------------------------------------------
+ * Replaces render_forward (src/trigrad/render.cu:713-763).  Runs stages 1-6 on `stream`.
+ *   sorted_ids   [list_capacity] int32   out, first K entries valid
+ *   offsets      [tiles+1] int32         out
+ *   info_host    uint32[2] in (preferably pinned) host memory.  [0] receives K; the call
+ *                synchronises the stream once to read it (the reference does the same,
+ *                src/trigrad/render.cu:290).  [1] receives the device error word (0 = fine) by an
+ *                asynchronous copy: it is valid after the caller next synchronises the stream.
+ *   stage_ms_host  NULL or float[5]: milliseconds of {init, per_tile_lists, sorting,
+ *                bary_transforms, rasterization} measured with CUDA events (synchronises)
+ * If K > list_capacity nothing past the scan is run and TG_ERR_CAPACITY is returned with info_host[0]
+ * set; call again with a larger list and workspace.
+ */
+size_t tg_forward_workspace_bytes(int T, int tiles, uint32_t list_capacity);
+int tg_render_forward(const float* vertices, const int32_t* indices, const float* colors, const float* opacities,
+                      int T, int W, int H, int tile_w, int tile_h, float early_stopping_threshold,
+                      int per_pixel_sort, int max_layers, float* image, float* depthmap, float* final_weights,
+                      int32_t* ends, float* tri_geo, float* tri_attr, int32_t* sorted_ids, uint32_t list_capacity,
+                      int32_t* offsets, void* workspace, size_t workspace_bytes, uint32_t* info_host,
+                      float* stage_ms_host, tg_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRIGRAD_B200_H */

@@ -1,0 +1,203 @@
+"""GPU parity tests proper: every stage of the CUDA path, called through the C ABI, against the CPU oracle.
+
+Bars (from the task's north star): tile counts, sort keys, sorted order and tile ranges bit-exact;
+forward image within 1e-5 relative; gradients within 1e-4 relative.  Because the kernels mirror the
+oracle's decision arithmetic operation by operation, fragment selection (``ends``) is also required to
+be identical and the forward image is additionally checked for exact equality.
+"""
+import numpy as np
+import pytest
+import torch
+
+import helpers as Hh
+import oracle as O
+from trigrad_b200 import scenes as S
+
+pytestmark = pytest.mark.gpu
+
+IMG_TOL = 1e-5        # forward image, relative to the image maximum
+GRAD_TOL = 1e-4       # gradients, relative L2 error (the parity bar)
+GRAD_TOL_MAX = 1e-3   # sanity bound on the worst element, relative to the tensor maximum: fp32 atomics
+                      # accumulate in a run-dependent order and the expanded barycentric partials cancel
+
+
+def edge_case_scene():
+    """Degenerate, off-screen, huge and sliver triangles plus negative / mixed-sign depths."""
+    v = np.array([
+        [0.0, 0.0, 1.0], [0.0, 0.0, 1.0], [0.0, 0.0, 1.0],          # 0: all vertices equal (degenerate)
+        [-0.5, -0.5, 2.0], [0.0, 0.0, 2.0], [0.5, 0.5, 2.0],        # 1: collinear (degenerate)
+        [2.0, -0.2, 1.5], [3.0, -0.2, 1.5], [2.5, 0.4, 1.5],        # 2: right of the screen (clamped onto border)
+        [-9.0, -7.0, 3.0], [9.0, -7.0, 3.0], [0.0, 11.0, 3.0],      # 3: covers everything
+        [-0.9, 0.31, 0.7], [0.9, 0.3101, 0.7], [0.0, 0.3125, 0.7],  # 4: sliver across many tiles
+        [-0.3, -0.8, -1.0], [0.4, -0.7, -2.0], [0.1, -0.1, -1.5],   # 5: negative depths
+        [-0.8, 0.5, 1.0], [-0.2, 0.6, 4.0], [-0.5, 0.95, 2.0],      # 6: strongly varying depth
+        [0.2, 0.2, 1e-3], [0.6, 0.25, 1e-3], [0.4, 0.7, 1e-3],      # 7: tiny depth (huge w)
+    ], dtype=np.float32)
+    idx = np.arange(24, dtype=np.int32).reshape(8, 3)
+    rng = np.random.default_rng(21)
+    col = rng.random((24, 3), dtype=np.float32)
+    op = rng.uniform(0.2, 0.95, 24).astype(np.float32)
+    return S.Scene("edge_cases", S.add_w(v), idx, col, op, 200, 120, 16, 16)
+
+
+SCENES = {
+    "cfg1": lambda: S.config1_icosphere(),
+    "cfg2": lambda: S.config2_random10k(),
+    "cfg3_small": lambda: S.config3_random200k(T=20_000, width=640, height=360),
+    "cfg5_small": lambda: S.config5_overlap(T=4_000, width=320, height=192),
+    "squares": lambda: S.overlapping_squares(10),
+    "large": lambda: S.large_triangles(3),
+    "depth_overlap": lambda: S.depth_overlap(),
+    "layers40": lambda: S.full_screen_layers(40, width=48, height=40),
+    "edge": edge_case_scene,
+    "odd_tiles": lambda: S.random_triangles(3000, 333, 217, 0.05, 0.6, name="odd"),
+}
+SCENES["odd_tiles_5x7"] = lambda: (lambda s: (setattr(s, "tile_width", 5), setattr(s, "tile_height", 7), s)[2])(
+    S.random_triangles(3000, 333, 217, 0.05, 0.6, name="odd57"))
+SCENES["big_tile_32x32"] = lambda: (lambda s: (setattr(s, "tile_width", 32), setattr(s, "tile_height", 32), s)[2])(
+    S.random_triangles(2000, 256, 160, 0.08, 0.6, name="big32"))
+
+
+@pytest.fixture(scope="module", params=list(SCENES))
+def pipeline(request):
+    """Run every stage once per scene through the C ABI and the oracle."""
+    sc = SCENES[request.param]()
+    tens = Hh.scene_tensors(sc)
+    counts, rects, geo, attr = Hh.preprocess(sc, tens)
+    tri_off = Hh.scan(counts)
+    K = int(tri_off[-1])
+    keys, ids = Hh.emit_keys(sc, tri_off, K, tens)
+    tiles = Hh.num_tiles(sc)
+    end_bit = 32 + max(0, int(np.ceil(np.log2(tiles)))) if tiles > 1 else 32
+    skeys, sids = Hh.sort_pairs(keys, ids, 0, end_bit)
+    offsets = Hh.tile_ranges(skeys, tiles)
+    st = O.build_lists_staged(sc.vertices, sc.indices, sc.width, sc.height, sc.tile_width, sc.tile_height)
+    return dict(sc=sc, tens=tens, counts=counts, rects=rects, geo=geo, attr=attr, tri_off=tri_off, K=K, keys=keys,
+                ids=ids, skeys=skeys, sids=sids, offsets=offsets, st=st, tiles=tiles)
+
+
+def test_preprocess_counts_and_rects_bit_exact(pipeline):
+    p = pipeline
+    assert np.array_equal(p["counts"].cpu().numpy(), p["st"].counts)
+    assert np.array_equal(p["rects"].cpu().numpy(), p["st"].rects)
+
+
+def test_preprocess_records_bit_exact(pipeline):
+    p, sc = pipeline, pipeline["sc"]
+    M = O.bary_matrices(sc.vertices, sc.indices).reshape(-1, 9)
+    geo = p["geo"].cpu().numpy()
+    assert np.array_equal(geo[:, :9].view(np.uint32), M.view(np.uint32))
+    v = sc.vertices[sc.indices]                      # [T,3,4]
+    assert np.array_equal(geo[:, 9:12], v[:, :, 2])
+    assert np.array_equal(geo[:, 12:15], v[:, :, 3])
+    attr = p["attr"].cpu().numpy()
+    assert np.array_equal(attr[:, 0:3], sc.opacities[sc.indices])
+    assert np.array_equal(attr[:, 3:12], sc.colors[sc.indices].reshape(-1, 9))
+    assert np.array_equal(attr[:, 12:15].view(np.int32), sc.indices)
+    assert np.array_equal(attr[:, 16:22], v[:, :, :2].reshape(-1, 6))
+
+
+def test_scan_bit_exact(pipeline):
+    p = pipeline
+    assert np.array_equal(p["tri_off"].cpu().numpy().astype(np.int64), p["st"].tri_offsets)
+
+
+def test_emitted_keys_bit_exact(pipeline):
+    p = pipeline
+    assert p["K"] == p["st"].keys_unsorted.shape[0]
+    assert np.array_equal(p["keys"].cpu().numpy().view(np.uint64), p["st"].keys_unsorted)
+    assert np.array_equal(p["ids"].cpu().numpy(), p["st"].ids_unsorted)
+
+
+def test_sorted_keys_and_ids_bit_exact(pipeline):
+    p = pipeline
+    assert np.array_equal(p["skeys"].cpu().numpy().view(np.uint64), p["st"].keys_sorted)
+    assert np.array_equal(p["sids"].cpu().numpy(), p["st"].ids_sorted)
+
+
+def test_tile_ranges_bit_exact(pipeline):
+    p = pipeline
+    assert np.array_equal(p["offsets"].cpu().numpy(), p["st"].offsets)
+    # and they are the reference's objects: per-tile counts cumulated (oracle native path)
+    sc = p["sc"]
+    li = O.build_lists(sc.vertices, sc.indices, sc.width, sc.height, sc.tile_width, sc.tile_height)
+    assert np.array_equal(p["offsets"].cpu().numpy(), li.offsets)
+    assert np.array_equal(p["sids"].cpu().numpy(), li.ids)
+
+
+MODES = [
+    dict(per_pixel_sort=True, max_layers=32, thr=1 / 256),    # the reference default
+    dict(per_pixel_sort=False, max_layers=32, thr=1 / 256),
+    dict(per_pixel_sort=True, max_layers=7, thr=1 / 256),
+    dict(per_pixel_sort=True, max_layers=0, thr=1 / 256),     # <= 0 means unlimited (T+1)
+    dict(per_pixel_sort=False, max_layers=0, thr=0.2),
+    dict(per_pixel_sort=True, max_layers=40, thr=0.5),        # second batch only while alpha > thr
+]
+
+
+@pytest.mark.parametrize("mode", MODES, ids=lambda m: f"sort{int(m['per_pixel_sort'])}_L{m['max_layers']}_t{m['thr']:.3f}")
+def test_forward_and_backward_vs_oracle(pipeline, mode):
+    p, sc = pipeline, pipeline["sc"]
+    T = sc.num_triangles
+    ml = mode["max_layers"] if mode["max_layers"] > 0 else T + 1
+    fwd = Hh.blend_forward(sc, p["geo"], p["attr"], p["sids"], p["offsets"], mode["thr"], mode["per_pixel_sort"], ml)
+    image, depth, fw, ends = [t.cpu().numpy() for t in fwd]
+    of = O.forward(sc.vertices, sc.indices, sc.colors, sc.opacities, sc.width, sc.height, sc.tile_width,
+                   sc.tile_height, mode["thr"], mode["per_pixel_sort"], ml)
+    assert np.array_equal(ends, of.ends), "fragment selection differs"
+    assert Hh.rel_err(image, of.image) <= IMG_TOL
+    assert np.array_equal(np.isinf(depth), np.isinf(of.depthmap))
+    fin = np.isfinite(of.depthmap)
+    assert Hh.rel_err(depth[fin], of.depthmap[fin]) <= IMG_TOL if fin.any() else True
+    assert Hh.rel_err(fw, of.final_weights) <= IMG_TOL
+    # the kernels mirror the oracle's arithmetic: the result is in fact identical
+    assert np.array_equal(image.view(np.uint32), of.image.view(np.uint32))
+    assert np.array_equal(depth.view(np.uint32), of.depthmap.view(np.uint32))
+
+    rng = np.random.default_rng(7)
+    gi = rng.normal(size=image.shape).astype(np.float32)
+    gd = rng.normal(size=depth.shape).astype(np.float32)
+    g = Hh.blend_backward(sc, p["geo"], p["attr"], p["sids"], p["offsets"], fwd, Hh.cuda(gi), Hh.cuda(gd),
+                          mode["per_pixel_sort"], ml)
+    og = O.backward(sc.vertices, sc.indices, sc.colors, sc.opacities, sc.width, sc.height, of, gi, gd, sc.tile_width,
+                    sc.tile_height, mode["per_pixel_sort"], ml)
+    for name, a, b in zip(("vertices", "colors", "opacities"), g, og):
+        a = a.cpu().numpy()
+        assert np.all(a[:, 2] == 0) if name == "vertices" else True
+        err, err_max = Hh.rel_l2(a, b), Hh.rel_err(a, b)
+        assert err <= GRAD_TOL, f"grad_{name}: relative L2 error {err:.3e}"
+        assert err_max <= GRAD_TOL_MAX, f"grad_{name}: worst element {err_max:.3e}"
+
+
+def test_large_sort_random_keys():
+    """Sort alone on 3M random 45-bit keys, odd length, against numpy's stable sort."""
+    rng = np.random.default_rng(3)
+    n = 3_000_017
+    keys = rng.integers(0, 1 << 45, n, dtype=np.int64)
+    keys[::7] = keys[3]           # many duplicates: stability matters
+    vals = np.arange(n, dtype=np.int32)
+    sk, sv = Hh.sort_pairs(Hh.cuda(keys), Hh.cuda(vals), 0, 45)
+    order = np.argsort(keys, kind="stable")
+    assert np.array_equal(sk.cpu().numpy(), keys[order])
+    assert np.array_equal(sv.cpu().numpy(), vals[order])
+
+
+@pytest.mark.parametrize("n", [0, 1, 255, 2048, 2049, 100_000, 5_000_001])
+def test_scan_sizes(n):
+    rng = np.random.default_rng(n)
+    x = rng.integers(0, 50, n, dtype=np.int32)
+    out = Hh.scan(Hh.cuda(x)).cpu().numpy().astype(np.int64)
+    ref = np.zeros(n + 1, np.int64)
+    np.cumsum(x, out=ref[1:])
+    assert np.array_equal(out, ref)
+
+
+@pytest.mark.parametrize("n,bits", [(1, 64), (4096, 64), (4097, 40), (12345, 33), (70_000, 64)])
+def test_sort_sizes(n, bits):
+    rng = np.random.default_rng(n)
+    keys = rng.integers(0, 1 << min(bits, 62), n, dtype=np.int64)
+    vals = rng.integers(0, 1 << 31, n, dtype=np.int32)
+    sk, sv = Hh.sort_pairs(Hh.cuda(keys), Hh.cuda(vals), 0, bits)
+    order = np.argsort(keys, kind="stable")
+    assert np.array_equal(sk.cpu().numpy(), keys[order])
+    assert np.array_equal(sv.cpu().numpy(), vals[order])

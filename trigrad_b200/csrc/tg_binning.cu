@@ -1,0 +1,440 @@
+// Binning stages: per-triangle preprocess, device-wide scan, key emission, tile ranges.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "tg_common.cuh"
+
+namespace tg {
+
+// ================================================================================================
+// Stage 1: preprocess.  One thread per triangle: gathers its three vertices and attributes,
+// counts the tiles its bounding box touches and writes the two packed records the compositing
+// kernels stream.  HBM-bound: reads 12 B + 3 gathers of (16+12+4) B, writes 4 + 64 + 96 B.
+__global__ void __launch_bounds__(256) preprocess_kernel(const float4* __restrict__ vertices,
+                                                         const int* __restrict__ indices,
+                                                         const float* __restrict__ colors,
+                                                         const float* __restrict__ opacities, int T, int W, int H,
+                                                         int tw, int th, int tiles_x, int tiles_y,
+                                                         uint32_t* __restrict__ tri_counts, int4* __restrict__ tri_rects,
+                                                         float4* __restrict__ tri_geo, float4* __restrict__ tri_attr) {
+    int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    int ia = indices[3 * (size_t)t], ib = indices[3 * (size_t)t + 1], ic = indices[3 * (size_t)t + 2];
+    float4 a = vertices[ia], b = vertices[ib], c = vertices[ic];
+
+    Rect r;
+    bool ok = tile_rect(a.x, a.y, b.x, b.y, c.x, c.y, W, H, tw, th, tiles_x, tiles_y, r);
+    tri_counts[t] = ok ? (uint32_t)(r.x1 - r.x0 + 1) * (uint32_t)(r.y1 - r.y0 + 1) : 0u;
+    if (tri_rects) tri_rects[t] = make_int4(r.x0, r.y0, r.x1, r.y1);
+
+    // barycentric matrix, reference render.cu:324-336: plain mul/sub/div
+    float denom = add(add(mul(a.x, sub(b.y, c.y)), mul(b.x, sub(c.y, a.y))), mul(c.x, sub(a.y, b.y)));
+    if (fabsf(denom) < kEffZero) denom = 1.0f;
+    float m0 = div(sub(b.y, c.y), denom);
+    float m1 = div(sub(c.x, b.x), denom);
+    float m2 = div(sub(mul(b.x, c.y), mul(c.x, b.y)), denom);
+    float m3 = div(sub(c.y, a.y), denom);
+    float m4 = div(sub(a.x, c.x), denom);
+    float m5 = div(sub(mul(c.x, a.y), mul(a.x, c.y)), denom);
+    float m6 = div(sub(a.y, b.y), denom);
+    float m7 = div(sub(b.x, a.x), denom);
+    float m8 = div(sub(mul(a.x, b.y), mul(b.x, a.y)), denom);
+
+    // Lower bound of the per-pixel sort depth: with weights of one sign the interpolated depth is
+    // a convex combination of the vertex depths; a relative margin covers fp32 rounding.
+    float zlow = -INFINITY;
+    bool same_sign = (a.w > 0.f && b.w > 0.f && c.w > 0.f) || (a.w < 0.f && b.w < 0.f && c.w < 0.f);
+    if (same_sign) {
+        float zmin = fminf(fminf(a.z, b.z), c.z);
+        float zabs = fmaxf(fmaxf(fabsf(a.z), fabsf(b.z)), fabsf(c.z));
+        float lo = zmin - 4e-6f * zabs;
+        if (isfinite(lo)) zlow = lo;
+    }
+
+    float4* g = tri_geo + 4 * (size_t)t;
+    g[0] = make_float4(m0, m1, m2, m3);
+    g[1] = make_float4(m4, m5, m6, m7);
+    g[2] = make_float4(m8, a.z, b.z, c.z);
+    g[3] = make_float4(a.w, b.w, c.w, zlow);
+
+    float4* q = tri_attr + 6 * (size_t)t;
+    const float* ca = colors + 3 * (size_t)ia;
+    const float* cb = colors + 3 * (size_t)ib;
+    const float* cc = colors + 3 * (size_t)ic;
+    q[0] = make_float4(opacities[ia], opacities[ib], opacities[ic], ca[0]);
+    q[1] = make_float4(ca[1], ca[2], cb[0], cb[1]);
+    q[2] = make_float4(cb[2], cc[0], cc[1], cc[2]);
+    q[3] = make_float4(__int_as_float(ia), __int_as_float(ib), __int_as_float(ic), 0.f);
+    q[4] = make_float4(a.x, a.y, b.x, b.y);
+    q[5] = make_float4(c.x, c.y, 0.f, 0.f);
+}
+
+// ================================================================================================
+// Stage 2: single-pass exclusive scan with decoupled look-back.
+// scratch: word 0 = ticket counter (uint32, padded to 8 bytes), then one uint64 per partition:
+// (flag << 32) | value, flag 0 = nothing yet, 1 = partition aggregate, 2 = inclusive prefix.
+constexpr int kScanThreads = 256;
+constexpr int kScanItems = 8;
+constexpr int kScanTile = kScanThreads * kScanItems;
+constexpr uint32_t kSpinLimit = 1u << 22;   // bounded wait: ~ seconds with the nanosleep below
+
+__device__ __forceinline__ uint64_t ld_volatile(const uint64_t* p) { return *(const volatile uint64_t*)p; }
+__device__ __forceinline__ void st_volatile(uint64_t* p, uint64_t v) { *(volatile uint64_t*)p = v; }
+
+// Wait (bounded) until the partition word has a non-zero flag.  Returns false if the wait ran out.
+__device__ __forceinline__ bool wait_flag(const uint64_t* p, uint64_t& word) {
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        word = ld_volatile(p);
+        if ((word >> 32) != 0) return true;
+        if (it > 64) __nanosleep(100);
+    }
+    return false;
+}
+
+__global__ void __launch_bounds__(kScanThreads) scan_kernel(const uint32_t* __restrict__ in,
+                                                            uint32_t* __restrict__ out, int n, int num_parts,
+                                                            uint32_t* ticket, uint64_t* part_status,
+                                                            uint32_t* status) {
+    __shared__ uint32_t s_part;
+    __shared__ uint32_t s_warp[kScanThreads / 32];
+    __shared__ uint32_t s_excl;
+    if (threadIdx.x == 0) s_part = atomicAdd(ticket, 1u);
+    __syncthreads();
+    const int p = (int)s_part;
+    if (p >= num_parts) return;
+    const int base = p * kScanTile + threadIdx.x * kScanItems;
+
+    uint32_t v[kScanItems];
+    uint32_t sum = 0;
+#pragma unroll
+    for (int i = 0; i < kScanItems; i++) {
+        v[i] = (base + i < n) ? in[base + i] : 0u;
+        sum += v[i];
+    }
+    // block exclusive scan of `sum`
+    uint32_t incl = sum;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        uint32_t y = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane_id() >= (unsigned)d) incl += y;
+    }
+    const int warp = threadIdx.x >> 5;
+    if (lane_id() == 31) s_warp[warp] = incl;
+    __syncthreads();
+    uint32_t warp_off = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < kScanThreads / 32; w++) {
+        uint32_t x = s_warp[w];
+        if (w < warp) warp_off += x;
+        total += x;
+    }
+    uint32_t thread_excl = warp_off + incl - sum;
+
+    if (warp == 0) {
+        uint32_t excl = 0;
+        if (p == 0) {
+            if (lane_id() == 0) st_volatile(&part_status[0], (2ull << 32) | total);
+        } else {
+            if (lane_id() == 0) st_volatile(&part_status[p], (1ull << 32) | total);
+            int q = p - 1 - (int)lane_id();
+            bool failed = false;
+            while (true) {
+                uint64_t word = 2ull << 32;   // virtual partitions before 0: inclusive prefix 0
+                if (q >= 0 && !wait_flag(&part_status[q], word)) { failed = true; word = 2ull << 32; }
+                const uint32_t flag = (uint32_t)(word >> 32), val = (uint32_t)word;
+                const unsigned incl_mask = __ballot_sync(0xffffffffu, flag == 2u);
+                uint32_t contrib = val;
+                if (incl_mask) {
+                    const int first = __ffs(incl_mask) - 1;
+                    if ((int)lane_id() > first) contrib = 0;
+                }
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) contrib += __shfl_xor_sync(0xffffffffu, contrib, d);
+                excl += contrib;
+                if (incl_mask) break;
+                q -= 32;
+            }
+            if (__any_sync(0xffffffffu, failed) && lane_id() == 0) atomicExch(status, 1u);
+            if (lane_id() == 0) st_volatile(&part_status[p], (2ull << 32) | (uint64_t)(excl + total));
+        }
+        if (lane_id() == 0) {
+            s_excl = excl;
+            if (p == num_parts - 1) out[n] = excl + total;
+        }
+    }
+    __syncthreads();
+    uint32_t run = s_excl + thread_excl;
+#pragma unroll
+    for (int i = 0; i < kScanItems; i++) {
+        if (base + i < n) out[base + i] = run;
+        run += v[i];
+    }
+}
+
+// ================================================================================================
+// Stage 3: key emission.
+struct Plane { float A, B, C; };
+
+// reference render.cu:140-152, `1.0 / det` in double.
+__device__ __forceinline__ Plane depth_plane(float ax, float ay, float az, float bx, float by, float bz, float cx,
+                                             float cy, float cz) {
+    float det = add(add(mul(ax, sub(by, cy)), mul(bx, sub(cy, ay))), mul(cx, sub(ay, by)));
+    float id = (float)__ddiv_rn(1.0, (double)det);
+    Plane p;
+    p.A = mul(add(add(mul(az, sub(by, cy)), mul(bz, sub(cy, ay))), mul(cz, sub(ay, by))), id);
+    p.B = mul(add(add(mul(ax, sub(bz, cz)), mul(bx, sub(cz, az))), mul(cx, sub(az, bz))), id);
+    p.C = mul(add(add(mul(ax, sub(mul(by, cz), mul(cy, bz))), mul(bx, sub(mul(cy, az), mul(ay, cz)))),
+                  mul(cx, sub(mul(ay, bz), mul(by, az)))),
+              id);
+    return p;
+}
+
+__device__ __forceinline__ float plane_depth(const Plane& p, float x, float y) { return fma_(p.A, x, fma_(p.B, y, p.C)); }
+
+// One Sutherland-Hodgman pass against an axis-aligned half-plane (reference render.cu:159-189).
+template <int AXIS>
+__device__ __forceinline__ int clip_pass(const float2* in, int n_in, float2* out, float bound) {
+    auto dist = [&](const float2& p) -> float {
+        if (AXIS == 0) return sub(p.x, bound);
+        if (AXIS == 1) return sub(bound, p.x);
+        if (AXIS == 2) return sub(p.y, bound);
+        return sub(bound, p.y);
+    };
+    int n_out = 0;
+    float2 p0 = in[n_in - 1];
+    float d0 = dist(p0);
+    bool in0 = d0 >= 0.f;
+    for (int i = 0; i < n_in; i++) {
+        float2 p1 = in[i];
+        float d1 = dist(p1);
+        bool in1 = d1 >= 0.f;
+        if (in1 != in0) {
+            float t = div(d0, sub(d0, d1));
+            out[n_out++] = make_float2(fma_(t, sub(p1.x, p0.x), p0.x), fma_(t, sub(p1.y, p0.y), p0.y));
+        }
+        if (in1) out[n_out++] = p1;
+        p0 = p1; d0 = d1; in0 = in1;
+    }
+    return n_out;
+}
+
+struct TriXYZ { float ax, ay, az, bx, by, bz, cx, cy, cz; };
+
+__device__ float tile_key(const TriXYZ& v, const Plane& pl, int tx, int ty, int W, int H, int tw, int th) {
+    const float xmin = sub(mul(div((float)(tx * tw), (float)W), 2.f), 1.f);
+    const float xmax = sub(mul(div((float)((tx + 1) * tw), (float)W), 2.f), 1.f);
+    const float ymin = sub(mul(div((float)(ty * th), (float)H), 2.f), 1.f);
+    const float ymax = sub(mul(div((float)((ty + 1) * th), (float)H), 2.f), 1.f);
+    // triangle entirely inside the tile: the clipper would return it unchanged
+    const float lox = fminf(fminf(v.ax, v.bx), v.cx), hix = fmaxf(fmaxf(v.ax, v.bx), v.cx);
+    const float loy = fminf(fminf(v.ay, v.by), v.cy), hiy = fmaxf(fmaxf(v.ay, v.by), v.cy);
+    if (sub(lox, xmin) >= 0.f && sub(xmax, hix) >= 0.f && sub(loy, ymin) >= 0.f && sub(ymax, hiy) >= 0.f) {
+        float md0 = fminf(FLT_MAX, plane_depth(pl, v.ax, v.ay));
+        md0 = fminf(md0, plane_depth(pl, v.bx, v.by));
+        return fminf(md0, plane_depth(pl, v.cx, v.cy));
+    }
+    float2 poly[8], buf[8];
+    poly[0] = make_float2(v.ax, v.ay);
+    poly[1] = make_float2(v.bx, v.by);
+    poly[2] = make_float2(v.cx, v.cy);
+    int n = clip_pass<0>(poly, 3, buf, xmin);
+    if (n <= 0) return 1e30f;
+    n = clip_pass<1>(buf, n, poly, xmax);
+    if (n <= 0) return 1e30f;
+    n = clip_pass<2>(poly, n, buf, ymin);
+    if (n <= 0) return 1e30f;
+    n = clip_pass<3>(buf, n, poly, ymax);
+    if (n <= 0) return 1e30f;
+    float md = FLT_MAX;
+    for (int i = 0; i < n; i++) md = fminf(md, plane_depth(pl, poly[i].x, poly[i].y));
+    return md;
+}
+
+constexpr int kEmitSmall = 16;   // triangles touching more tiles than this are emitted by the whole warp
+
+__global__ void __launch_bounds__(256) emit_keys_kernel(const float4* __restrict__ vertices,
+                                                        const int* __restrict__ indices, int T, int W, int H, int tw,
+                                                        int th, int tiles_x, int tiles_y,
+                                                        const uint32_t* __restrict__ tri_offsets,
+                                                        uint64_t* __restrict__ keys, uint32_t* __restrict__ ids,
+                                                        uint32_t capacity) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    TriXYZ v = {};
+    Rect r = {0, -1, 0, -1};
+    uint32_t base = 0, n = 0;
+    Plane pl = {0.f, 0.f, 0.f};
+    if (t < T) {
+        int ia = indices[3 * (size_t)t], ib = indices[3 * (size_t)t + 1], ic = indices[3 * (size_t)t + 2];
+        float4 a = vertices[ia], b = vertices[ib], c = vertices[ic];
+        v = {a.x, a.y, a.z, b.x, b.y, b.z, c.x, c.y, c.z};
+        if (tile_rect(a.x, a.y, b.x, b.y, c.x, c.y, W, H, tw, th, tiles_x, tiles_y, r)) {
+            n = (uint32_t)(r.x1 - r.x0 + 1) * (uint32_t)(r.y1 - r.y0 + 1);
+            base = tri_offsets[t];
+            if ((uint64_t)base + n > capacity) n = 0;   // defensive: host checks K <= capacity before launching
+            pl = depth_plane(a.x, a.y, a.z, b.x, b.y, b.z, c.x, c.y, c.z);
+        }
+    }
+    if (n > 0 && n <= (uint32_t)kEmitSmall) {
+        const int ny = r.y1 - r.y0 + 1;
+        for (uint32_t i = 0; i < n; i++) {
+            int tx = r.x0 + (int)i / ny, ty = r.y0 + (int)i % ny;
+            float key = tile_key(v, pl, tx, ty, W, H, tw, th);
+            keys[base + i] = ((uint64_t)(uint32_t)(ty * tiles_x + tx) << 32) | float_to_ordered(key);
+            ids[base + i] = (uint32_t)t;
+        }
+    }
+    // large triangles: the warp walks the rectangle together
+    unsigned big = __ballot_sync(0xffffffffu, n > (uint32_t)kEmitSmall);
+    while (big) {
+        const int src = __ffs(big) - 1;
+        big &= big - 1;
+        TriXYZ bv;
+        bv.ax = __shfl_sync(0xffffffffu, v.ax, src); bv.ay = __shfl_sync(0xffffffffu, v.ay, src);
+        bv.az = __shfl_sync(0xffffffffu, v.az, src); bv.bx = __shfl_sync(0xffffffffu, v.bx, src);
+        bv.by = __shfl_sync(0xffffffffu, v.by, src); bv.bz = __shfl_sync(0xffffffffu, v.bz, src);
+        bv.cx = __shfl_sync(0xffffffffu, v.cx, src); bv.cy = __shfl_sync(0xffffffffu, v.cy, src);
+        bv.cz = __shfl_sync(0xffffffffu, v.cz, src);
+        Plane bp;
+        bp.A = __shfl_sync(0xffffffffu, pl.A, src);
+        bp.B = __shfl_sync(0xffffffffu, pl.B, src);
+        bp.C = __shfl_sync(0xffffffffu, pl.C, src);
+        const int bx0 = __shfl_sync(0xffffffffu, r.x0, src), by0 = __shfl_sync(0xffffffffu, r.y0, src);
+        const int by1 = __shfl_sync(0xffffffffu, r.y1, src);
+        const uint32_t bn = __shfl_sync(0xffffffffu, n, src), bbase = __shfl_sync(0xffffffffu, base, src);
+        const uint32_t bt = __shfl_sync(0xffffffffu, (uint32_t)t, src);
+        const int ny = by1 - by0 + 1;
+        for (uint32_t i = lane_id(); i < bn; i += 32) {
+            int tx = bx0 + (int)(i / (uint32_t)ny), ty = by0 + (int)(i % (uint32_t)ny);
+            float key = tile_key(bv, bp, tx, ty, W, H, tw, th);
+            keys[bbase + i] = ((uint64_t)(uint32_t)(ty * tiles_x + tx) << 32) | float_to_ordered(key);
+            ids[bbase + i] = bt;
+        }
+    }
+}
+
+// ================================================================================================
+// Stage 5: tile ranges from the sorted keys.  Thread i looks at the boundary before entry i.
+__global__ void __launch_bounds__(256) tile_ranges_kernel(const uint64_t* __restrict__ keys, uint32_t n, int tiles,
+                                                          int* __restrict__ offsets) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i > n) return;
+    const int prev = (i == 0) ? -1 : (int)(keys[i - 1] >> 32);
+    int cur = (i == n) ? tiles : (int)(keys[i] >> 32);
+    if (cur > tiles) cur = tiles;
+    for (int t = prev + 1; t <= cur; t++) offsets[t] = (int)i;
+}
+
+}  // namespace tg
+
+// ================================================================================================
+// host side
+namespace tg_host {
+static thread_local char g_err[512] = "";
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+int cuda_fail(cudaError_t e, const char* what) {
+    set_error("CUDA error %d (%s) at %s", (int)e, cudaGetErrorString(e), what);
+    return TG_ERR_CUDA;
+}
+const char* last_error() { return g_err; }
+}  // namespace tg_host
+
+extern "C" {
+
+int tg_version(void) { return 1; }
+
+const char* tg_last_error(void) { return tg_host::last_error(); }
+
+const char* tg_status_string(int s) {
+    switch (s) {
+        case TG_OK: return "ok";
+        case TG_ERR_BAD_ARG: return "bad argument";
+        case TG_ERR_WORKSPACE: return "workspace too small";
+        case TG_ERR_CAPACITY: return "list capacity exceeded";
+        case TG_ERR_DEVICE_FLAG: return "device error flag set (a bounded wait ran out)";
+        case TG_ERR_CUDA: return "CUDA error";
+        default: return "unknown status";
+    }
+}
+
+static int check_dims(int T, int W, int H, int tw, int th) {
+    TG_REQUIRE(T >= 0, "T < 0");
+    TG_REQUIRE(W > 0 && H > 0, "image size must be positive");
+    TG_REQUIRE(tw > 0 && th > 0, "tile size must be positive");
+    TG_REQUIRE(tw * th <= 1024, "tile_width * tile_height must be <= 1024");
+    return TG_OK;
+}
+
+int tg_preprocess(const float* vertices, const int32_t* indices, const float* colors, const float* opacities, int T,
+                  int W, int H, int tw, int th, uint32_t* tri_counts, int32_t* tri_rects, float* tri_geo,
+                  float* tri_attr, tg_stream_t stream) {
+    if (int s = check_dims(T, W, H, tw, th)) return s;
+    if (T == 0) return TG_OK;
+    TG_REQUIRE(vertices && indices && colors && opacities && tri_counts && tri_geo && tri_attr, "null pointer");
+    TG_REQUIRE(((uintptr_t)vertices & 15) == 0 && ((uintptr_t)tri_geo & 15) == 0 && ((uintptr_t)tri_attr & 15) == 0 &&
+                   ((uintptr_t)tri_rects & 15) == 0,
+               "vertices / tri_geo / tri_attr / tri_rects must be 16-byte aligned");
+    const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
+    tg::preprocess_kernel<<<(T + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+        (const float4*)vertices, indices, colors, opacities, T, W, H, tw, th, tiles_x, tiles_y, tri_counts,
+        (int4*)tri_rects, (float4*)tri_geo, (float4*)tri_attr);
+    TG_LAUNCH_CHECK("preprocess_kernel");
+    return TG_OK;
+}
+
+size_t tg_scan_scratch_bytes(int n) {
+    size_t parts = (size_t)((n > 0 ? n : 0) + tg::kScanTile - 1) / tg::kScanTile;
+    return 8 + 8 * (parts + 1);
+}
+
+int tg_scan(const uint32_t* in, uint32_t* out, int n, void* scratch, size_t scratch_bytes, uint32_t* status,
+            tg_stream_t stream) {
+    TG_REQUIRE(n >= 0, "n < 0");
+    TG_REQUIRE(out && scratch && status, "null pointer");
+    TG_REQUIRE(((uintptr_t)scratch & 7) == 0, "scratch must be 8-byte aligned");
+    if (scratch_bytes < tg_scan_scratch_bytes(n)) {
+        tg_host::set_error("scan scratch: need %zu bytes, got %zu", tg_scan_scratch_bytes(n), scratch_bytes);
+        return TG_ERR_WORKSPACE;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    if (n == 0) {
+        TG_CUDA(cudaMemsetAsync(out, 0, sizeof(uint32_t), s));
+        return TG_OK;
+    }
+    TG_REQUIRE(in != nullptr, "null pointer");
+    const int parts = (n + tg::kScanTile - 1) / tg::kScanTile;
+    TG_CUDA(cudaMemsetAsync(scratch, 0, tg_scan_scratch_bytes(n), s));
+    tg::scan_kernel<<<parts, tg::kScanThreads, 0, s>>>(in, out, n, parts, (uint32_t*)scratch,
+                                                      (uint64_t*)((char*)scratch + 8), status);
+    TG_LAUNCH_CHECK("scan_kernel");
+    return TG_OK;
+}
+
+int tg_emit_keys(const float* vertices, const int32_t* indices, int T, int W, int H, int tw, int th,
+                 const uint32_t* tri_offsets, uint64_t* keys, uint32_t* ids, uint32_t capacity, tg_stream_t stream) {
+    if (int s = check_dims(T, W, H, tw, th)) return s;
+    if (T == 0) return TG_OK;
+    TG_REQUIRE(vertices && indices && tri_offsets && keys && ids, "null pointer");
+    const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
+    tg::emit_keys_kernel<<<(T + 255) / 256, 256, 0, (cudaStream_t)stream>>>((const float4*)vertices, indices, T, W, H,
+                                                                            tw, th, tiles_x, tiles_y, tri_offsets, keys,
+                                                                            ids, capacity);
+    TG_LAUNCH_CHECK("emit_keys_kernel");
+    return TG_OK;
+}
+
+int tg_tile_ranges(const uint64_t* sorted_keys, uint32_t n, int tiles, int32_t* offsets, tg_stream_t stream) {
+    TG_REQUIRE(tiles > 0 && offsets, "bad tiles / offsets");
+    TG_REQUIRE(n == 0 || sorted_keys, "null keys");
+    TG_REQUIRE(n < 0x80000000u, "K must stay below 2^31");
+    const uint32_t threads = n + 1;
+    tg::tile_ranges_kernel<<<(threads + 255) / 256, 256, 0, (cudaStream_t)stream>>>(sorted_keys, n, tiles, offsets);
+    TG_LAUNCH_CHECK("tile_ranges_kernel");
+    return TG_OK;
+}
+
+}  // extern "C"

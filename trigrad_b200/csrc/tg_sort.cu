@@ -1,0 +1,289 @@
+// Stage 4: onesweep least-significant-digit radix sort of (uint64 key, uint32 value) pairs.
+//
+// One histogram kernel counts every 8-bit digit of every pass in a single read of the keys and
+// turns the counts into global digit offsets.  Then one kernel per pass: each CTA takes a tile of
+// kSortTile pairs (ticket order), ranks them stably by the pass digit (warp match-any ranking),
+// publishes its per-digit counts, obtains the counts of all earlier tiles by decoupled look-back
+// (one thread per digit, bounded waits) and scatters keys and values through shared memory so
+// that global writes are contiguous runs per digit.  Every pass reads 12 B and writes 12 B per
+// pair: HBM-bound.
+#include "tg_common.cuh"
+
+namespace tg {
+
+constexpr int kRadixBits = 8;
+constexpr int kRadix = 1 << kRadixBits;
+constexpr int kMaxPasses = 8;
+constexpr int kSortThreads = 256;
+constexpr int kSortWarps = kSortThreads / 32;
+constexpr int kSortItems = 16;
+constexpr int kSortTile = kSortThreads * kSortItems;   // 4096 pairs per CTA
+constexpr uint32_t kSortSpinLimit = 1u << 22;
+
+constexpr uint64_t kFlagAggregate = 1ull << 32;
+constexpr uint64_t kFlagInclusive = 2ull << 32;
+
+// scratch layout (bytes): [0, 8 KB) digit histograms / offsets [kMaxPasses][256] uint32,
+// [8 KB, 8 KB + 64) tickets[kMaxPasses] + histogram-done counter, then the look-back words
+// [passes][parts][256] uint64.
+constexpr size_t kHistBytes = (size_t)kMaxPasses * kRadix * sizeof(uint32_t);
+constexpr size_t kCtrBytes = 64;
+
+__device__ __forceinline__ uint32_t block_exclusive_scan_256(uint32_t v, uint32_t* s_warp_tot /*[8]*/,
+                                                             uint32_t* block_total = nullptr) {
+    uint32_t incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        uint32_t y = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane_id() >= (unsigned)d) incl += y;
+    }
+    const int warp = threadIdx.x >> 5;
+    __syncthreads();   // protect s_warp_tot from a previous use
+    if (lane_id() == 31) s_warp_tot[warp] = incl;
+    __syncthreads();
+    uint32_t off = 0, tot = 0;
+#pragma unroll
+    for (int w = 0; w < kSortWarps; w++) {
+        uint32_t x = s_warp_tot[w];
+        if (w < warp) off += x;
+        tot += x;
+    }
+    if (block_total) *block_total = tot;
+    return off + incl - v;
+}
+
+__global__ void __launch_bounds__(kSortThreads) sort_histogram_kernel(const uint64_t* __restrict__ keys, uint32_t n,
+                                                                      int begin_bit, int end_bit, int passes,
+                                                                      uint32_t* __restrict__ hist,
+                                                                      uint32_t* __restrict__ done_counter) {
+    __shared__ uint32_t s_hist[kMaxPasses * kRadix];
+    __shared__ uint32_t s_warp_tot[kSortWarps];
+    __shared__ bool s_last;
+    for (int i = threadIdx.x; i < passes * kRadix; i += kSortThreads) s_hist[i] = 0;
+    __syncthreads();
+    const uint32_t stride = gridDim.x * kSortThreads;
+    for (uint32_t i = blockIdx.x * kSortThreads + threadIdx.x; i < n; i += stride) {
+        const uint64_t k = keys[i];
+        for (int p = 0; p < passes; p++) {
+            const int shift = begin_bit + p * kRadixBits;
+            const int bits = min(kRadixBits, end_bit - shift);
+            const uint32_t d = (uint32_t)(k >> shift) & ((1u << bits) - 1u);
+            atomicAdd(&s_hist[p * kRadix + d], 1u);
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < passes * kRadix; i += kSortThreads) {
+        const uint32_t c = s_hist[i];
+        if (c) atomicAdd(&hist[i], c);
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(done_counter, 1u) == gridDim.x - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // last CTA: counts -> exclusive global digit offsets, per pass
+    for (int p = 0; p < passes; p++) {
+        const uint32_t c = __ldcg(&hist[p * kRadix + threadIdx.x]);
+        const uint32_t e = block_exclusive_scan_256(c, s_warp_tot);
+        hist[p * kRadix + threadIdx.x] = e;
+    }
+}
+
+__device__ __forceinline__ uint64_t ld_word(const uint64_t* p) { return *(const volatile uint64_t*)p; }
+__device__ __forceinline__ void st_word(uint64_t* p, uint64_t v) { *(volatile uint64_t*)p = v; }
+
+struct SortSmem {
+    uint64_t keys[kSortTile];
+    uint32_t vals[kSortTile];
+    uint32_t warp_hist[kSortWarps][kRadix];
+    uint32_t digit_start[kRadix];
+    uint32_t bin_offset[kRadix];
+    uint32_t warp_tot[kSortWarps];
+    uint32_t part;
+    uint32_t fail;
+};
+
+__global__ void __launch_bounds__(kSortThreads) onesweep_pass_kernel(
+    const uint64_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in, uint64_t* __restrict__ keys_out,
+    uint32_t* __restrict__ vals_out, uint32_t n, int shift, int bits, const uint32_t* __restrict__ digit_offsets,
+    uint32_t* __restrict__ ticket, uint64_t* __restrict__ lookback /*[parts][256]*/, uint32_t* __restrict__ status) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    SortSmem& sm = *reinterpret_cast<SortSmem*>(smem_raw);
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const unsigned lane = lane_id();
+    const uint32_t digit_mask = (1u << bits) - 1u;
+
+    if (tid == 0) { sm.part = atomicAdd(ticket, 1u); sm.fail = 0; }
+    for (int i = tid; i < kSortWarps * kRadix; i += kSortThreads) (&sm.warp_hist[0][0])[i] = 0;
+    __syncthreads();
+    const uint32_t p = sm.part;
+    const uint64_t tile_base = (uint64_t)p * kSortTile;
+    if (tile_base >= n) return;
+    const uint32_t valid = (uint32_t)min((uint64_t)kSortTile, (uint64_t)n - tile_base);
+
+    // warp-striped load: warp w owns [w*512, (w+1)*512), lane l takes items i*32 + l
+    uint64_t key[kSortItems];
+    uint32_t val[kSortItems];
+    uint16_t rank[kSortItems];
+    const uint32_t warp_base = warp * (32 * kSortItems);
+#pragma unroll
+    for (int i = 0; i < kSortItems; i++) {
+        const uint32_t idx = warp_base + i * 32 + lane;
+        if (idx < valid) {
+            key[i] = keys_in[tile_base + idx];
+            val[i] = vals_in[tile_base + idx];
+        } else {
+            key[i] = ~0ull;
+            val[i] = 0;
+        }
+    }
+    // stable ranking inside the warp, digit by digit group
+    const unsigned lt_mask = (1u << lane) - 1u;
+#pragma unroll
+    for (int i = 0; i < kSortItems; i++) {
+        const uint32_t idx = warp_base + i * 32 + lane;
+        const bool ok = idx < valid;
+        const uint32_t d = ok ? ((uint32_t)(key[i] >> shift) & digit_mask) : (uint32_t)kRadix;
+        const unsigned peers = __match_any_sync(0xffffffffu, d);
+        const int leader = __ffs(peers) - 1;
+        uint32_t old = 0;
+        if ((int)lane == leader && ok) {
+            old = sm.warp_hist[warp][d];
+            sm.warp_hist[warp][d] = old + __popc(peers);
+        }
+        old = __shfl_sync(0xffffffffu, old, leader);
+        rank[i] = (uint16_t)(old + __popc(peers & lt_mask));
+        __syncwarp();
+    }
+    __syncthreads();
+
+    // per digit (thread d): offsets of each warp inside the digit, CTA count, CTA start, look-back
+    uint32_t cta_count = 0;
+    {
+        uint32_t run = 0;
+#pragma unroll
+        for (int w = 0; w < kSortWarps; w++) {
+            const uint32_t c = sm.warp_hist[w][tid];
+            sm.warp_hist[w][tid] = run;
+            run += c;
+        }
+        cta_count = run;
+    }
+    const uint32_t dstart = block_exclusive_scan_256(cta_count, sm.warp_tot);
+    {
+        uint64_t* mine = lookback + (size_t)p * kRadix + tid;
+        uint32_t excl = 0;
+        if (p == 0) {
+            st_word(mine, kFlagInclusive | cta_count);
+        } else {
+            st_word(mine, kFlagAggregate | cta_count);
+            bool failed = false;
+            for (int64_t q = (int64_t)p - 1; q >= 0; --q) {
+                const uint64_t* w = lookback + (size_t)q * kRadix + tid;
+                uint64_t word = 0;
+                uint32_t it = 0;
+                for (; it < kSortSpinLimit; ++it) {
+                    word = ld_word(w);
+                    if (word >> 32) break;
+                    if (it > 64) __nanosleep(100);
+                }
+                if (it == kSortSpinLimit) { failed = true; break; }
+                excl += (uint32_t)word;
+                if ((word >> 32) == 2u) break;
+            }
+            if (failed) { sm.fail = 1; atomicExch(status, 2u); }
+            st_word(mine, kFlagInclusive | (uint64_t)(excl + cta_count));
+        }
+        sm.digit_start[tid] = dstart;
+        sm.bin_offset[tid] = digit_offsets[tid] + excl - dstart;   // modulo 2^32 on purpose
+    }
+    __syncthreads();
+    if (sm.fail) return;
+
+    // scatter into CTA-sorted order in shared memory
+#pragma unroll
+    for (int i = 0; i < kSortItems; i++) {
+        const uint32_t idx = warp_base + i * 32 + lane;
+        if (idx < valid) {
+            const uint32_t d = (uint32_t)(key[i] >> shift) & digit_mask;
+            const uint32_t r = sm.digit_start[d] + sm.warp_hist[warp][d] + rank[i];
+            sm.keys[r] = key[i];
+            sm.vals[r] = val[i];
+        }
+    }
+    __syncthreads();
+    // coalesced runs out to global memory
+    for (uint32_t k = tid; k < valid; k += kSortThreads) {
+        const uint64_t kk = sm.keys[k];
+        const uint32_t d = (uint32_t)(kk >> shift) & digit_mask;
+        const uint32_t dst = sm.bin_offset[d] + k;
+        keys_out[dst] = kk;
+        vals_out[dst] = sm.vals[k];
+    }
+}
+
+}  // namespace tg
+
+extern "C" {
+
+static inline int sort_passes(int begin_bit, int end_bit) { return (end_bit - begin_bit + tg::kRadixBits - 1) / tg::kRadixBits; }
+
+size_t tg_sort_scratch_bytes(uint32_t n) {
+    const size_t parts = ((size_t)n + tg::kSortTile - 1) / tg::kSortTile;
+    return tg::kHistBytes + tg::kCtrBytes + (size_t)tg::kMaxPasses * (parts ? parts : 1) * tg::kRadix * sizeof(uint64_t);
+}
+
+int tg_sort_pairs(uint64_t* keys_a, uint64_t* keys_b, uint32_t* vals_a, uint32_t* vals_b, uint32_t n, int begin_bit,
+                  int end_bit, void* scratch, size_t scratch_bytes, uint32_t* status, int* result_in_b_host,
+                  tg_stream_t stream) {
+    TG_REQUIRE(begin_bit >= 0 && end_bit <= 64 && begin_bit < end_bit, "bit range");
+    TG_REQUIRE(n < 0x80000000u, "n must stay below 2^31");
+    const int passes = sort_passes(begin_bit, end_bit);
+    TG_REQUIRE(passes <= tg::kMaxPasses, "too many passes");
+    if (result_in_b_host) *result_in_b_host = 0;
+    if (n == 0) return TG_OK;
+    TG_REQUIRE(keys_a && keys_b && vals_a && vals_b && scratch && status, "null pointer");
+    TG_REQUIRE(((uintptr_t)scratch & 15) == 0, "scratch must be 16-byte aligned");
+    const size_t parts = ((size_t)n + tg::kSortTile - 1) / tg::kSortTile;
+    const size_t need = tg::kHistBytes + tg::kCtrBytes + (size_t)passes * parts * tg::kRadix * sizeof(uint64_t);
+    if (scratch_bytes < need) {
+        tg_host::set_error("sort scratch: need %zu bytes, got %zu", need, scratch_bytes);
+        return TG_ERR_WORKSPACE;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    uint32_t* hist = (uint32_t*)scratch;
+    uint32_t* ctr = (uint32_t*)((char*)scratch + tg::kHistBytes);   // [0..7] tickets, [8] histogram-done
+    uint64_t* lookback = (uint64_t*)((char*)scratch + tg::kHistBytes + tg::kCtrBytes);
+    TG_CUDA(cudaMemsetAsync(scratch, 0, need, s));
+
+    static thread_local int smem_set_device = -1;
+    int dev = 0;
+    TG_CUDA(cudaGetDevice(&dev));
+    if (smem_set_device != dev) {
+        TG_CUDA(cudaFuncSetAttribute(tg::onesweep_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)sizeof(tg::SortSmem)));
+        smem_set_device = dev;
+    }
+    int hist_grid = (int)((n + tg::kSortThreads * 16 - 1) / (tg::kSortThreads * 16));
+    if (hist_grid > 148 * 8) hist_grid = 148 * 8;
+    if (hist_grid < 1) hist_grid = 1;
+    tg::sort_histogram_kernel<<<hist_grid, tg::kSortThreads, 0, s>>>(keys_a, n, begin_bit, end_bit, passes, hist, ctr + 8);
+    TG_LAUNCH_CHECK("sort_histogram_kernel");
+    uint64_t* kin = keys_a; uint64_t* kout = keys_b;
+    uint32_t* vin = vals_a; uint32_t* vout = vals_b;
+    for (int p = 0; p < passes; p++) {
+        const int shift = begin_bit + p * tg::kRadixBits;
+        const int bits = (end_bit - shift < tg::kRadixBits) ? (end_bit - shift) : tg::kRadixBits;
+        tg::onesweep_pass_kernel<<<(unsigned)parts, tg::kSortThreads, sizeof(tg::SortSmem), s>>>(
+            kin, vin, kout, vout, n, shift, bits, hist + p * tg::kRadix, ctr + p, lookback + (size_t)p * parts * tg::kRadix,
+            status);
+        TG_LAUNCH_CHECK("onesweep_pass_kernel");
+        uint64_t* tk = kin; kin = kout; kout = tk;
+        uint32_t* tv = vin; vin = vout; vout = tv;
+    }
+    if (result_in_b_host) *result_in_b_host = passes & 1;
+    return TG_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,119 @@
+"""Stage-level access to the CUDA path: thin torch-tensor wrappers over the C-ABI stage entry points.
+
+Each function allocates its outputs with torch, passes raw pointers and the current stream to one
+``tg_*`` entry point of ``include/trigrad_b200.h`` and raises on a non-zero status.  Used by the
+parity tests (one stage at a time against the oracle) and by the benchmark's per-stage timing.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _native as N
+
+
+def ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def cuda(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.cuda()
+
+
+def scene_tensors(sc):
+    return (cuda(sc.vertices), cuda(sc.indices), cuda(sc.colors), cuda(sc.opacities))
+
+
+def num_tiles(sc):
+    return ((sc.width + sc.tile_width - 1) // sc.tile_width) * ((sc.height + sc.tile_height - 1) // sc.tile_height)
+
+
+def preprocess(sc, tensors=None):
+    v, i, c, o = tensors or scene_tensors(sc)
+    T = i.shape[0]
+    counts = torch.empty(T, dtype=torch.int32, device="cuda")
+    rects = torch.empty((T, 4), dtype=torch.int32, device="cuda")
+    geo = torch.empty((T, N.GEO_WORDS), dtype=torch.float32, device="cuda")
+    attr = torch.empty((T, N.ATTR_WORDS), dtype=torch.float32, device="cuda")
+    N.check("preprocess", N.lib().tg_preprocess(ptr(v), ptr(i), ptr(c), ptr(o), T, sc.width, sc.height, sc.tile_width,
+                                                sc.tile_height, ptr(counts), ptr(rects), ptr(geo), ptr(attr), stream()))
+    return counts, rects, geo, attr
+
+
+def scan(counts: torch.Tensor):
+    n = counts.numel()
+    out = torch.empty(n + 1, dtype=torch.int32, device="cuda")
+    nb = N.lib().tg_scan_scratch_bytes(n)
+    scratch = torch.empty(nb + 16, dtype=torch.uint8, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    N.check("scan", N.lib().tg_scan(ptr(counts), ptr(out), n, ptr(scratch), nb, ptr(status), stream()))
+    assert int(status[0]) == 0
+    return out
+
+
+def emit_keys(sc, tri_offsets, K, tensors=None):
+    v, i, c, o = tensors or scene_tensors(sc)
+    keys = torch.empty(max(K, 1), dtype=torch.int64, device="cuda")
+    ids = torch.empty(max(K, 1), dtype=torch.int32, device="cuda")
+    N.check("emit", N.lib().tg_emit_keys(ptr(v), ptr(i), i.shape[0], sc.width, sc.height, sc.tile_width, sc.tile_height,
+                                         ptr(tri_offsets), ptr(keys), ptr(ids), K, stream()))
+    return keys[:K], ids[:K]
+
+
+def sort_pairs(keys: torch.Tensor, vals: torch.Tensor, begin_bit=0, end_bit=64):
+    n = keys.numel()
+    ka = keys.clone()
+    va = vals.clone()
+    kb = torch.empty_like(ka)
+    vb = torch.empty_like(va)
+    nb = N.lib().tg_sort_scratch_bytes(n)
+    scratch = torch.empty(nb + 16, dtype=torch.uint8, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    in_b = C.c_int(0)
+    N.check("sort", N.lib().tg_sort_pairs(ptr(ka), ptr(kb), ptr(va), ptr(vb), n, begin_bit, end_bit, ptr(scratch), nb,
+                                          ptr(status), C.byref(in_b), stream()))
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    return (kb, vb) if in_b.value else (ka, va)
+
+
+def tile_ranges(sorted_keys: torch.Tensor, tiles: int):
+    off = torch.empty(tiles + 1, dtype=torch.int32, device="cuda")
+    N.check("ranges", N.lib().tg_tile_ranges(ptr(sorted_keys), sorted_keys.numel(), tiles, ptr(off), stream()))
+    return off
+
+
+def blend_forward(sc, geo, attr, ids, offsets, thr=1 / 256, per_pixel_sort=True, max_layers=32):
+    H, W = sc.height, sc.width
+    image = torch.empty((H, W, 4), dtype=torch.float32, device="cuda")
+    depth = torch.empty((H, W), dtype=torch.float32, device="cuda")
+    fw = torch.empty((H, W), dtype=torch.float32, device="cuda")
+    ends = torch.empty((H, W), dtype=torch.int32, device="cuda")
+    N.check("blend_forward", N.lib().tg_blend_forward(ptr(geo), ptr(attr), ptr(ids), ptr(offsets), W, H, sc.tile_width,
+                                                      sc.tile_height, float(thr), int(per_pixel_sort), int(max_layers),
+                                                      ptr(image), ptr(depth), ptr(fw), ptr(ends), stream()))
+    return image, depth, fw, ends
+
+
+def blend_backward(sc, geo, attr, ids, offsets, fwd, gimage, gdepth, per_pixel_sort=True, max_layers=32):
+    image, depth, fw, ends = fwd
+    V = sc.num_vertices
+    gV = torch.empty((V, 4), dtype=torch.float32, device="cuda")
+    gC = torch.empty((V, 3), dtype=torch.float32, device="cuda")
+    gO = torch.empty((V,), dtype=torch.float32, device="cuda")
+    N.check("blend_backward", N.lib().tg_blend_backward(
+        ptr(geo), ptr(attr), ptr(ids), ptr(offsets), V, sc.width, sc.height, sc.tile_width, sc.tile_height,
+        int(per_pixel_sort), int(max_layers), ptr(gimage), ptr(gdepth), ptr(image), ptr(depth), ptr(fw), ptr(ends),
+        ptr(gV), ptr(gC), ptr(gO), 0, stream()))
+    return gV, gC, gO
+
+

@@ -1,0 +1,90 @@
+"""Batches of views over several GPUs: contiguous view sharding and one all-reduce of the gradients.
+
+The reference renders one view per call and has no multi-device code.  Views are independent, so a
+batch shards with no data-path exchange: rank r of N renders views [r*B/N, (r+1)*B/N) of the same
+mesh (every GPU holds the whole mesh).  World-space gradients of positions, colours and opacities
+accumulate over the rank's views into ONE contiguous fp32 buffer laid out as
+``[gP (V,3) | gC (V,3) | gO (V)]``; a single ``all_reduce(SUM)`` over NCCL then runs in place on that
+buffer.  The projection world -> NDC and its VJP are plain torch ops outside the hot path, as in the
+reference viewer (``viewer.py:274-280``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Sequence
+
+import torch
+
+from .wrapper import render as _render
+
+
+def shard_views(n_views: int, rank: int, world_size: int) -> range:
+    """Contiguous block of views of `rank`; blocks differ by at most one view and cover [0, n_views)."""
+    if not (0 <= rank < world_size):
+        raise ValueError("rank out of range")
+    base, extra = divmod(n_views, world_size)
+    start = rank * base + min(rank, extra)
+    return range(start, start + base + (1 if rank < extra else 0))
+
+
+def project(points: torch.Tensor, pv: torch.Tensor) -> torch.Tensor:
+    """World points (V,3) -> render vertices (x/w', y/w', z/w', 1/w'), differentiable."""
+    ones = torch.ones((points.shape[0], 1), dtype=points.dtype, device=points.device)
+    clip = torch.cat([points, ones], dim=1) @ pv.T
+    inv_w = 1.0 / clip[:, 3:4]
+    return torch.cat([clip[:, :3] * inv_w, inv_w], dim=1).contiguous()
+
+
+@dataclass
+class GradBuffer:
+    """One contiguous fp32 buffer holding the three gradients, with typed views into it."""
+
+    flat: torch.Tensor
+    points: torch.Tensor     # (V,3) view
+    colors: torch.Tensor     # (V,3) view
+    opacities: torch.Tensor  # (V,)  view
+
+    @staticmethod
+    def allocate(num_vertices: int, device) -> "GradBuffer":
+        V = num_vertices
+        flat = torch.zeros(7 * V, dtype=torch.float32, device=device)
+        return GradBuffer(flat, flat[:3 * V].view(V, 3), flat[3 * V:6 * V].view(V, 3), flat[6 * V:])
+
+    def zero_(self) -> None:
+        self.flat.zero_()
+
+
+def render_views_l2(points: torch.Tensor, indices: torch.Tensor, colors: torch.Tensor, opacities: torch.Tensor,
+                    pvs: torch.Tensor, targets: Sequence[torch.Tensor] | torch.Tensor, view_ids: Sequence[int],
+                    width: int, height: int, grads: GradBuffer, render_fn: Callable = _render,
+                    **render_kwargs) -> torch.Tensor:
+    """Render the given views, accumulate d(sum of per-view MSE)/d(points, colors, opacities) into `grads`.
+
+    Returns the summed loss (a 0-d tensor on the device).  `targets[k]` is the (H,W,4) target of view k.
+    """
+    total = torch.zeros((), dtype=torch.float32, device=points.device)
+    for k in view_ids:
+        p = points.detach().requires_grad_(True)
+        c = colors.detach().requires_grad_(True)
+        o = opacities.detach().requires_grad_(True)
+        verts = project(p, pvs[k])
+        out = render_fn(verts, indices, c, o, width, height, **render_kwargs)
+        image = out[0]
+        loss = torch.mean((image - targets[k]) ** 2)
+        gp, gc, go = torch.autograd.grad(loss, (p, c, o))
+        grads.points += gp
+        grads.colors += gc
+        grads.opacities += go
+        total = total + loss.detach()
+    return total
+
+
+def allreduce_gradients(grads: GradBuffer, loss: torch.Tensor | None = None, group=None) -> None:
+    """Sum the gradient buffer (and optionally the loss) over all ranks, in place, with one collective each."""
+    import torch.distributed as dist
+
+    if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return
+    dist.all_reduce(grads.flat, op=dist.ReduceOp.SUM, group=group)
+    if loss is not None:
+        dist.all_reduce(loss, op=dist.ReduceOp.SUM, group=group)

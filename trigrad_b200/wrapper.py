@@ -1,0 +1,204 @@
+"""Python entry point: ``render`` and the ``Renderer`` autograd function.
+
+Mirrors the public interface of the reference (``src/trigrad/wrapper.py:12-158``): same argument
+order and defaults, same exceptions (``TypeError`` for device / dtype, ``ValueError`` for shapes and
+oversized tiles), same outputs ``(image, depthmap[, timings])`` and the same twelve gradient slots.
+The work itself is done by hand-written sm_100a kernels behind the C ABI of
+``include/trigrad_b200.h``; this module only allocates tensors and passes raw pointers and the
+current CUDA stream.  There is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Tuple
+
+import torch
+from torch.autograd import Function
+
+from . import _native as N
+from .util import create_check
+
+precision = torch.float32
+check_tensor = create_check("cuda", precision)
+
+TIMING_KEYS = ("init", "per_tile_lists", "sorting", "bary_transforms", "rasterization")
+
+
+class _DeviceState:
+    """Per (device, stream) reusable buffers: workspace, pinned read-back slots, K estimate."""
+
+    SLOTS = 256
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.workspace = torch.empty(0, dtype=torch.uint8, device=device)
+        self.info = torch.zeros((self.SLOTS, 2), dtype=torch.int32).pin_memory()
+        self.slot = 0
+        self.k_estimate = 0
+
+    def next_slot(self) -> int:
+        s = self.slot
+        self.slot = (self.slot + 1) % self.SLOTS
+        stale = int(self.info[s, 1])
+        if stale:
+            self.info[s, 1] = 0
+            raise RuntimeError(f"trigrad_b200: an earlier render reported device error word {stale} "
+                               "(a bounded wait ran out inside a kernel)")
+        return s
+
+    def ensure_workspace(self, nbytes: int) -> torch.Tensor:
+        if self.workspace.numel() < nbytes:
+            self.workspace = torch.empty(int(nbytes * 1.25) + 256, dtype=torch.uint8, device=self.device)
+        return self.workspace
+
+
+_states: dict = {}
+
+
+def _state(device: torch.device) -> _DeviceState:
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    st = _states.get(key)
+    if st is None:
+        st = _states[key] = _DeviceState(device)
+    return st
+
+
+def _ptr(t: torch.Tensor | None):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def forward_native(vertices, indices, colors, opacities, width, height, tile_width, tile_height,
+                   early_stopping_threshold, record_timing, per_pixel_sort, max_layers):
+    """Run the whole forward path.  Returns the public outputs and the state saved for backward."""
+    lib = N.lib()
+    device = vertices.device
+    T = indices.shape[0]
+    tiles = ((width + tile_width - 1) // tile_width) * ((height + tile_height - 1) // tile_height)
+    with torch.cuda.device(device):
+        st = _state(device)
+        stream = torch.cuda.current_stream(device).cuda_stream
+        f32 = dict(dtype=torch.float32, device=device)
+        image = torch.empty((height, width, 4), **f32)
+        depthmap = torch.empty((height, width), **f32)
+        final_weights = torch.empty((height, width), **f32)
+        ends = torch.empty((height, width), dtype=torch.int32, device=device)
+        tri_geo = torch.empty((T, N.GEO_WORDS), **f32)
+        tri_attr = torch.empty((T, N.ATTR_WORDS), **f32)
+        offsets = torch.empty(tiles + 1, dtype=torch.int32, device=device)
+        stage_ms = (C.c_float * 5)() if record_timing else None
+        cap = max(int(st.k_estimate * 1.25) + 1024, 2 * T + 1024)
+        while True:
+            sorted_ids = torch.empty(cap, dtype=torch.int32, device=device)
+            ws = st.ensure_workspace(lib.tg_forward_workspace_bytes(T, tiles, cap))
+            base = (ws.data_ptr() + 255) // 256 * 256
+            slot = st.next_slot()
+            info = st.info[slot]
+            status = lib.tg_render_forward(
+                _ptr(vertices), _ptr(indices), _ptr(colors), _ptr(opacities), T, width, height, tile_width,
+                tile_height, float(early_stopping_threshold), int(bool(per_pixel_sort)), int(max_layers),
+                _ptr(image), _ptr(depthmap), _ptr(final_weights), _ptr(ends), _ptr(tri_geo), _ptr(tri_attr),
+                _ptr(sorted_ids), cap, _ptr(offsets), C.c_void_p(base), ws.numel() - (base - ws.data_ptr()),
+                C.c_void_p(info.data_ptr()), stage_ms, C.c_void_p(stream))
+            K = int(info[0])
+            if status == N.TG_ERR_CAPACITY:
+                cap = int(K * 1.25) + 1024
+                continue
+            N.check("render_forward", status)
+            break
+        st.k_estimate = K
+        timings = None
+        if record_timing:
+            timings = {k: float(stage_ms[i]) / 1000.0 for i, k in enumerate(TIMING_KEYS)}
+    return image, depthmap, final_weights, sorted_ids[:K], offsets, tri_geo, tri_attr, ends, timings
+
+
+def backward_native(grad_image, grad_depthmap, saved, V, width, height, tile_width, tile_height, per_pixel_sort,
+                    max_layers, out=None):
+    """Gradient kernel.  ``out`` = (gV, gC, gO) to accumulate into, or None to get fresh tensors."""
+    lib = N.lib()
+    sorted_ids, offsets, tri_geo, tri_attr, image, depthmap, final_weights, ends = saved
+    device = image.device
+    with torch.cuda.device(device):
+        stream = torch.cuda.current_stream(device).cuda_stream
+        grad_image = grad_image.contiguous()
+        grad_depthmap = grad_depthmap.contiguous()
+        accumulate = out is not None
+        if out is None:
+            f32 = dict(dtype=torch.float32, device=device)
+            out = (torch.empty((V, 4), **f32), torch.empty((V, 3), **f32), torch.empty((V,), **f32))
+        gV, gC, gO = out
+        status = lib.tg_blend_backward(
+            _ptr(tri_geo), _ptr(tri_attr), _ptr(sorted_ids), _ptr(offsets), V, width, height, tile_width, tile_height,
+            int(bool(per_pixel_sort)), int(max_layers), _ptr(grad_image), _ptr(grad_depthmap), _ptr(image),
+            _ptr(depthmap), _ptr(final_weights), _ptr(ends), _ptr(gV), _ptr(gC), _ptr(gO), int(accumulate),
+            C.c_void_p(stream))
+        N.check("blend_backward", status)
+    return gV, gC, gO
+
+
+class Renderer(Function):
+    @staticmethod
+    def forward(ctx, vertices: torch.Tensor, indices: torch.Tensor, colors: torch.Tensor, opacities: torch.Tensor,
+                width: int = 500, height: int = 500, tile_width: int = 16, tile_height: int = 16,
+                early_stopping_threshold: float = 1 / 256, record_timing: bool = False, per_pixel_sort: bool = True,
+                max_layers: int = 32):
+        n, _ = vertices.shape
+        check_tensor(vertices, "vertices", (n, 4))
+        check_tensor(colors, "colors", (n, 3))
+        check_tensor(opacities, "opacities", (n,))
+        ctx.num_vertices = n
+        n, _ = indices.shape
+        check_tensor(indices, "indices", (n, 3), torch.int32)
+        if max_layers <= 0:
+            max_layers = n + 1
+        ctx.width, ctx.height = width, height
+        ctx.tile_width, ctx.tile_height = tile_width, tile_height
+        ctx.per_pixel_sort, ctx.max_layers = per_pixel_sort, max_layers
+        if n < 1:
+            ctx.skipped = True
+            image = torch.zeros((height, width, 4), dtype=colors.dtype, device=colors.device)
+            image[..., 3] = 1.0
+            depthmap = torch.full((height, width), float("inf"), dtype=colors.dtype, device=colors.device)
+            timings = None
+            ctx.save_for_backward(vertices, colors, opacities)
+        else:
+            ctx.skipped = False
+            (image, depthmap, final_weights, sorted_ids, offsets, tri_geo, tri_attr, ends, timings) = forward_native(
+                vertices.contiguous(), indices.contiguous(), colors.contiguous(), opacities.contiguous(), width, height,
+                tile_width, tile_height, early_stopping_threshold, record_timing, per_pixel_sort, max_layers)
+            ctx.save_for_backward(sorted_ids, offsets, tri_geo, tri_attr, image, depthmap, final_weights, ends)
+        if record_timing:
+            return image, depthmap, timings
+        return image, depthmap
+
+    @staticmethod
+    def backward(ctx, grad_image: torch.Tensor, grad_depthmap: torch.Tensor, grad_timings=None):
+        if ctx.skipped:
+            vertices, colors, opacities = ctx.saved_tensors
+            gV, gC, gO = torch.zeros_like(vertices), torch.zeros_like(colors), torch.zeros_like(opacities)
+        else:
+            gV, gC, gO = backward_native(grad_image, grad_depthmap, ctx.saved_tensors, ctx.num_vertices, ctx.width,
+                                         ctx.height, ctx.tile_width, ctx.tile_height, ctx.per_pixel_sort, ctx.max_layers)
+        return (gV, None, gC, gO, None, None, None, None, None, None, None, None)
+
+
+def render(vertices: torch.Tensor, indices: torch.Tensor, colors: torch.Tensor, opacities: torch.Tensor,
+           width: int = 500, height: int = 500, tile_width: int = 16, tile_height: int = 16,
+           early_stopping_threshold: float = 1 / 256, record_timing: bool = False, per_pixel_sort: bool = True,
+           max_layers: int = 32) -> Tuple[torch.Tensor, torch.Tensor] | Tuple[torch.Tensor, torch.Tensor, dict]:
+    """Render semi-transparent triangles (same contract as the reference ``trigrad.render``).
+
+        vertices  : (N, 4) float32 CUDA tensor (x'/w', y'/w', z'/w', 1/w') in [-1, 1] clip space
+        indices   : (M, 3) int32 triangle vertex indices
+        colors    : (N, 3) vertex colours, opacities : (N,) vertex opacities
+        per_pixel_sort : sort fragments per pixel (default) or blend in per-tile order
+        max_layers     : maximum number of layers composited per pixel, <= 0 for no limit
+
+    Returns ``image`` (height, width, 4) whose alpha channel holds the remaining translucency,
+    ``depthmap`` (height, width) and, with ``record_timing``, a dict of stage times in seconds.
+    """
+    if tile_width * tile_height > 1024:
+        raise ValueError("tile_width * tile_height must be <= 1024")
+    return Renderer.apply(vertices, indices, colors, opacities, width, height, tile_width, tile_height,
+                          early_stopping_threshold, record_timing, per_pixel_sort, max_layers)
