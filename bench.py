@@ -1,0 +1,429 @@
+"""Benchmark of the differentiable-rasterisation hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg3|cfg2|cfg1|cfg5]
+
+Workload (default): BASELINE config 3 - 200 000 seeded random triangles, 1920x1080, 16x16 tiles, fp32,
+forward + backward of mean((image - target)^2).  One step = one view through the whole path.  With
+N > 1 GPUs (one process per GPU under torchrun) every rank renders its own view of the same mesh per
+step and the vertex/colour/opacity gradients are summed with one NCCL all-reduce (weak scaling).
+
+Prints ONE JSON line (rank 0).  `value` is fwd+bwd Mpix/s with inputs resident in HBM, timed with CUDA
+events per step with an L2 flush between steps; `e2e` is the same through ``trigrad_b200.render`` from
+pinned HOST buffers (inputs copied in, loss and gradients copied out, every step); `roofline` describes
+the dominant kernel; `cpu_baseline` is the CPU oracle timed on this machine's host cores.
+
+`--impl reference` times the reference algorithm on the host cores (the reference has no CPU path and
+only exists as CUDA; the CPU restatement under ``oracle/`` stands in), with all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "fwd+bwd Mpix/s"
+UNIT = "Mpix/s"
+
+
+# ----------------------------------------------------------------------------------------------------
+def make_scene(name: str):
+    from trigrad_b200 import scenes as S
+
+    if name == "cfg3":
+        return S.config3_random200k(), "cfg3_random200k_1920x1080"
+    if name == "cfg2":
+        return S.config2_random10k(), "cfg2_random10k_512x512"
+    if name == "cfg1":
+        return S.config1_icosphere(), "cfg1_icosphere1280_256x256"
+    if name == "cfg5":
+        return S.config5_overlap(), "cfg5_overlap2M_3840x2160"
+    raise SystemExit(f"unknown workload {name}")
+
+
+def view_vertices(vertices: np.ndarray, k: int) -> np.ndarray:
+    """View k of the scene: the NDC xy plane rotated by 0.01*k rad (view 0 is the scene itself)."""
+    if k == 0:
+        return vertices
+    a = 0.01 * k
+    out = vertices.copy()
+    out[:, 0] = np.cos(a) * vertices[:, 0] - np.sin(a) * vertices[:, 1]
+    out[:, 1] = np.sin(a) * vertices[:, 0] + np.cos(a) * vertices[:, 1]
+    return out
+
+
+def tile_bits(tiles: int) -> int:
+    b = 0
+    while (1 << b) < tiles:
+        b += 1
+    return b
+
+
+# ----------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) while a region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        self.period = period_s
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                for n, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+
+    def summary(self) -> dict:
+        med = statistics.median(self.samples) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------------------------------------------
+def cpu_step_factory(scene, tile_stride: int = 1):
+    """The CPU oracle's fwd+bwd step on prepared float32 arrays (lists, matrices, forward, loss, backward)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle as O
+
+    v, i, c, o = scene.vertices, scene.indices, scene.colors, scene.opacities
+    target = scene.target()
+    W, H, tw, th = scene.width, scene.height, scene.tile_width, scene.tile_height
+    scale = np.float32(2.0 / (W * H * 4))
+    gd = np.zeros((H, W), np.float32)
+
+    def step():
+        f = O.forward(v, i, c, o, W, H, tw, th, tile_stride=tile_stride)
+        gi = (f.image - target) * scale
+        return O.backward(v, i, c, o, W, H, f, gi, gd, tw, th, tile_stride=tile_stride)
+
+    return step, O
+
+
+def time_cpu(scene, steps: int, warmup: int, budget_s: float):
+    """Times `steps` CPU steps after `warmup`; picks a tile stride so that the run fits the budget."""
+    step, O = cpu_step_factory(scene, 1)
+    t0 = time.perf_counter()
+    step()
+    first = time.perf_counter() - t0
+    stride = 1
+    total_steps = steps + max(warmup - 1, 0)
+    if first * total_steps > budget_s:
+        stride = int(np.ceil(first * total_steps / budget_s))
+        step, O = cpu_step_factory(scene, stride)
+    for _ in range(max(warmup - 1, 0) if stride == 1 else warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    px = O.sampled_pixels(scene, stride)
+    sample = (f"{steps} full steps" if stride == 1 else
+              f"{steps} steps compositing every {stride}th tile ({px} of {scene.width * scene.height} pixels); "
+              "binning and sorting in full")
+    return px / dt / 1e6, dt, O.num_threads(), sample
+
+
+def run_reference_arm(args, rank: int, world: int) -> None:
+    if rank != 0:
+        return
+    scene, wname = make_scene(args.workload)
+    value, dt, cores, sample = time_cpu(scene, args.steps, args.warmup, budget_s=150.0)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wname, "triangles": scene.num_triangles, "width": scene.width, "height": scene.height,
+                   "tile": [scene.tile_width, scene.tile_height], "per_pixel_sort": True, "max_layers": 32,
+                   "note": "reference algorithm on host cores: the reference ships no CPU path, its CPU restatement (oracle/) is timed"},
+        "triangles_per_s": scene.num_triangles / dt * (1.0 if "full" in sample else float("nan")),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line, allow_nan=True).replace("NaN", "null"))
+
+
+# ----------------------------------------------------------------------------------------------------
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg3")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import trigrad_b200
+    from trigrad_b200 import _native as N
+    from trigrad_b200 import stages as St
+    from trigrad_b200 import views as Vw
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    scene, wname = make_scene(args.workload)
+    W, H = scene.width, scene.height
+    T, V = scene.num_triangles, scene.num_vertices
+    verts_np = view_vertices(scene.vertices, rank)
+    target_np = scene.target()
+
+    v = torch.from_numpy(verts_np).to(dev)
+    i = torch.from_numpy(scene.indices).to(dev)
+    c = torch.from_numpy(scene.colors).to(dev)
+    o = torch.from_numpy(scene.opacities).to(dev)
+    target = torch.from_numpy(target_np).to(dev)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)    # > L2 (126 MB)
+    grads = Vw.GradBuffer.allocate(V, dev)
+    gV4 = torch.zeros((V, 4), dtype=torch.float32, device=dev)
+
+    lib = N.lib()
+    launches_before = 0
+
+    def step():
+        """fwd + bwd of one view through the public API, gradients into the all-reduce buffer."""
+        vv = v.detach().requires_grad_(True)
+        cc = c.detach().requires_grad_(True)
+        oo = o.detach().requires_grad_(True)
+        image, _ = trigrad_b200.render(vv, i, cc, oo, W, H, scene.tile_width, scene.tile_height)
+        loss = torch.mean((image - target) ** 2)
+        gv, gc, go = torch.autograd.grad(loss, (vv, cc, oo))
+        if world > 1:
+            grads.points.copy_(gv[:, [0, 1, 3]])
+            grads.colors.copy_(gc)
+            grads.opacities.copy_(go)
+            Vw.allreduce_gradients(grads)
+        return loss, gv, gc, go
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+
+    # ---- timed region: K steps, CUDA events per step, L2 flushed between steps -----------------------
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    n_launch0 = lib.tg_launch_count()
+    with ClockSampler(local_rank) as clk:
+        barrier()
+        t_wall0 = time.perf_counter()
+        for k in range(args.steps):
+            flush.zero_()
+            starts[k].record()
+            step()
+            stops[k].record()
+        barrier()
+        t_wall = time.perf_counter() - t_wall0
+    n_launch = lib.tg_launch_count() - n_launch0
+    step_ms = [s.elapsed_time(e) for s, e in zip(starts, stops)]
+    total_ms = torch.tensor([sum(step_ms)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
+    ms_per_step = float(total_ms.item()) / args.steps
+    value = W * H * world / (ms_per_step * 1e-3) / 1e6
+
+    # ---- end to end from host buffers through the public API -----------------------------------------
+    hv = torch.from_numpy(verts_np).pin_memory()
+    hi = torch.from_numpy(scene.indices).pin_memory()
+    hc = torch.from_numpy(scene.colors).pin_memory()
+    ho = torch.from_numpy(scene.opacities).pin_memory()
+    ht = torch.from_numpy(target_np).pin_memory()
+    out_gv = torch.empty((V, 4), dtype=torch.float32).pin_memory()
+    out_gc = torch.empty((V, 3), dtype=torch.float32).pin_memory()
+    out_go = torch.empty((V,), dtype=torch.float32).pin_memory()
+    out_loss = torch.empty((), dtype=torch.float32).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in (hv, hi, hc, ho, ht))
+    d2h = sum(t.numel() * t.element_size() for t in (out_gv, out_gc, out_go, out_loss))
+
+    def e2e_step():
+        nonlocal v, i, c, o, target
+        v = hv.to(dev, non_blocking=True)
+        i = hi.to(dev, non_blocking=True)
+        c = hc.to(dev, non_blocking=True)
+        o = ho.to(dev, non_blocking=True)
+        target = ht.to(dev, non_blocking=True)
+        loss, gv, gc, go = step()
+        if world > 1:
+            gv, gc, go = grads.points, grads.colors, grads.opacities
+            out_gv[:, :3].copy_(gv, non_blocking=True)
+        else:
+            out_gv.copy_(gv, non_blocking=True)
+        out_gc.copy_(gc, non_blocking=True)
+        out_go.copy_(go, non_blocking=True)
+        out_loss.copy_(loss, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_steps = max(5, min(args.steps, 50))
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_dt = torch.tensor([(time.perf_counter() - t0) / e2e_steps], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_dt, op=dist.ReduceOp.MAX)
+    e2e_value = W * H * world / float(e2e_dt.item()) / 1e6
+
+    # ---- per-kernel timing for the roofline (stage entry points, CUDA events, L2 flushed) ------------
+    stages = measure_stages(torch, St, scene, verts_np, flush, reps=max(5, min(20, args.steps)))
+    peaks = load_peaks()
+    dominant = max((s for s in stages.values() if isinstance(s, dict) and s.get("kernel")), key=lambda s: s["ms"])
+    roofline = {
+        "kernel": dominant["kernel"], "bound": "hbm", "achieved": dominant["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+        "frac": dominant["gbs"] / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+        "algorithmic_bytes_per_launch": dominant["bytes"], "ms_per_launch": dominant["ms"],
+    }
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": wname, "triangles": T, "vertices": V, "width": W, "height": H,
+                   "tile": [scene.tile_width, scene.tile_height], "per_pixel_sort": True, "max_layers": 32,
+                   "views_per_gpu_per_step": 1, "K_pairs": stages["_K"], "l2": "256 MB buffer rewritten between timed steps",
+                   "exchange": "none" if world == 1 else "one NCCL all_reduce of 7V fp32 gradients per step"},
+        "triangles_per_s": T * world / (ms_per_step * 1e-3),
+        "wall_s_timed_region": t_wall,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": float(e2e_dt.item()) * 1e3},
+        "gpu_launches": int(n_launch),
+        "clocks": clk.summary(),
+        "roofline": roofline,
+        "stages": {k: s for k, s in stages.items() if not k.startswith("_")},
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cv, cdt, cores, sample = time_cpu(scene, steps=3, warmup=1, budget_s=25.0)
+        line["cpu_baseline"] = {"value": cv, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
+                                "ms_per_step": cdt * 1e3}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def load_peaks() -> dict:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": float(d["hbm_gbs"]), "source": "measured (MEASURED_PEAKS.json)"}
+    return {"hbm_gbs": 6650.0, "source": "fallback"}
+
+
+def measure_stages(torch, St, scene, verts_np, flush, reps: int) -> dict:
+    """Average device time of each kernel of the path on the bench workload and its algorithmic bytes."""
+    import copy
+
+    sc = copy.copy(scene)
+    sc.vertices = verts_np
+    tens = St.scene_tensors(sc)
+    T, V, W, H = sc.num_triangles, sc.num_vertices, sc.width, sc.height
+    tiles = St.num_tiles(sc)
+    end_bit = 32 + tile_bits(tiles)
+    P = (end_bit + 7) // 8
+
+    def timed(fn, setup=None):
+        ms = []
+        out = None
+        for _ in range(reps):
+            if setup is not None:
+                setup()
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            out = fn()
+            b.record()
+            b.synchronize()
+            ms.append(a.elapsed_time(b))
+        return statistics.median(ms), out
+
+    res = {}
+    ms, (counts, rects, geo, attr) = timed(lambda: St.preprocess(sc, tens))
+    res["preprocess"] = {"kernel": "preprocess_kernel", "ms": ms, "bytes": 16 * T + 16 * V}
+    ms, tri_off = timed(lambda: St.scan(counts))
+    res["scan"] = {"kernel": "scan_kernel", "ms": ms, "bytes": 8 * T}
+    K = int(tri_off[-1])
+    ms, (keys, ids) = timed(lambda: St.emit_keys(sc, tri_off, K, tens))
+    res["emit_keys"] = {"kernel": "emit_keys_kernel", "ms": ms, "bytes": 16 * T + 16 * V + 12 * K}
+    sb = St.SortBuffers(K)
+    ms, (skeys, sids) = timed(lambda: sb.sort(0, end_bit), setup=lambda: sb.load(keys, ids))
+    res["sort"] = {"kernel": "sort_histogram_kernel + onesweep_pass_kernel x P", "ms": ms, "bytes": (8 + 24 * P) * K,
+                   "passes": P}
+    ms, offsets = timed(lambda: St.tile_ranges(skeys, tiles))
+    res["tile_ranges"] = {"kernel": "tile_ranges_kernel", "ms": ms, "bytes": 8 * K + 8 * tiles}
+    ms, fwd = timed(lambda: St.blend_forward(sc, geo, attr, sids, offsets))
+    res["blend_forward"] = {"kernel": "blend_forward_kernel", "ms": ms, "bytes": 100 * K + 28 * W * H}
+    gi = torch.randn((H, W, 4), device="cuda")
+    gd = torch.zeros((H, W), device="cuda")
+    ms, _ = timed(lambda: St.blend_backward(sc, geo, attr, sids, offsets, fwd, gi, gd))
+    res["blend_backward"] = {"kernel": "blend_backward_kernel", "ms": ms, "bytes": 100 * K + 48 * W * H + 32 * V}
+    for s in res.values():
+        s["gbs"] = s["bytes"] / (s["ms"] * 1e-3) / 1e9 if s["ms"] > 0 else 0.0
+    res["_K"] = K
+    return res
+
+
+if __name__ == "__main__":
+    main()

@@ -46,6 +46,9 @@ int tg_version(void);
 const char* tg_status_string(int status);
 /* Text of the last failure on the calling thread ("" if none). */
 const char* tg_last_error(void);
+/* Number of kernels this library has launched in this process so far (diagnostic counter; the
+ * reference has no counterpart). */
+unsigned long long tg_launch_count(void);
 
 /* ---- stage 1: per-triangle preprocess ------------------------------------------------------
  * Tile rectangle of the bounding box, tile-overlap count, barycentric matrix and packed records.

@@ -188,7 +188,7 @@ class ForwardOut:
 
 
 def forward(verts, idx, colors, opac, W, H, tw=16, th=16, thr=1 / 256, per_pixel_sort=True, max_layers=32,
-            lists: Lists | None = None) -> ForwardOut:
+            lists: Lists | None = None, tile_stride: int = 1) -> ForwardOut:
     dt = np.asarray(verts).dtype
     verts = np.ascontiguousarray(verts, dtype=dt)
     idx = np.ascontiguousarray(idx, dtype=np.int32)
@@ -207,12 +207,12 @@ def forward(verts, idx, colors, opac, W, H, tw=16, th=16, thr=1 / 256, per_pixel
     ids = np.ascontiguousarray(lists.ids)
     _fn("tgo_forward", dt)(_p(verts), _p(idx), _p(colors), _p(opac), T, W, H, tw, th, _p(ids), _p(lists.offsets), _p(M),
                            _sc(dt, thr), int(bool(per_pixel_sort)), int(max_layers), _p(image), _p(depth), _p(fw),
-                           _p(ends))
+                           _p(ends), int(tile_stride))
     return ForwardOut(image, depth, fw, ends, lists, M)
 
 
 def backward(verts, idx, colors, opac, W, H, fwd: ForwardOut, grad_image, grad_depth, tw=16, th=16,
-             per_pixel_sort=True, max_layers=32):
+             per_pixel_sort=True, max_layers=32, tile_stride: int = 1):
     dt = np.asarray(verts).dtype
     verts = np.ascontiguousarray(verts, dtype=dt)
     idx = np.ascontiguousarray(idx, dtype=np.int32)
@@ -229,12 +229,25 @@ def backward(verts, idx, colors, opac, W, H, fwd: ForwardOut, grad_image, grad_d
     ids = np.ascontiguousarray(fwd.lists.ids)
     _fn("tgo_backward", dt)(_p(verts), _p(idx), _p(colors), _p(opac), T, W, H, tw, th, _p(ids), _p(fwd.lists.offsets),
                             _p(fwd.M), int(bool(per_pixel_sort)), int(max_layers), _p(gi), _p(gd), _p(fwd.image),
-                            _p(fwd.depthmap), _p(fwd.final_weights), _p(fwd.ends), _p(gV), _p(gC), _p(gO))
+                            _p(fwd.depthmap), _p(fwd.final_weights), _p(fwd.ends), _p(gV), _p(gC), _p(gO), int(tile_stride))
     return gV, gC, gO
 
 
-def render_l2(scene, dtype=np.float32, per_pixel_sort=True, max_layers=32, thr=1 / 256, target=None):
-    """fwd + bwd of ``mean((image - target)**2)`` on a ``trigrad_b200.scenes.Scene``; the timed CPU step."""
+def sampled_pixels(scene, tile_stride: int) -> int:
+    """Number of image pixels inside the tiles a ``tile_stride`` sample renders."""
+    tx = (scene.width + scene.tile_width - 1) // scene.tile_width
+    ty = (scene.height + scene.tile_height - 1) // scene.tile_height
+    t = np.arange(0, tx * ty, max(1, tile_stride))
+    w = np.minimum(scene.tile_width, scene.width - (t % tx) * scene.tile_width)
+    h = np.minimum(scene.tile_height, scene.height - (t // tx) * scene.tile_height)
+    return int((w * h).sum())
+
+
+def render_l2(scene, dtype=np.float32, per_pixel_sort=True, max_layers=32, thr=1 / 256, target=None, tile_stride=1):
+    """fwd + bwd of ``mean((image - target)**2)`` on a ``trigrad_b200.scenes.Scene``; the timed CPU step.
+
+    ``tile_stride`` > 1 composites only every tile_stride-th tile (binning and sorting still run in
+    full): a bounded sample of the workload for timing; outputs outside the sampled tiles stay zero."""
     v = scene.vertices.astype(dtype)
     c = scene.colors.astype(dtype)
     o = scene.opacities.astype(dtype)
@@ -242,11 +255,11 @@ def render_l2(scene, dtype=np.float32, per_pixel_sort=True, max_layers=32, thr=1
         target = scene.target()
     target = target.astype(dtype)
     f = forward(v, scene.indices, c, o, scene.width, scene.height, scene.tile_width, scene.tile_height, thr,
-                per_pixel_sort, max_layers)
+                per_pixel_sort, max_layers, tile_stride=tile_stride)
     diff = f.image - target
     loss = float(np.mean(diff.astype(np.float64) ** 2))
     gi = (diff * dtype(2.0 / diff.size)).astype(dtype)
     gd = np.zeros((scene.height, scene.width), dtype)
     g = backward(v, scene.indices, c, o, scene.width, scene.height, f, gi, gd, scene.tile_width, scene.tile_height,
-                 per_pixel_sort, max_layers)
+                 per_pixel_sort, max_layers, tile_stride=tile_stride)
     return loss, f, g

@@ -21,6 +21,7 @@ SIGNATURES = {
     "tg_version": (_i, []),
     "tg_status_string": (C.c_char_p, [_i]),
     "tg_last_error": (C.c_char_p, []),
+    "tg_launch_count": (C.c_ulonglong, []),
     "tg_preprocess": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "tg_scan_scratch_bytes": (_sz, [_i]),
     "tg_scan": (_i, [_vp, _vp, _i, _vp, _sz, _vp, _vp]),

@@ -2,6 +2,8 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <atomic>
+
 #include "tg_common.cuh"
 
 namespace tg {
@@ -341,11 +343,15 @@ int cuda_fail(cudaError_t e, const char* what) {
     return TG_ERR_CUDA;
 }
 const char* last_error() { return g_err; }
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 }  // namespace tg_host
 
 extern "C" {
 
 int tg_version(void) { return 1; }
+
+unsigned long long tg_launch_count(void) { return tg_host::g_launches.load(std::memory_order_relaxed); }
 
 const char* tg_last_error(void) { return tg_host::last_error(); }
 

@@ -115,6 +115,7 @@ __device__ __forceinline__ unsigned lane_id() { return threadIdx.x & 31u; }
 namespace tg_host {
 void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
+void count_launch();
 }  // namespace tg_host
 
 #define TG_CUDA(call)                                                   \
@@ -124,6 +125,7 @@ int cuda_fail(cudaError_t e, const char* what);
     } while (0)
 #define TG_LAUNCH_CHECK(name)                                           \
     do {                                                                \
+        tg_host::count_launch();                                        \
         cudaError_t e__ = cudaGetLastError();                           \
         if (e__ != cudaSuccess) return tg_host::cuda_fail(e__, name);   \
     } while (0)

@@ -69,6 +69,32 @@ def emit_keys(sc, tri_offsets, K, tensors=None):
     return keys[:K], ids[:K]
 
 
+class SortBuffers:
+    """Ping-pong buffers and scratch for ``tg_sort_pairs`` on n pairs."""
+
+    def __init__(self, n: int):
+        self.n = n
+        self.ka = torch.empty(max(n, 1), dtype=torch.int64, device="cuda")
+        self.kb = torch.empty_like(self.ka)
+        self.va = torch.empty(max(n, 1), dtype=torch.int32, device="cuda")
+        self.vb = torch.empty_like(self.va)
+        self.nbytes = N.lib().tg_sort_scratch_bytes(n)
+        self.scratch = torch.empty(self.nbytes + 16, dtype=torch.uint8, device="cuda")
+        self.status = torch.zeros(4, dtype=torch.int32, device="cuda")
+
+    def load(self, keys: torch.Tensor, vals: torch.Tensor) -> None:
+        self.ka[:self.n].copy_(keys)
+        self.va[:self.n].copy_(vals)
+
+    def sort(self, begin_bit: int, end_bit: int):
+        """Asynchronous: launches the sort on the current stream; returns (keys, vals) views of the result."""
+        in_b = C.c_int(0)
+        N.check("sort", N.lib().tg_sort_pairs(ptr(self.ka), ptr(self.kb), ptr(self.va), ptr(self.vb), self.n, begin_bit,
+                                              end_bit, ptr(self.scratch), self.nbytes, ptr(self.status), C.byref(in_b),
+                                              stream()))
+        return (self.kb[:self.n], self.vb[:self.n]) if in_b.value else (self.ka[:self.n], self.va[:self.n])
+
+
 def sort_pairs(keys: torch.Tensor, vals: torch.Tensor, begin_bit=0, end_bit=64):
     n = keys.numel()
     ka = keys.clone()
