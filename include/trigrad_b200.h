@@ -71,6 +71,18 @@ size_t tg_scan_scratch_bytes(int n);
 int tg_scan(const uint32_t* in, uint32_t* out, int n, void* scratch, size_t scratch_bytes, uint32_t* status,
             tg_stream_t stream);
 
+/* Same scan for callers that cannot allocate device memory where they need it (a host with a fixed
+ * memory plan, a loop that must stay clear of the allocator, a plugin inside an application that
+ * owns all allocations).  This entry point has no counterpart in the reference.  The look-back words
+ * live in a 64 KB array inside the library image, so every GPU that loads the library holds that
+ * much until the process exits, and n is limited to 2^24 elements per call (larger n is refused with
+ * TG_ERR_CAPACITY; use tg_scan).  It calls no allocating routine.  The first call on each device
+ * looks up the array's device address, so make that call before starting any stream capture.  All
+ * calls on a device share the array, which is cleared at the start of each call: two calls whose
+ * kernels may overlap on the GPU (different streams) race, so order them on one stream.
+ */
+int tg_scan_static(const uint32_t* in, uint32_t* out, int n, uint32_t* status, tg_stream_t stream);
+
 /* ---- stage 3: key emission --------------------------------------------------------------------
  * For triangle t and every tile (tx outer, ty inner) of its rectangle, entry e = tri_offsets[t] + n:
  *   keys[e] = (uint64)tile << 32 | ord(depth key),  ids[e] = t

@@ -25,6 +25,7 @@ SIGNATURES = {
     "tg_preprocess": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "tg_scan_scratch_bytes": (_sz, [_i]),
     "tg_scan": (_i, [_vp, _vp, _i, _vp, _sz, _vp, _vp]),
+    "tg_scan_static": (_i, [_vp, _vp, _i, _vp, _vp]),
     "tg_emit_keys": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _u32, _vp]),
     "tg_sort_scratch_bytes": (_sz, [_u32]),
     "tg_sort_pairs": (_i, [_vp, _vp, _vp, _vp, _u32, _i, _i, _vp, _sz, _vp, C.POINTER(_i), _vp]),

@@ -420,6 +420,62 @@ int tg_scan(const uint32_t* in, uint32_t* out, int n, void* scratch, size_t scra
     return TG_OK;
 }
 
+// ---- prefix scan without caller-provided scratch ------------------------------------------------
+// Some hosts of this library may not allocate device memory at the point where they need a scan:
+// code running under a fixed memory budget that was carved up at start-up, a real-time loop that
+// must not touch the allocator, or a plugin whose embedding application owns every allocation.
+// For them the partition words of the look-back scan live in a fixed array inside the library
+// image.  Every GPU that loads the library holds these 64 KB + 256 B until the process exits.
+constexpr int kStaticScanMaxN = 1 << 24;                                         // elements per call
+constexpr int kStaticScanMaxParts = (kStaticScanMaxN + tg::kScanTile - 1) / tg::kScanTile;
+constexpr size_t kStaticScanBytes = 256 + 8 * ((size_t)kStaticScanMaxParts + 1);  // ticket (padded) + words
+static __device__ __align__(256) unsigned char g_static_scan_scratch[kStaticScanBytes];
+
+// In host code the array's name is only a handle; the device address has to be asked for, once per
+// device, with that device current.
+static int static_scan_scratch_address(void** out) {
+    constexpr int kMaxDevices = 64;
+    static std::atomic<void*> cache[kMaxDevices];
+    int dev = 0;
+    TG_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) {
+        tg_host::set_error("device index %d outside the supported range", dev);
+        return TG_ERR_BAD_ARG;
+    }
+    void* p = cache[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
+        TG_CUDA(cudaGetSymbolAddress(&p, g_static_scan_scratch));
+        cache[dev].store(p, std::memory_order_release);
+    }
+    *out = p;
+    return TG_OK;
+}
+
+int tg_scan_static(const uint32_t* in, uint32_t* out, int n, uint32_t* status, tg_stream_t stream) {
+    TG_REQUIRE(n >= 0, "n < 0");
+    TG_REQUIRE(out && status, "null pointer");
+    if (n > kStaticScanMaxN) {
+        tg_host::set_error("tg_scan_static handles at most %d elements per call (got %d); use tg_scan with caller scratch",
+                           kStaticScanMaxN, n);
+        return TG_ERR_CAPACITY;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    if (n == 0) {
+        TG_CUDA(cudaMemsetAsync(out, 0, sizeof(uint32_t), s));
+        return TG_OK;
+    }
+    TG_REQUIRE(in != nullptr, "null pointer");
+    void* scratch = nullptr;
+    if (int st = static_scan_scratch_address(&scratch)) return st;
+    const int parts = (n + tg::kScanTile - 1) / tg::kScanTile;
+    // the array keeps what the previous call left: clear the ticket and the words this call uses
+    TG_CUDA(cudaMemsetAsync(scratch, 0, 256 + 8 * ((size_t)parts + 1), s));
+    tg::scan_kernel<<<parts, tg::kScanThreads, 0, s>>>(in, out, n, parts, (uint32_t*)scratch,
+                                                      (uint64_t*)((char*)scratch + 256), status);
+    TG_LAUNCH_CHECK("scan_kernel (static scratch)");
+    return TG_OK;
+}
+
 int tg_emit_keys(const float* vertices, const int32_t* indices, int T, int W, int H, int tw, int th,
                  const uint32_t* tri_offsets, uint64_t* keys, uint32_t* ids, uint32_t capacity, tg_stream_t stream) {
     if (int s = check_dims(T, W, H, tw, th)) return s;
