@@ -113,25 +113,35 @@ int tg_tile_ranges(const uint64_t* sorted_keys, uint32_t n, int tiles, int32_t* 
 /* ---- stage 6: forward compositing ---------------------------------------------------------------
  * One CTA per tile, one thread per pixel.  Replaces render_forward_kernel
  * (src/trigrad/render.cu:540-619 with :338-453).  max_layers must be >= 1.
+ * selection: NULL, or [tg_selection_planes()][H*W] int32 that receives, per pixel, the triangle ids of
+ * the fragments it blended, in blending order (plane k = k-th fragment, k < ends).  The backward pass
+ * then needs no second search of the tile lists.  tg_selection_planes() is max_layers in per-pixel
+ * mode with max_layers <= 32 and 0 otherwise (then `selection` is ignored).
  */
+int tg_selection_planes(int per_pixel_sort, int max_layers);
 int tg_blend_forward(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids, const int32_t* offsets,
                      int W, int H, int tile_w, int tile_h, float early_stopping_threshold, int per_pixel_sort,
                      int max_layers, float* image, float* depthmap, float* final_weights, int32_t* ends,
-                     tg_stream_t stream);
+                     int32_t* selection, tg_stream_t stream);
 
 /* ---- stage 7: backward ------------------------------------------------------------------------
  * Replaces render_backward_kernel (src/trigrad/render.cu:621-695 with :455-538).
- * grad_vertices [V,4] (z column stays 0), grad_colors [V,3], grad_opacities [V].
- * accumulate == 0: the three gradient buffers are zeroed first; != 0: added to.
+ * grad_vertices [V,4] (z column stays 0; 16-byte aligned), grad_colors [V,3], grad_opacities [V].
+ * accumulate == 0: the three gradient buffers are overwritten; != 0: added to.
+ * selection: what tg_blend_forward wrote, or NULL (the lists are then searched again).
+ * scratch: tg_backward_scratch_bytes(V) bytes, 16-byte aligned (packed per-vertex accumulator).
  */
+size_t tg_backward_scratch_bytes(int V);
 int tg_blend_backward(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids, const int32_t* offsets,
                       int V, int W, int H, int tile_w, int tile_h, int per_pixel_sort, int max_layers,
                       const float* grad_image, const float* grad_depthmap, const float* image, const float* depthmap,
-                      const float* final_weights, const int32_t* ends, float* grad_vertices, float* grad_colors,
-                      float* grad_opacities, int accumulate, tg_stream_t stream);
+                      const float* final_weights, const int32_t* ends, const int32_t* selection, float* grad_vertices,
+                      float* grad_colors, float* grad_opacities, int accumulate, void* scratch, size_t scratch_bytes,
+                      tg_stream_t stream);
 
 /* ---- whole forward path -------------------------------------------------------------------------
  * Replaces render_forward (src/trigrad/render.cu:713-763).  Runs stages 1-6 on `stream`.
+ *   selection    as for tg_blend_forward (may be NULL)
  *   sorted_ids   [list_capacity] int32   out, first K entries valid
  *   offsets      [tiles+1] int32         out
  *   info_host    uint32[2] in (preferably pinned) host memory.  [0] receives K; the call
@@ -147,8 +157,8 @@ size_t tg_forward_workspace_bytes(int T, int tiles, uint32_t list_capacity);
 int tg_render_forward(const float* vertices, const int32_t* indices, const float* colors, const float* opacities,
                       int T, int W, int H, int tile_w, int tile_h, float early_stopping_threshold,
                       int per_pixel_sort, int max_layers, float* image, float* depthmap, float* final_weights,
-                      int32_t* ends, float* tri_geo, float* tri_attr, int32_t* sorted_ids, uint32_t list_capacity,
-                      int32_t* offsets, void* workspace, size_t workspace_bytes, uint32_t* info_host,
+                      int32_t* ends, int32_t* selection, float* tri_geo, float* tri_attr, int32_t* sorted_ids,
+                      uint32_t list_capacity, int32_t* offsets, void* workspace, size_t workspace_bytes, uint32_t* info_host,
                       float* stage_ms_host, tg_stream_t stream);
 
 #ifdef __cplusplus

@@ -44,10 +44,10 @@ def test_status_strings():
 def test_argument_errors_are_reported_before_any_device_work():
     lib = N.lib()
     # tile larger than 1024 threads
-    st = lib.tg_blend_forward(None, None, None, None, 64, 64, 64, 64, 0.0, 1, 32, None, None, None, None, None)
+    st = lib.tg_blend_forward(None, None, None, None, 64, 64, 64, 64, 0.0, 1, 32, None, None, None, None, None, None)
     assert st == N.TG_ERR_BAD_ARG and b"1024" in lib.tg_last_error()
     # max_layers must be >= 1 at the ABI (the Python layer maps <= 0 to T + 1)
-    st = lib.tg_blend_forward(None, None, None, None, 64, 64, 16, 16, 0.0, 1, 0, None, None, None, None, None)
+    st = lib.tg_blend_forward(None, None, None, None, 64, 64, 16, 16, 0.0, 1, 0, None, None, None, None, None, None)
     assert st == N.TG_ERR_BAD_ARG
     # bad bit range for the sort
     st = lib.tg_sort_pairs(None, None, None, None, 10, 8, 8, None, 0, None, None, None)

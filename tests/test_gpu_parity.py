@@ -141,7 +141,7 @@ def test_forward_and_backward_vs_oracle(pipeline, mode):
     T = sc.num_triangles
     ml = mode["max_layers"] if mode["max_layers"] > 0 else T + 1
     fwd = Hh.blend_forward(sc, p["geo"], p["attr"], p["sids"], p["offsets"], mode["thr"], mode["per_pixel_sort"], ml)
-    image, depth, fw, ends = [t.cpu().numpy() for t in fwd]
+    image, depth, fw, ends = [t.cpu().numpy() for t in fwd[:4]]
     of = O.forward(sc.vertices, sc.indices, sc.colors, sc.opacities, sc.width, sc.height, sc.tile_width,
                    sc.tile_height, mode["thr"], mode["per_pixel_sort"], ml)
     assert np.array_equal(ends, of.ends), "fragment selection differs"
@@ -161,12 +161,18 @@ def test_forward_and_backward_vs_oracle(pipeline, mode):
                           mode["per_pixel_sort"], ml)
     og = O.backward(sc.vertices, sc.indices, sc.colors, sc.opacities, sc.width, sc.height, of, gi, gd, sc.tile_width,
                     sc.tile_height, mode["per_pixel_sort"], ml)
-    for name, a, b in zip(("vertices", "colors", "opacities"), g, og):
+    checks = [("saved selection" if fwd[4] is not None else "list search", g)]
+    if fwd[4] is not None:
+        # the same gradients without the ids saved by the forward pass (lists searched again)
+        checks.append(("list search", Hh.blend_backward(sc, p["geo"], p["attr"], p["sids"], p["offsets"], fwd[:4] + (None,),
+                                                        Hh.cuda(gi), Hh.cuda(gd), mode["per_pixel_sort"], ml)))
+    for path, gg in checks:
+      for name, a, b in zip(("vertices", "colors", "opacities"), gg, og):
         a = a.cpu().numpy()
         assert np.all(a[:, 2] == 0) if name == "vertices" else True
         err, err_max = Hh.rel_l2(a, b), Hh.rel_err(a, b)
-        assert err <= GRAD_TOL, f"grad_{name}: relative L2 error {err:.3e}"
-        assert err_max <= GRAD_TOL_MAX, f"grad_{name}: worst element {err_max:.3e}"
+        assert err <= GRAD_TOL, f"grad_{name} ({path}): relative L2 error {err:.3e}"
+        assert err_max <= GRAD_TOL_MAX, f"grad_{name} ({path}): worst element {err_max:.3e}"
 
 
 def test_large_sort_random_keys():

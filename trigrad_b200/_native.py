@@ -30,11 +30,13 @@ SIGNATURES = {
     "tg_sort_scratch_bytes": (_sz, [_u32]),
     "tg_sort_pairs": (_i, [_vp, _vp, _vp, _vp, _u32, _i, _i, _vp, _sz, _vp, C.POINTER(_i), _vp]),
     "tg_tile_ranges": (_i, [_vp, _u32, _i, _vp, _vp]),
-    "tg_blend_forward": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "tg_selection_planes": (_i, [_i, _i]),
+    "tg_blend_forward": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "tg_backward_scratch_bytes": (_sz, [_i]),
     "tg_blend_backward": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
-                               _vp, _i, _vp]),
+                               _vp, _vp, _i, _vp, _sz, _vp]),
     "tg_forward_workspace_bytes": (_sz, [_i, _i, _u32]),
-    "tg_render_forward": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+    "tg_render_forward": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                _u32, _vp, _vp, _sz, _vp, _vp, _vp]),
 }
 

@@ -70,8 +70,8 @@ size_t tg_forward_workspace_bytes(int T, int tiles, uint32_t list_capacity) {
 
 int tg_render_forward(const float* vertices, const int32_t* indices, const float* colors, const float* opacities, int T,
                       int W, int H, int tw, int th, float thr, int per_pixel_sort, int max_layers, float* image,
-                      float* depthmap, float* final_weights, int32_t* ends, float* tri_geo, float* tri_attr,
-                      int32_t* sorted_ids, uint32_t list_capacity, int32_t* offsets, void* workspace,
+                      float* depthmap, float* final_weights, int32_t* ends, int32_t* selection, float* tri_geo,
+                      float* tri_attr, int32_t* sorted_ids, uint32_t list_capacity, int32_t* offsets, void* workspace,
                       size_t workspace_bytes, uint32_t* info_host, float* stage_ms_host, tg_stream_t stream) {
     TG_REQUIRE(T >= 0 && W > 0 && H > 0 && tw > 0 && th > 0, "sizes");
     TG_REQUIRE(tw * th <= 1024, "tile_width * tile_height must be <= 1024");
@@ -126,7 +126,7 @@ int tg_render_forward(const float* vertices, const int32_t* indices, const float
     if (st) return st;
     timer.mark();                                                    // [4] start of "rasterization"
     st = tg_blend_forward(tri_geo, tri_attr, sorted_ids, offsets, W, H, tw, th, thr, per_pixel_sort, max_layers, image,
-                          depthmap, final_weights, ends, stream);
+                          depthmap, final_weights, ends, selection, stream);
     if (st) return st;
     timer.mark();                                                    // [5] end
     // device error word: valid on the host once the stream has been synchronised

@@ -1,15 +1,24 @@
 // Stages 6 and 7: per-tile forward compositing and the backward (gradient) kernel.
 //
-// One CTA per tile, one thread per pixel (tile_w*tile_h threads rounded up to a warp multiple).
-// The tile's depth-sorted triangle list is streamed through shared memory in coalesced,
-// vectorised chunks of packed 64-byte geometry records; every pixel tests every staged record.
+// One CTA per tile, one thread per pixel (tile_w*tile_h threads rounded up to a warp multiple); a
+// warp owns an 8x4 pixel block when the tile size allows it.  The tile's depth-sorted triangle
+// list is streamed through shared memory in coalesced, vectorised chunks of packed 64-byte
+// geometry records.  For every staged chunk each warp first rejects, with one lane per record, the
+// records that cannot cover any of its 32 pixels (exact corner test on the same rounded
+// arithmetic as the per-pixel test); only the survivors are tested per pixel.
 //
 // per_pixel_sort = true  (the reference default): each pixel keeps the nearest <= 32 covering
-//     fragments by (interpolated depth, list position), then blends them in that order; further
-//     batches of 32 follow while transmittance > threshold and blended < max_layers.
+//     fragments by (interpolated depth, list position) and blends them in that order; further
+//     batches of 32 follow while transmittance > threshold and blended < max_layers.  The ids of
+//     the blended fragments can be saved per pixel so that the backward pass need not search again.
 // per_pixel_sort = false: fragments are blended in list order; a pixel stops once its
-//     transmittance is <= threshold, a whole warp skips records once all its lanes stopped and the
-//     CTA leaves the list as soon as every warp voted "done".
+//     transmittance is <= threshold, a warp skips chunks once all its lanes stopped (ballot) and
+//     the CTA leaves the list as soon as every warp voted "done".
+//
+// Backward: per pixel the recorded fragments are walked last to first with the reference's
+// recurrences; every lane adds its contribution with 128-bit vector reductions
+// (red.global.add.v4.f32) into a packed per-vertex buffer (x, y, w, opacity | r, g, b, -) that a
+// small kernel then unpacks into grad_vertices / grad_colors / grad_opacities.
 #include "tg_common.cuh"
 
 namespace tg {
@@ -31,17 +40,11 @@ struct PixelAcc {
     int blended = 0;
 };
 
-struct Frag {
-    Bary bary;
-    float w0, w1, w2;
-};
-
 // Load the geometry record of triangle `id` straight from global memory (L1/L2 resident).
-__device__ __forceinline__ void load_geo(const float4* geo, int id, float* m, float* z, float* w) {
+__device__ __forceinline__ void load_geo(const float4* geo, int id, float* m, float* w) {
     const float4 g0 = __ldg(geo + 4 * (size_t)id), g1 = __ldg(geo + 4 * (size_t)id + 1);
     const float4 g2 = __ldg(geo + 4 * (size_t)id + 2), g3 = __ldg(geo + 4 * (size_t)id + 3);
     m[0] = g0.x; m[1] = g0.y; m[2] = g0.z; m[3] = g0.w; m[4] = g1.x; m[5] = g1.y; m[6] = g1.z; m[7] = g1.w; m[8] = g2.x;
-    z[0] = g2.y; z[1] = g2.z; z[2] = g2.w;
     w[0] = g3.x; w[1] = g3.y; w[2] = g3.z;
 }
 
@@ -84,17 +87,30 @@ __device__ __forceinline__ void blend_one(const Bary& b, const float* w, const A
     acc.blended++;
 }
 
+// NDC extent (pixel centres) of the active pixels of one warp.
+struct WarpRect { float x0, x1, y0, y1; };
+
 struct TileCtx {
     int tile, start, end, ix, iy;
     bool active;
     float px, py;
+    WarpRect rect;
 };
 
 __device__ __forceinline__ TileCtx tile_context(const BlendParams& P) {
     TileCtx c;
     c.tile = blockIdx.x;
     const int tx = c.tile % P.tiles_x, ty = c.tile / P.tiles_x;
-    const int lx = threadIdx.x % P.tw, ly = threadIdx.x / P.tw;
+    int lx, ly;
+    if ((P.tw & 7) == 0 && (P.th & 3) == 0) {
+        // a warp owns an 8x4 block of the tile: compact footprint, fewer records survive its cull
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, bpr = P.tw >> 3;
+        lx = (warp % bpr) * 8 + (lane & 7);
+        ly = (warp / bpr) * 4 + (lane >> 3);
+    } else {
+        lx = threadIdx.x % P.tw;
+        ly = threadIdx.x / P.tw;
+    }
     c.ix = tx * P.tw + lx;
     c.iy = ty * P.th + ly;
     c.active = (int)threadIdx.x < P.tw * P.th && c.ix < P.W && c.iy < P.H;
@@ -102,7 +118,31 @@ __device__ __forceinline__ TileCtx tile_context(const BlendParams& P) {
     c.end = P.offsets[c.tile + 1];
     c.px = pixel_coord(c.ix, P.W);
     c.py = pixel_coord(c.iy, P.H);
+    float x0 = c.active ? c.px : INFINITY, x1 = c.active ? c.px : -INFINITY;
+    float y0 = c.active ? c.py : INFINITY, y1 = c.active ? c.py : -INFINITY;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        x0 = fminf(x0, __shfl_xor_sync(0xffffffffu, x0, d));
+        x1 = fmaxf(x1, __shfl_xor_sync(0xffffffffu, x1, d));
+        y0 = fminf(y0, __shfl_xor_sync(0xffffffffu, y0, d));
+        y1 = fmaxf(y1, __shfl_xor_sync(0xffffffffu, y1, d));
+    }
+    c.rect = {x0, x1, y0, y1};
     return c;
+}
+
+// Can the triangle with matrix m cover any pixel centre inside R?  Each barycentric is evaluated at
+// the corner of R that maximises it, with the very operations of the per-pixel test; correctly
+// rounded FMAs are monotone, so a pixel inside R can never get a larger value than the corner.
+__device__ __forceinline__ bool rect_may_cover(const float* m, const WarpRect& R) {
+#pragma unroll
+    for (int k = 0; k < 3; k++) {
+        const float cx = (m[3 * k] >= 0.f) ? R.x1 : R.x0;
+        const float cy = (m[3 * k + 1] >= 0.f) ? R.y1 : R.y0;
+        const float v = fma_(m[3 * k], cx, fma_(m[3 * k + 1], cy, m[3 * k + 2]));
+        if (v < kEffZero) return false;
+    }
+    return true;
 }
 
 // Stage `n` records of the list starting at `first` into shared memory (ids + geometry).
@@ -115,19 +155,33 @@ __device__ __forceinline__ void stage_chunk(const BlendParams& P, int first, int
     }
 }
 
+// Bit mask (64 records) of the staged records that may cover a pixel of this warp.
+__device__ __forceinline__ unsigned long long warp_cull(const float4* s_geo, int n, const WarpRect& R) {
+    const int lane = lane_id();
+    const bool k0 = lane < n && rect_may_cover(reinterpret_cast<const float*>(s_geo + 4 * lane), R);
+    const bool k1 = lane + 32 < n && rect_may_cover(reinterpret_cast<const float*>(s_geo + 4 * (lane + 32)), R);
+    const unsigned m0 = __ballot_sync(0xffffffffu, k0), m1 = __ballot_sync(0xffffffffu, k1);
+    return (unsigned long long)m0 | ((unsigned long long)m1 << 32);
+}
+
 // One selection sweep over the whole tile list (select_next_k_in_tile, reference render.cu:375-415):
 // keeps the `bs` covered fragments smallest in (depth, j) among those after (lastDepth, lastJ).
 // All threads of the CTA must call it; `go` says whether this thread collects.
 __device__ __forceinline__ int select_sweep(const BlendParams& P, const TileCtx& c, bool go, int bs, float lastDepth,
                                             int lastJ, float* dl, int* jl, float4* s_geo, int* s_id) {
     int found = 0;
+    const bool warp_go = __any_sync(0xffffffffu, go);
     for (int first = c.start; first < c.end; first += kChunk) {
         const int n = min(kChunk, c.end - first);
         __syncthreads();
         stage_chunk(P, first, n, s_geo, s_id);
         __syncthreads();
-        if (!go) continue;
-        for (int r = 0; r < n; r++) {
+        if (!warp_go) continue;
+        unsigned long long mask = warp_cull(s_geo, n, c.rect);
+        while (mask) {
+            const int r = __ffsll((long long)mask) - 1;
+            mask &= mask - 1;
+            if (!go) continue;
             const float* g = reinterpret_cast<const float*>(s_geo + 4 * r);
             const Bary b = apply_bary(g, c.px, c.py);
             if (!covered(b)) continue;
@@ -163,10 +217,12 @@ __device__ __forceinline__ void store_pixel(const TileCtx& c, const BlendParams&
     image[index] = make_float4(acc.r, acc.g, acc.b, acc.alpha);
 }
 
+// sel: optional [planes][H*W] int32; plane k of a pixel receives the triangle id of its k-th blended
+// fragment (k < ends).  Only written when it is not null (per-pixel mode, max_layers <= 32).
 template <bool SORT, int MAXT>
 __global__ void __launch_bounds__(MAXT) blend_forward_kernel(BlendParams P, float4* __restrict__ image,
                                                              float* __restrict__ depthmap, float* __restrict__ final_w,
-                                                             int* __restrict__ ends) {
+                                                             int* __restrict__ ends, int* __restrict__ sel) {
     __shared__ float4 s_geo[kChunk * 4];
     __shared__ int s_id[kChunk];
     const TileCtx c = tile_context(P);
@@ -178,26 +234,29 @@ __global__ void __launch_bounds__(MAXT) blend_forward_kernel(BlendParams P, floa
         float lastDepth = -INFINITY;
         int lastJ = -1;
         bool want = c.active;
+        const size_t plane = (size_t)P.W * P.H, index = (size_t)c.iy * P.W + c.ix;
         while (true) {
             const bool go = want && acc.alpha > P.thr && acc.blended < P.max_layers;
             if (!__syncthreads_or(go)) break;
             const int bs = min(kBatchLayers, P.max_layers - acc.blended);
             const int found = select_sweep(P, c, go, bs, lastDepth, lastJ, dl, jl, s_geo, s_id);
             if (go) {
-                if (found == 0) want = false;
-                else {
-                    const int n = min(found, P.max_layers - acc.blended);
-                    for (int i = 0; i < n; i++) {
-                        const int id = P.ids[jl[i]];
-                        float m[9], z[3], w[3];
-                        load_geo(P.geo, id, m, z, w);
-                        const Bary b = apply_bary(m, c.px, c.py);
-                        const AttrRec a = load_attr<false>(P.attr, id);
-                        blend_one(b, w, a, acc);
-                    }
+                const int n = min(found, P.max_layers - acc.blended);
+                for (int i = 0; i < n; i++) {
+                    const int id = P.ids[jl[i]];
+                    float m[9], w[3];
+                    load_geo(P.geo, id, m, w);
+                    const Bary b = apply_bary(m, c.px, c.py);
+                    const AttrRec a = load_attr<false>(P.attr, id);
+                    if (sel) sel[(size_t)acc.blended * plane + index] = id;
+                    blend_one(b, w, a, acc);
+                }
+                if (n > 0) {
                     lastDepth = dl[n - 1];
                     lastJ = jl[n - 1];
                 }
+                // fewer than a full batch found: the sweep saw every remaining fragment, nothing is left
+                if (found < bs) want = false;
             }
         }
     } else {
@@ -209,8 +268,12 @@ __global__ void __launch_bounds__(MAXT) blend_forward_kernel(BlendParams P, floa
             __syncthreads();
             // a warp whose lanes have all stopped skips the chunk
             if (!__all_sync(0xffffffffu, done)) {
-                for (int r = 0; r < n && !done; r++) {
-                    if (!(acc.alpha > P.thr && acc.blended < P.max_layers)) { done = true; break; }
+                unsigned long long mask = warp_cull(s_geo, n, c.rect);
+                while (mask) {
+                    const int r = __ffsll((long long)mask) - 1;
+                    mask &= mask - 1;
+                    if (done) continue;
+                    if (!(acc.alpha > P.thr && acc.blended < P.max_layers)) { done = true; continue; }
                     const float* g = reinterpret_cast<const float*>(s_geo + 4 * r);
                     const Bary b = apply_bary(g, c.px, c.py);
                     if (!covered(b)) continue;
@@ -235,101 +298,77 @@ struct PixelGrad {
     float final_alpha, final_weight, final_depth;
 };
 
-// Gradient contributions of one fragment: per vertex (x, y, w, r, g, b, o).
-struct FragGrad { float v[21]; };
-
-// Scalar interpolation VJP (reference util.h:299-317).
-__device__ __forceinline__ void interp_bwd(float g, const Bary& b, float a0, float a1, float a2, float w0, float w1,
-                                           float w2, float* gbary, float* gvals, float* gw) {
-    const float nom = b.x * w0 * a0 + b.y * w1 * a1 + b.z * w2 * a2;
-    const float den = b.x * w0 + b.y * w1 + b.z * w2;
-    if (den * den < kEffZero) {
-        gbary[0] = gbary[1] = gbary[2] = 0.f;
-        gvals[0] = gvals[1] = gvals[2] = 0.f;
-        gw[0] = gw[1] = gw[2] = 0.f;
-        return;
-    }
-    const float inv = 1.f / den, inv2 = inv * inv;
-    const float e0 = (a0 * den - nom) * inv2, e1 = (a1 * den - nom) * inv2, e2 = (a2 * den - nom) * inv2;
-    gbary[0] = g * w0 * e0; gbary[1] = g * w1 * e1; gbary[2] = g * w2 * e2;
-    gvals[0] = g * b.x * w0 * inv; gvals[1] = g * b.y * w1 * inv; gvals[2] = g * b.z * w2 * inv;
-    gw[0] = g * b.x * e0; gw[1] = g * b.y * e1; gw[2] = g * b.z * e2;
+// Packed per-vertex gradient accumulator: slot 0 = (d/dx, d/dy, d/dw, d/dopacity), slot 1 = (d/dr, d/dg, d/db, 0).
+__device__ __forceinline__ void red_add_v4(float4* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-// process_backward of the reference (render.cu:455-538).  Vertex-position gradients follow the
-// reference's expanded partial derivatives (util.h:405-455) term by term: for small triangles
-// their fp32 rounding is systematic and part of what "the same result" means.
+// process_backward of the reference (render.cu:455-538) for one fragment of one pixel; adds this
+// pixel's contribution for the triangle's three vertices into `gpack`.  The interpolation VJPs
+// (util.h:299-355) share 1/den; vertex-position gradients follow the reference's expanded partial
+// derivatives (util.h:405-455) term by term: for small triangles their fp32 cancellation is
+// systematic and part of what "the same result" means.
 __device__ __forceinline__ void backward_one(const float* w, const AttrRec& a, const Bary& b, float px, float py,
-                                             const PixelGrad& pg, BackState& st, FragGrad& out) {
-    float o = interp_rn(b, a.o[0], a.o[1], a.o[2], w[0], w[1], w[2]);
-    o = fminf(fmaxf(o, 0.f), kMaxOpacity);
-    const float cr = interp_rn(b, a.c[0], a.c[3], a.c[6], w[0], w[1], w[2]);
-    const float cg = interp_rn(b, a.c[1], a.c[4], a.c[7], w[0], w[1], w[2]);
-    const float cb = interp_rn(b, a.c[2], a.c[5], a.c[8], w[0], w[1], w[2]);
+                                             const PixelGrad& pg, BackState& st, float4* __restrict__ gpack) {
+    const float bw0 = b.x * w[0], bw1 = b.y * w[1], bw2 = b.z * w[2];
+    const float den = bw0 + bw1 + bw2;
+    const bool ok = !(den * den < kEffZero);
+    const float inv = 1.f / den;
+    const float o_raw = (bw0 * a.o[0] + bw1 * a.o[1] + bw2 * a.o[2]) * inv;
+    const float o = fminf(fmaxf(o_raw, 0.f), kMaxOpacity);
+    const float cr = (bw0 * a.c[0] + bw1 * a.c[3] + bw2 * a.c[6]) * inv;
+    const float cg = (bw0 * a.c[1] + bw1 * a.c[4] + bw2 * a.c[7]) * inv;
+    const float cb = (bw0 * a.c[2] + bw1 * a.c[5] + bw2 * a.c[8]) * inv;
     const float iw0 = 1.f / w[0], iw1 = 1.f / w[1], iw2 = 1.f / w[2];
-    const float z = interp_rn(b, iw0, iw1, iw2, 1.f, 1.f, 1.f);
-    const float om = 1.f - o, iom = 1.f / om;
+    const float denz = b.x + b.y + b.z;
+    const bool okz = !(denz * denz < kEffZero);
+    const float invz = 1.f / denz;
+    const float z = (b.x * iw0 + b.y * iw1 + b.z * iw2) * invz;
+    const float iom = 1.f / (1.f - o);
 
-    const float drgb_do = ((cr * st.alpha - st.sr) * iom * pg.gr + (cg * st.alpha - st.sg) * iom * pg.gg +
-                           (cb * st.alpha - st.sb) * iom * pg.gb) -
-                          pg.ga * pg.final_alpha * iom;
+    const float drgb_do = ((cr * st.alpha - st.sr) * pg.gr + (cg * st.alpha - st.sg) * pg.gg + (cb * st.alpha - st.sb) * pg.gb -
+                           pg.ga * pg.final_alpha) * iom;
     st.alpha = st.alpha * iom;
-    st.sr += cr * o * st.alpha;
-    st.sg += cg * o * st.alpha;
-    st.sb += cb * o * st.alpha;
+    const float ao = st.alpha * o;
+    st.sr += cr * ao;
+    st.sg += cg * ao;
+    st.sb += cb * ao;
     const float ddw_do = st.alpha - st.oa * iom;
     const float dud_do = st.alpha * z - st.zoa * iom;
-    st.oa += o * st.alpha;
-    st.zoa += z * o * st.alpha;
+    st.oa += ao;
+    st.zoa += z * ao;
     const bool has_w = !(pg.final_weight < kEffZero);
     const float inv_fw = has_w ? 1.f / pg.final_weight : 0.f;
-    const float dd_do = has_w ? (dud_do - pg.final_depth * ddw_do) * inv_fw * pg.gd : 0.f;
-    const float d_do = drgb_do + dd_do;
+    const float dd_do = (dud_do - pg.final_depth * ddw_do) * inv_fw * pg.gd;
+    const float d_do = drgb_do + (has_w ? dd_do : 0.f);
 
-    float gb_o[3], gv_o[3], gw_o[3];
-    interp_bwd(d_do, b, a.o[0], a.o[1], a.o[2], w[0], w[1], w[2], gb_o, gv_o, gw_o);
+    // upstream of the four weighted interpolations (0 where the reference's guard returns zeros)
+    const float uo = ok ? d_do * inv : 0.f;
+    const float ur = ok ? ao * pg.gr * inv : 0.f, ug = ok ? ao * pg.gg * inv : 0.f, ub = ok ? ao * pg.gb * inv : 0.f;
+    // e_k = sum over attributes of upstream * (a_k - value): d/d(b_k w_k) of the interpolated values
+    const float e0 = uo * (a.o[0] - o_raw) + ur * (a.c[0] - cr) + ug * (a.c[1] - cg) + ub * (a.c[2] - cb);
+    const float e1 = uo * (a.o[1] - o_raw) + ur * (a.c[3] - cr) + ug * (a.c[4] - cg) + ub * (a.c[5] - cb);
+    const float e2 = uo * (a.o[2] - o_raw) + ur * (a.c[6] - cr) + ug * (a.c[7] - cg) + ub * (a.c[8] - cb);
+    // depth interpolation (values 1/w, unit weights)
+    const float uz = (okz && has_w) ? ao * pg.gd * inv_fw * invz : 0.f;
+    const float z0 = uz * (iw0 - z), z1 = uz * (iw1 - z), z2 = uz * (iw2 - z);
+    const float g0 = w[0] * e0 + z0, g1 = w[1] * e1 + z1, g2 = w[2] * e2 + z2;       // d/d bary
+    // d/dw: weighted interpolations, plus (as the reference does, render.cu:530) the gradient w.r.t. the unit
+    // weights of the depth interpolation, plus the chain through the values 1/w
+    const float gw0 = b.x * e0 + b.x * z0 - uz * b.x * iw0 * iw0;
+    const float gw1 = b.y * e1 + b.y * z1 - uz * b.y * iw1 * iw1;
+    const float gw2 = b.z * e2 + b.z * z2 - uz * b.z * iw2 * iw2;
 
-    const float ao = st.alpha * o;
-    float gbary[3] = {gb_o[0], gb_o[1], gb_o[2]};
-    float gw[3] = {gw_o[0], gw_o[1], gw_o[2]};
-    float gcol[9];
-    {
-        // colour: vector VJP = three scalar VJPs sharing bary / w
-        const float dcs[3] = {ao * pg.gr, ao * pg.gg, ao * pg.gb};
-#pragma unroll
-        for (int ch = 0; ch < 3; ch++) {
-            float gb_c[3], gv_c[3], gw_c[3];
-            interp_bwd(dcs[ch], b, a.c[ch], a.c[3 + ch], a.c[6 + ch], w[0], w[1], w[2], gb_c, gv_c, gw_c);
-#pragma unroll
-            for (int k = 0; k < 3; k++) {
-                gbary[k] += gb_c[k];
-                gw[k] += gw_c[k];
-                gcol[3 * k + ch] = gv_c[k];
-            }
-        }
-    }
-    {
-        const float dd_dz = has_w ? ao * pg.gd * inv_fw : 0.f;
-        float gb_z[3], gv_z[3], gw_z[3];
-        interp_bwd(dd_dz, b, iw0, iw1, iw2, 1.f, 1.f, 1.f, gb_z, gv_z, gw_z);
-        gbary[0] += gb_z[0]; gbary[1] += gb_z[1]; gbary[2] += gb_z[2];
-        // the reference also adds the gradient w.r.t. the unit weights of this interpolation to the
-        // w gradient (render.cu:530); kept for identical results
-        gw[0] += gw_z[0] - gv_z[0] * iw0 * iw0;
-        gw[1] += gw_z[1] - gv_z[1] * iw1 * iw1;
-        gw[2] += gw_z[2] - gv_z[2] * iw2 * iw2;
-    }
     // barycentric_backward: l by cross products, then the expanded partials
     const float ax = a.xy[0], ay = a.xy[1], bx = a.xy[2], by = a.xy[3], cx = a.xy[4], cy = a.xy[5];
     float gxy[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     const float d = ax * (by - cy) + bx * (-ay + cy) + cx * (ay - by);
     if (!(fabsf(d) < kEffZero)) {
-        const float Tt = (bx - ax) * (cy - ay) - (by - ay) * (cx - ax);
-        const float lx = ((bx - px) * (cy - py) - (by - py) * (cx - px)) / Tt;
-        const float ly = ((cx - px) * (ay - py) - (cy - py) * (ax - px)) / Tt;
-        const float lz = ((ax - px) * (by - py) - (ay - py) * (bx - px)) / Tt;
+        const float iT = 1.f / ((bx - ax) * (cy - ay) - (by - ay) * (cx - ax));
+        const float lx = ((bx - px) * (cy - py) - (by - py) * (cx - px)) * iT;
+        const float ly = ((cx - px) * (ay - py) - (cy - py) * (ax - px)) * iT;
+        const float lz = ((ax - px) * (by - py) - (ay - py) * (bx - px)) * iT;
         const float id = 1.f / d;
-        const float g0 = gbary[0], g1 = gbary[1], g2 = gbary[2];
         gxy[0] = (g0 * (lx * (-by + cy)) + g1 * (-cy - ly * (by - cy) + py) + g2 * (by - lz * (by - cy) - py)) * id;
         gxy[1] = (g0 * (lx * (bx - cx)) + g1 * (cx + ly * (bx - cx) - px) + g2 * (-bx + lz * (bx - cx) + px)) * id;
         gxy[2] = (g0 * (cy + lx * (ay - cy) - py) + g1 * (ly * (ay - cy)) + g2 * (-ay + lz * (ay - cy) + py)) * id;
@@ -337,81 +376,69 @@ __device__ __forceinline__ void backward_one(const float* w, const AttrRec& a, c
         gxy[4] = (g0 * (-by - lx * (ay - by) + py) + g1 * (ay - ly * (ay - by) - py) + g2 * (lz * (-ay + by))) * id;
         gxy[5] = (g0 * (bx + lx * (ax - bx) - px) + g1 * (-ax + ly * (ax - bx) + px) + g2 * (lz * (ax - bx))) * id;
     }
-#pragma unroll
-    for (int k = 0; k < 3; k++) {
-        out.v[7 * k + 0] = gxy[2 * k + 0];
-        out.v[7 * k + 1] = gxy[2 * k + 1];
-        out.v[7 * k + 2] = gw[k];
-        out.v[7 * k + 3] = gcol[3 * k + 0];
-        out.v[7 * k + 4] = gcol[3 * k + 1];
-        out.v[7 * k + 5] = gcol[3 * k + 2];
-        out.v[7 * k + 6] = gv_o[k];
+    red_add_v4(gpack + 2 * (size_t)a.vid[0], gxy[0], gxy[1], gw0, uo * bw0);
+    red_add_v4(gpack + 2 * (size_t)a.vid[0] + 1, ur * bw0, ug * bw0, ub * bw0, 0.f);
+    red_add_v4(gpack + 2 * (size_t)a.vid[1], gxy[2], gxy[3], gw1, uo * bw1);
+    red_add_v4(gpack + 2 * (size_t)a.vid[1] + 1, ur * bw1, ug * bw1, ub * bw1, 0.f);
+    red_add_v4(gpack + 2 * (size_t)a.vid[2], gxy[4], gxy[5], gw2, uo * bw2);
+    red_add_v4(gpack + 2 * (size_t)a.vid[2] + 1, ur * bw2, ug * bw2, ub * bw2, 0.f);
+}
+
+struct BackwardIn {
+    const float4* gimage;
+    const float* gdepth;
+    const float4* image;
+    const float* depthmap;
+    const float* final_w;
+    const int* ends;
+};
+
+__device__ __forceinline__ int load_pixel_state(const TileCtx& c, const BlendParams& P, const BackwardIn& in,
+                                                PixelGrad& pg, BackState& st) {
+    pg = PixelGrad{};
+    st.alpha = 1.f;
+    if (!c.active) return 0;
+    const size_t index = (size_t)c.iy * P.W + c.ix;
+    const float4 gi = in.gimage[index];
+    pg.gr = gi.x; pg.gg = gi.y; pg.gb = gi.z; pg.ga = gi.w;
+    pg.gd = in.gdepth[index];
+    pg.final_alpha = in.image[index].w;
+    pg.final_weight = in.final_w[index];
+    pg.final_depth = in.depthmap[index];
+    st.alpha = pg.final_alpha;
+    return min(in.ends[index], P.max_layers);
+}
+
+// Default mode with the per-pixel fragment ids saved by the forward pass: no list search, no shared
+// memory, no barriers - every thread walks its own fragments last to first.
+template <int MAXT>
+__global__ void __launch_bounds__(MAXT) blend_backward_saved_kernel(BlendParams P, BackwardIn in,
+                                                                    const int* __restrict__ sel,
+                                                                    float4* __restrict__ gpack) {
+    const TileCtx c = tile_context(P);
+    PixelGrad pg;
+    BackState st;
+    const int n = load_pixel_state(c, P, in, pg, st);
+    const size_t plane = (size_t)P.W * P.H, index = (size_t)c.iy * P.W + c.ix;
+    for (int k = n - 1; k >= 0; --k) {
+        const int id = sel[(size_t)k * plane + index];
+        float m[9], w[3];
+        load_geo(P.geo, id, m, w);
+        const Bary b = apply_bary(m, c.px, c.py);
+        const AttrRec a = load_attr<true>(P.attr, id);
+        backward_one(w, a, b, c.px, c.py, pg, st, gpack);
     }
 }
 
-struct GradOut { float* gV; float* gC; float* gO; };
-
-// Warp-level reduction before atomics: lanes holding the same triangle are summed with shuffles
-// and one lane issues the 21 atomics of that triangle.
-__device__ __forceinline__ void warp_accumulate(bool has, int tri, const int* vid, const FragGrad& fg, const GradOut& G) {
-    unsigned todo = __ballot_sync(0xffffffffu, has);
-    while (todo) {
-        const int leader = __ffs(todo) - 1;
-        const int tsel = __shfl_sync(0xffffffffu, tri, leader);
-        const bool mine = has && tri == tsel;
-        const unsigned grp = __ballot_sync(0xffffffffu, mine);
-        todo &= ~grp;
-        float s[21];
-#pragma unroll
-        for (int k = 0; k < 21; k++) {
-            float x = mine ? fg.v[k] : 0.f;
-            if (grp != (1u << leader)) {
-#pragma unroll
-                for (int d = 16; d > 0; d >>= 1) x += __shfl_xor_sync(0xffffffffu, x, d);
-            }
-            s[k] = x;
-        }
-        if ((int)lane_id() == leader) {
-#pragma unroll
-            for (int k = 0; k < 3; k++) {
-                const int v = vid[k];
-                atomicAdd(G.gV + 4 * (size_t)v + 0, s[7 * k + 0]);
-                atomicAdd(G.gV + 4 * (size_t)v + 1, s[7 * k + 1]);
-                atomicAdd(G.gV + 4 * (size_t)v + 3, s[7 * k + 2]);
-                atomicAdd(G.gC + 3 * (size_t)v + 0, s[7 * k + 3]);
-                atomicAdd(G.gC + 3 * (size_t)v + 1, s[7 * k + 4]);
-                atomicAdd(G.gC + 3 * (size_t)v + 2, s[7 * k + 5]);
-                atomicAdd(G.gO + v, s[7 * k + 6]);
-            }
-        }
-    }
-}
-
+// General path (any max_layers, both modes): searches the list again as the reference does.
 template <bool SORT, int MAXT>
-__global__ void __launch_bounds__(MAXT) blend_backward_kernel(BlendParams P, const float4* __restrict__ gimage,
-                                                              const float* __restrict__ gdepth,
-                                                              const float4* __restrict__ image,
-                                                              const float* __restrict__ depthmap,
-                                                              const float* __restrict__ final_w,
-                                                              const int* __restrict__ ends, GradOut G) {
+__global__ void __launch_bounds__(MAXT) blend_backward_kernel(BlendParams P, BackwardIn in, float4* __restrict__ gpack) {
     __shared__ float4 s_geo[kChunk * 4];
     __shared__ int s_id[kChunk];
     const TileCtx c = tile_context(P);
-    PixelGrad pg = {};
+    PixelGrad pg;
     BackState st;
-    st.alpha = 1.f;
-    int limit = 0;
-    if (c.active) {
-        const size_t index = (size_t)c.iy * P.W + c.ix;
-        const float4 gi = gimage[index];
-        pg.gr = gi.x; pg.gg = gi.y; pg.gb = gi.z; pg.ga = gi.w;
-        pg.gd = gdepth[index];
-        pg.final_alpha = image[index].w;
-        pg.final_weight = final_w[index];
-        pg.final_depth = depthmap[index];
-        st.alpha = pg.final_alpha;
-        limit = min(ends[index], P.max_layers);
-    }
+    const int limit = load_pixel_state(c, P, in, pg, st);
 
     if (SORT) {
         float dl[kBatchLayers];
@@ -424,46 +451,31 @@ __global__ void __launch_bounds__(MAXT) blend_backward_kernel(BlendParams P, con
             if (!__syncthreads_or(go)) break;
             const int bs = min(kBatchLayers, remaining);
             const int found = select_sweep(P, c, go, bs, lastDepth, lastJ, dl, jl, s_geo, s_id);
-            int n = 0;
             if (go) {
-                if (found == 0) remaining = 0;
-                else n = min(found, remaining);
-            }
-            // walk the batch back to front; the warp iterates together so that lanes can be reduced
-            int nmax = n;
-#pragma unroll
-            for (int d = 16; d > 0; d >>= 1) nmax = max(nmax, __shfl_xor_sync(0xffffffffu, nmax, d));
-            for (int s = 0; s < nmax; s++) {
-                const bool has = s < n;
-                int id = -1;
-                FragGrad fg;
-                AttrRec a;
-                a.vid[0] = a.vid[1] = a.vid[2] = 0;
-                if (has) {
-                    id = P.ids[jl[n - 1 - s]];
-                    float m[9], z[3], w[3];
-                    load_geo(P.geo, id, m, z, w);
+                const int n = min(found, remaining);
+                for (int i = n - 1; i >= 0; --i) {          // reference render.cu:684-688
+                    const int id = P.ids[jl[i]];
+                    float m[9], w[3];
+                    load_geo(P.geo, id, m, w);
                     const Bary b = apply_bary(m, c.px, c.py);
-                    a = load_attr<true>(P.attr, id);
-                    backward_one(w, a, b, c.px, c.py, pg, st, fg);
+                    const AttrRec a = load_attr<true>(P.attr, id);
+                    backward_one(w, a, b, c.px, c.py, pg, st, gpack);
                 }
-                warp_accumulate(has, id, a.vid, fg, G);
-            }
-            if (n > 0) {
-                lastDepth = dl[n - 1];
-                lastJ = jl[n - 1];
-                remaining -= n;
+                if (n > 0) {
+                    lastDepth = dl[n - 1];
+                    lastJ = jl[n - 1];
+                    remaining -= n;
+                } else {
+                    remaining = 0;
+                }
             }
         }
     } else {
         // reference render.cu:659-666: the first `limit` list entries, front to back
-        int lim_max = limit;
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) lim_max = max(lim_max, __shfl_xor_sync(0xffffffffu, lim_max, d));
         __shared__ int s_lim;
         if (threadIdx.x == 0) s_lim = 0;
         __syncthreads();
-        if (lane_id() == 0) atomicMax(&s_lim, lim_max);
+        if (limit > 0) atomicMax(&s_lim, limit);
         __syncthreads();
         const int cta_lim = min(s_lim, c.end - c.start);
         for (int first = 0; first < cta_lim; first += kChunk) {
@@ -471,27 +483,40 @@ __global__ void __launch_bounds__(MAXT) blend_backward_kernel(BlendParams P, con
             __syncthreads();
             stage_chunk(P, c.start + first, n, s_geo, s_id);
             __syncthreads();
-            const int warp_n = min(n, lim_max - first);
-            for (int r = 0; r < warp_n; r++) {
+            if (!__any_sync(0xffffffffu, first < limit)) continue;
+            unsigned long long mask = warp_cull(s_geo, n, c.rect);
+            while (mask) {
+                const int r = __ffsll((long long)mask) - 1;
+                mask &= mask - 1;
+                if (first + r >= limit) continue;
                 const float* g = reinterpret_cast<const float*>(s_geo + 4 * r);
-                bool has = (first + r) < limit;
-                Bary b = {0.f, 0.f, 0.f};
-                if (has) {
-                    b = apply_bary(g, c.px, c.py);
-                    has = covered(b);
-                }
-                const int id = s_id[r];
-                FragGrad fg;
-                AttrRec a;
-                a.vid[0] = a.vid[1] = a.vid[2] = 0;
-                if (__any_sync(0xffffffffu, has)) {
-                    a = load_attr<true>(P.attr, id);
-                    if (has) backward_one(g + 12, a, b, c.px, c.py, pg, st, fg);
-                    warp_accumulate(has, id, a.vid, fg, G);
-                }
+                const Bary b = apply_bary(g, c.px, c.py);
+                if (!covered(b)) continue;
+                const AttrRec a = load_attr<true>(P.attr, s_id[r]);
+                backward_one(g + 12, a, b, c.px, c.py, pg, st, gpack);
             }
         }
     }
+}
+
+// Packed accumulator -> the three gradient tensors of the reference (render.cu:789-791).
+__global__ void __launch_bounds__(256) unpack_gradients_kernel(const float4* __restrict__ gpack, int V,
+                                                               float4* __restrict__ gV, float* __restrict__ gC,
+                                                               float* __restrict__ gO, int accumulate) {
+    const int v = blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= V) return;
+    const float4 a = gpack[2 * (size_t)v], b = gpack[2 * (size_t)v + 1];
+    float4 ov = make_float4(a.x, a.y, 0.f, a.z);
+    float c0 = b.x, c1 = b.y, c2 = b.z, o = a.w;
+    if (accumulate) {
+        const float4 old = gV[v];
+        ov.x += old.x; ov.y += old.y; ov.z = old.z; ov.w += old.w;
+        c0 += gC[3 * (size_t)v]; c1 += gC[3 * (size_t)v + 1]; c2 += gC[3 * (size_t)v + 2];
+        o += gO[v];
+    }
+    gV[v] = ov;
+    gC[3 * (size_t)v] = c0; gC[3 * (size_t)v + 1] = c1; gC[3 * (size_t)v + 2] = c2;
+    gO[v] = o;
 }
 
 }  // namespace tg
@@ -505,71 +530,83 @@ static int blend_args(int W, int H, int tw, int th, int max_layers) {
     return TG_OK;
 }
 
-int tg_blend_forward(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids, const int32_t* offsets,
-                     int W, int H, int tw, int th, float thr, int per_pixel_sort, int max_layers, float* image,
-                     float* depthmap, float* final_weights, int32_t* ends, tg_stream_t stream) {
-    if (int s = blend_args(W, H, tw, th, max_layers)) return s;
-    TG_REQUIRE(offsets && image && depthmap && final_weights && ends, "null pointer");
-    TG_REQUIRE(((uintptr_t)image & 15) == 0 && ((uintptr_t)tri_geo & 15) == 0 && ((uintptr_t)tri_attr & 15) == 0,
-               "image / tri_geo / tri_attr must be 16-byte aligned");
+static tg::BlendParams make_params(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids,
+                                   const int32_t* offsets, int W, int H, int tw, int th, float thr, int max_layers) {
     tg::BlendParams P;
     P.geo = (const float4*)tri_geo; P.attr = (const float4*)tri_attr; P.ids = sorted_ids; P.offsets = offsets;
     P.W = W; P.H = H; P.tw = tw; P.th = th; P.tiles_x = (W + tw - 1) / tw;
     P.thr = thr; P.max_layers = max_layers;
+    return P;
+}
+
+int tg_selection_planes(int per_pixel_sort, int max_layers) {
+    return (per_pixel_sort && max_layers >= 1 && max_layers <= tg::kBatchLayers) ? max_layers : 0;
+}
+
+int tg_blend_forward(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids, const int32_t* offsets,
+                     int W, int H, int tw, int th, float thr, int per_pixel_sort, int max_layers, float* image,
+                     float* depthmap, float* final_weights, int32_t* ends, int32_t* selection, tg_stream_t stream) {
+    if (int s = blend_args(W, H, tw, th, max_layers)) return s;
+    TG_REQUIRE(offsets && image && depthmap && final_weights && ends, "null pointer");
+    TG_REQUIRE(((uintptr_t)image & 15) == 0 && ((uintptr_t)tri_geo & 15) == 0 && ((uintptr_t)tri_attr & 15) == 0,
+               "image / tri_geo / tri_attr must be 16-byte aligned");
+    if (tg_selection_planes(per_pixel_sort, max_layers) == 0) selection = nullptr;
+    const tg::BlendParams P = make_params(tri_geo, tri_attr, sorted_ids, offsets, W, H, tw, th, thr, max_layers);
     const int tiles = P.tiles_x * ((H + th - 1) / th);
     const int threads = ((tw * th + 31) / 32) * 32;
     cudaStream_t s = (cudaStream_t)stream;
     float4* img = (float4*)image;
     if (threads <= 256) {
-        if (per_pixel_sort) tg::blend_forward_kernel<true, 256><<<tiles, threads, 0, s>>>(P, img, depthmap, final_weights, ends);
-        else tg::blend_forward_kernel<false, 256><<<tiles, threads, 0, s>>>(P, img, depthmap, final_weights, ends);
+        if (per_pixel_sort) tg::blend_forward_kernel<true, 256><<<tiles, threads, 0, s>>>(P, img, depthmap, final_weights, ends, selection);
+        else tg::blend_forward_kernel<false, 256><<<tiles, threads, 0, s>>>(P, img, depthmap, final_weights, ends, nullptr);
     } else {
-        if (per_pixel_sort) tg::blend_forward_kernel<true, 1024><<<tiles, threads, 0, s>>>(P, img, depthmap, final_weights, ends);
-        else tg::blend_forward_kernel<false, 1024><<<tiles, threads, 0, s>>>(P, img, depthmap, final_weights, ends);
+        if (per_pixel_sort) tg::blend_forward_kernel<true, 1024><<<tiles, threads, 0, s>>>(P, img, depthmap, final_weights, ends, selection);
+        else tg::blend_forward_kernel<false, 1024><<<tiles, threads, 0, s>>>(P, img, depthmap, final_weights, ends, nullptr);
     }
     TG_LAUNCH_CHECK("blend_forward_kernel");
     return TG_OK;
 }
 
+size_t tg_backward_scratch_bytes(int V) { return (size_t)(V > 0 ? V : 0) * 32 + 32; }
+
 int tg_blend_backward(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids, const int32_t* offsets,
                       int V, int W, int H, int tw, int th, int per_pixel_sort, int max_layers, const float* grad_image,
                       const float* grad_depthmap, const float* image, const float* depthmap, const float* final_weights,
-                      const int32_t* ends, float* grad_vertices, float* grad_colors, float* grad_opacities,
-                      int accumulate, tg_stream_t stream) {
+                      const int32_t* ends, const int32_t* selection, float* grad_vertices, float* grad_colors,
+                      float* grad_opacities, int accumulate, void* scratch, size_t scratch_bytes, tg_stream_t stream) {
     if (int s = blend_args(W, H, tw, th, max_layers)) return s;
     TG_REQUIRE(V >= 0, "V < 0");
     TG_REQUIRE(offsets && grad_image && grad_depthmap && image && depthmap && final_weights && ends, "null pointer");
-    TG_REQUIRE(V == 0 || (grad_vertices && grad_colors && grad_opacities), "null gradient pointer");
+    if (V == 0) return TG_OK;
+    TG_REQUIRE(grad_vertices && grad_colors && grad_opacities && scratch, "null gradient / scratch pointer");
     TG_REQUIRE(((uintptr_t)image & 15) == 0 && ((uintptr_t)grad_image & 15) == 0 && ((uintptr_t)tri_geo & 15) == 0 &&
-                   ((uintptr_t)tri_attr & 15) == 0,
-               "image / grad_image / tri_geo / tri_attr must be 16-byte aligned");
-    cudaStream_t s = (cudaStream_t)stream;
-    if (!accumulate && V > 0) {
-        TG_CUDA(cudaMemsetAsync(grad_vertices, 0, sizeof(float) * 4 * (size_t)V, s));
-        TG_CUDA(cudaMemsetAsync(grad_colors, 0, sizeof(float) * 3 * (size_t)V, s));
-        TG_CUDA(cudaMemsetAsync(grad_opacities, 0, sizeof(float) * (size_t)V, s));
+                   ((uintptr_t)tri_attr & 15) == 0 && ((uintptr_t)grad_vertices & 15) == 0 && ((uintptr_t)scratch & 15) == 0,
+               "image / grad_image / tri_geo / tri_attr / grad_vertices / scratch must be 16-byte aligned");
+    if (scratch_bytes < tg_backward_scratch_bytes(V)) {
+        tg_host::set_error("backward scratch: need %zu bytes, got %zu", tg_backward_scratch_bytes(V), scratch_bytes);
+        return TG_ERR_WORKSPACE;
     }
-    tg::BlendParams P;
-    P.geo = (const float4*)tri_geo; P.attr = (const float4*)tri_attr; P.ids = sorted_ids; P.offsets = offsets;
-    P.W = W; P.H = H; P.tw = tw; P.th = th; P.tiles_x = (W + tw - 1) / tw;
-    P.thr = 0.f; P.max_layers = max_layers;
+    cudaStream_t s = (cudaStream_t)stream;
+    float4* gpack = (float4*)scratch;
+    TG_CUDA(cudaMemsetAsync(gpack, 0, (size_t)V * 32, s));
+    const tg::BlendParams P = make_params(tri_geo, tri_attr, sorted_ids, offsets, W, H, tw, th, 0.f, max_layers);
     const int tiles = P.tiles_x * ((H + th - 1) / th);
     const int threads = ((tw * th + 31) / 32) * 32;
-    tg::GradOut G = {grad_vertices, grad_colors, grad_opacities};
-    const float4* gi = (const float4*)grad_image;
-    const float4* im = (const float4*)image;
+    const tg::BackwardIn in = {(const float4*)grad_image, grad_depthmap, (const float4*)image, depthmap, final_weights, ends};
+    const bool saved = selection != nullptr && tg_selection_planes(per_pixel_sort, max_layers) > 0;
     if (threads <= 256) {
-        if (per_pixel_sort)
-            tg::blend_backward_kernel<true, 256><<<tiles, threads, 0, s>>>(P, gi, grad_depthmap, im, depthmap, final_weights, ends, G);
-        else
-            tg::blend_backward_kernel<false, 256><<<tiles, threads, 0, s>>>(P, gi, grad_depthmap, im, depthmap, final_weights, ends, G);
+        if (saved) tg::blend_backward_saved_kernel<256><<<tiles, threads, 0, s>>>(P, in, selection, gpack);
+        else if (per_pixel_sort) tg::blend_backward_kernel<true, 256><<<tiles, threads, 0, s>>>(P, in, gpack);
+        else tg::blend_backward_kernel<false, 256><<<tiles, threads, 0, s>>>(P, in, gpack);
     } else {
-        if (per_pixel_sort)
-            tg::blend_backward_kernel<true, 1024><<<tiles, threads, 0, s>>>(P, gi, grad_depthmap, im, depthmap, final_weights, ends, G);
-        else
-            tg::blend_backward_kernel<false, 1024><<<tiles, threads, 0, s>>>(P, gi, grad_depthmap, im, depthmap, final_weights, ends, G);
+        if (saved) tg::blend_backward_saved_kernel<1024><<<tiles, threads, 0, s>>>(P, in, selection, gpack);
+        else if (per_pixel_sort) tg::blend_backward_kernel<true, 1024><<<tiles, threads, 0, s>>>(P, in, gpack);
+        else tg::blend_backward_kernel<false, 1024><<<tiles, threads, 0, s>>>(P, in, gpack);
     }
     TG_LAUNCH_CHECK("blend_backward_kernel");
+    tg::unpack_gradients_kernel<<<(V + 255) / 256, 256, 0, s>>>(gpack, V, (float4*)grad_vertices, grad_colors,
+                                                              grad_opacities, accumulate);
+    TG_LAUNCH_CHECK("unpack_gradients_kernel");
     return TG_OK;
 }
 

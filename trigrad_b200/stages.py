@@ -118,28 +118,33 @@ def tile_ranges(sorted_keys: torch.Tensor, tiles: int):
     return off
 
 
-def blend_forward(sc, geo, attr, ids, offsets, thr=1 / 256, per_pixel_sort=True, max_layers=32):
+def blend_forward(sc, geo, attr, ids, offsets, thr=1 / 256, per_pixel_sort=True, max_layers=32, save_selection=True):
+    """Returns (image, depthmap, final_weights, ends, selection); selection is None when not applicable."""
     H, W = sc.height, sc.width
+    planes = N.lib().tg_selection_planes(int(per_pixel_sort), int(max_layers)) if save_selection else 0
+    sel = torch.empty((planes, H, W), dtype=torch.int32, device="cuda") if planes else None
     image = torch.empty((H, W, 4), dtype=torch.float32, device="cuda")
     depth = torch.empty((H, W), dtype=torch.float32, device="cuda")
     fw = torch.empty((H, W), dtype=torch.float32, device="cuda")
     ends = torch.empty((H, W), dtype=torch.int32, device="cuda")
     N.check("blend_forward", N.lib().tg_blend_forward(ptr(geo), ptr(attr), ptr(ids), ptr(offsets), W, H, sc.tile_width,
                                                       sc.tile_height, float(thr), int(per_pixel_sort), int(max_layers),
-                                                      ptr(image), ptr(depth), ptr(fw), ptr(ends), stream()))
-    return image, depth, fw, ends
+                                                      ptr(image), ptr(depth), ptr(fw), ptr(ends), ptr(sel), stream()))
+    return image, depth, fw, ends, sel
 
 
 def blend_backward(sc, geo, attr, ids, offsets, fwd, gimage, gdepth, per_pixel_sort=True, max_layers=32):
-    image, depth, fw, ends = fwd
+    image, depth, fw, ends, sel = fwd
     V = sc.num_vertices
+    nscratch = N.lib().tg_backward_scratch_bytes(V)
+    scratch = torch.empty(nscratch, dtype=torch.uint8, device="cuda")
     gV = torch.empty((V, 4), dtype=torch.float32, device="cuda")
     gC = torch.empty((V, 3), dtype=torch.float32, device="cuda")
     gO = torch.empty((V,), dtype=torch.float32, device="cuda")
     N.check("blend_backward", N.lib().tg_blend_backward(
         ptr(geo), ptr(attr), ptr(ids), ptr(offsets), V, sc.width, sc.height, sc.tile_width, sc.tile_height,
         int(per_pixel_sort), int(max_layers), ptr(gimage), ptr(gdepth), ptr(image), ptr(depth), ptr(fw), ptr(ends),
-        ptr(gV), ptr(gC), ptr(gO), 0, stream()))
+        ptr(sel), ptr(gV), ptr(gC), ptr(gO), 0, ptr(scratch), nscratch, stream()))
     return gV, gC, gO
 
 

@@ -86,6 +86,8 @@ def forward_native(vertices, indices, colors, opacities, width, height, tile_wid
         tri_geo = torch.empty((T, N.GEO_WORDS), **f32)
         tri_attr = torch.empty((T, N.ATTR_WORDS), **f32)
         offsets = torch.empty(tiles + 1, dtype=torch.int32, device=device)
+        planes = lib.tg_selection_planes(int(bool(per_pixel_sort)), int(max_layers))
+        selection = torch.empty((planes, height, width), dtype=torch.int32, device=device) if planes else None
         stage_ms = (C.c_float * 5)() if record_timing else None
         cap = max(int(st.k_estimate * 1.25) + 1024, 2 * T + 1024)
         while True:
@@ -97,7 +99,7 @@ def forward_native(vertices, indices, colors, opacities, width, height, tile_wid
             status = lib.tg_render_forward(
                 _ptr(vertices), _ptr(indices), _ptr(colors), _ptr(opacities), T, width, height, tile_width,
                 tile_height, float(early_stopping_threshold), int(bool(per_pixel_sort)), int(max_layers),
-                _ptr(image), _ptr(depthmap), _ptr(final_weights), _ptr(ends), _ptr(tri_geo), _ptr(tri_attr),
+                _ptr(image), _ptr(depthmap), _ptr(final_weights), _ptr(ends), _ptr(selection), _ptr(tri_geo), _ptr(tri_attr),
                 _ptr(sorted_ids), cap, _ptr(offsets), C.c_void_p(base), ws.numel() - (base - ws.data_ptr()),
                 C.c_void_p(info.data_ptr()), stage_ms, C.c_void_p(stream))
             K = int(info[0])
@@ -110,17 +112,19 @@ def forward_native(vertices, indices, colors, opacities, width, height, tile_wid
         timings = None
         if record_timing:
             timings = {k: float(stage_ms[i]) / 1000.0 for i, k in enumerate(TIMING_KEYS)}
-    return image, depthmap, final_weights, sorted_ids[:K], offsets, tri_geo, tri_attr, ends, timings
+    return image, depthmap, final_weights, sorted_ids[:K], offsets, tri_geo, tri_attr, ends, selection, timings
 
 
 def backward_native(grad_image, grad_depthmap, saved, V, width, height, tile_width, tile_height, per_pixel_sort,
                     max_layers, out=None):
     """Gradient kernel.  ``out`` = (gV, gC, gO) to accumulate into, or None to get fresh tensors."""
     lib = N.lib()
-    sorted_ids, offsets, tri_geo, tri_attr, image, depthmap, final_weights, ends = saved
+    sorted_ids, offsets, tri_geo, tri_attr, image, depthmap, final_weights, ends, selection = saved
     device = image.device
     with torch.cuda.device(device):
         stream = torch.cuda.current_stream(device).cuda_stream
+        nscratch = lib.tg_backward_scratch_bytes(V)
+        scratch = torch.empty(nscratch, dtype=torch.uint8, device=device)
         grad_image = grad_image.contiguous()
         grad_depthmap = grad_depthmap.contiguous()
         accumulate = out is not None
@@ -131,8 +135,8 @@ def backward_native(grad_image, grad_depthmap, saved, V, width, height, tile_wid
         status = lib.tg_blend_backward(
             _ptr(tri_geo), _ptr(tri_attr), _ptr(sorted_ids), _ptr(offsets), V, width, height, tile_width, tile_height,
             int(bool(per_pixel_sort)), int(max_layers), _ptr(grad_image), _ptr(grad_depthmap), _ptr(image),
-            _ptr(depthmap), _ptr(final_weights), _ptr(ends), _ptr(gV), _ptr(gC), _ptr(gO), int(accumulate),
-            C.c_void_p(stream))
+            _ptr(depthmap), _ptr(final_weights), _ptr(ends), _ptr(selection), _ptr(gV), _ptr(gC), _ptr(gO),
+            int(accumulate), _ptr(scratch), nscratch, C.c_void_p(stream))
         N.check("blend_backward", status)
     return gV, gC, gO
 
@@ -164,10 +168,13 @@ class Renderer(Function):
             ctx.save_for_backward(vertices, colors, opacities)
         else:
             ctx.skipped = False
-            (image, depthmap, final_weights, sorted_ids, offsets, tri_geo, tri_attr, ends, timings) = forward_native(
+            (image, depthmap, final_weights, sorted_ids, offsets, tri_geo, tri_attr, ends, selection,
+             timings) = forward_native(
                 vertices.contiguous(), indices.contiguous(), colors.contiguous(), opacities.contiguous(), width, height,
                 tile_width, tile_height, early_stopping_threshold, record_timing, per_pixel_sort, max_layers)
-            ctx.save_for_backward(sorted_ids, offsets, tri_geo, tri_attr, image, depthmap, final_weights, ends)
+            ctx.has_selection = selection is not None
+            saved = [sorted_ids, offsets, tri_geo, tri_attr, image, depthmap, final_weights, ends]
+            ctx.save_for_backward(*(saved + ([selection] if selection is not None else [])))
         if record_timing:
             return image, depthmap, timings
         return image, depthmap
@@ -178,7 +185,8 @@ class Renderer(Function):
             vertices, colors, opacities = ctx.saved_tensors
             gV, gC, gO = torch.zeros_like(vertices), torch.zeros_like(colors), torch.zeros_like(opacities)
         else:
-            gV, gC, gO = backward_native(grad_image, grad_depthmap, ctx.saved_tensors, ctx.num_vertices, ctx.width,
+            saved = tuple(ctx.saved_tensors) + (() if ctx.has_selection else (None,))
+            gV, gC, gO = backward_native(grad_image, grad_depthmap, saved, ctx.num_vertices, ctx.width,
                                          ctx.height, ctx.tile_width, ctx.tile_height, ctx.per_pixel_sort, ctx.max_layers)
         return (gV, None, gC, gO, None, None, None, None, None, None, None, None)
 
