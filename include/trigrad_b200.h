@@ -40,7 +40,7 @@ enum {
 
 /* Words per packed per-triangle record (float32 words). */
 #define TG_GEO_WORDS 16  /* M[9] row-major, z[3], w[3], depth lower bound */
-#define TG_ATTR_WORDS 24 /* opacity[3], colour a/b/c [9], vertex ids [3] (as int bits), pad, xy of a/b/c [6], pad[2] */
+#define TG_ATTR_WORDS 24 /* opacity[3], colour a/b/c [9], 1/w [3], vertex ids [3] (as int bits), xy of a/b/c [6] */
 
 int tg_version(void);
 const char* tg_status_string(int status);

@@ -93,8 +93,9 @@ def test_preprocess_records_bit_exact(pipeline):
     attr = p["attr"].cpu().numpy()
     assert np.array_equal(attr[:, 0:3], sc.opacities[sc.indices])
     assert np.array_equal(attr[:, 3:12], sc.colors[sc.indices].reshape(-1, 9))
-    assert np.array_equal(attr[:, 12:15].view(np.int32), sc.indices)
-    assert np.array_equal(attr[:, 16:22], v[:, :, :2].reshape(-1, 6))
+    assert np.array_equal(attr[:, 12:15], np.float32(1) / v[:, :, 3])
+    assert np.array_equal(attr[:, 15:18].view(np.int32), sc.indices)
+    assert np.array_equal(attr[:, 18:24], v[:, :, :2].reshape(-1, 6))
 
 
 def test_scan_bit_exact(pipeline):

@@ -66,9 +66,9 @@ __global__ void __launch_bounds__(256) preprocess_kernel(const float4* __restric
     q[0] = make_float4(opacities[ia], opacities[ib], opacities[ic], ca[0]);
     q[1] = make_float4(ca[1], ca[2], cb[0], cb[1]);
     q[2] = make_float4(cb[2], cc[0], cc[1], cc[2]);
-    q[3] = make_float4(__int_as_float(ia), __int_as_float(ib), __int_as_float(ic), 0.f);
-    q[4] = make_float4(a.x, a.y, b.x, b.y);
-    q[5] = make_float4(c.x, c.y, 0.f, 0.f);
+    q[3] = make_float4(div(1.f, a.w), div(1.f, b.w), div(1.f, c.w), __int_as_float(ia));
+    q[4] = make_float4(__int_as_float(ib), __int_as_float(ic), a.x, a.y);
+    q[5] = make_float4(b.x, b.y, c.x, c.y);
 }
 
 // ================================================================================================

@@ -49,34 +49,43 @@ __device__ __forceinline__ void load_geo(const float4* geo, int id, float* m, fl
 }
 
 constexpr int kAttrQuads = TG_ATTR_WORDS / 4;
-struct AttrRec { float o[3]; float c[9]; int vid[3]; float xy[6]; };
+struct AttrRec { float o[3]; float c[9]; float iw[3]; int vid[3]; float xy[6]; };
 
-// FULL = false loads only what the forward pass needs (opacities and colours).
+// FULL = false loads only what the forward pass needs (opacities, colours, 1/w).
 template <bool FULL>
 __device__ __forceinline__ AttrRec load_attr(const float4* attr, int id) {
     const float4* q = attr + kAttrQuads * (size_t)id;
-    const float4 q0 = __ldg(q), q1 = __ldg(q + 1), q2 = __ldg(q + 2);
+    const float4 q0 = __ldg(q), q1 = __ldg(q + 1), q2 = __ldg(q + 2), q3 = __ldg(q + 3);
     AttrRec a;
     a.o[0] = q0.x; a.o[1] = q0.y; a.o[2] = q0.z;
     a.c[0] = q0.w; a.c[1] = q1.x; a.c[2] = q1.y; a.c[3] = q1.z; a.c[4] = q1.w; a.c[5] = q2.x; a.c[6] = q2.y; a.c[7] = q2.z;
     a.c[8] = q2.w;
+    a.iw[0] = q3.x; a.iw[1] = q3.y; a.iw[2] = q3.z;
     if (FULL) {
-        const float4 q3 = __ldg(q + 3), q4 = __ldg(q + 4), q5 = __ldg(q + 5);
-        a.vid[0] = __float_as_int(q3.x); a.vid[1] = __float_as_int(q3.y); a.vid[2] = __float_as_int(q3.z);
-        a.xy[0] = q4.x; a.xy[1] = q4.y; a.xy[2] = q4.z; a.xy[3] = q4.w; a.xy[4] = q5.x; a.xy[5] = q5.y;
+        const float4 q4 = __ldg(q + 4), q5 = __ldg(q + 5);
+        a.vid[0] = __float_as_int(q3.w); a.vid[1] = __float_as_int(q4.x); a.vid[2] = __float_as_int(q4.y);
+        a.xy[0] = q4.z; a.xy[1] = q4.w; a.xy[2] = q5.x; a.xy[3] = q5.y; a.xy[4] = q5.z; a.xy[5] = q5.w;
     }
     return a;
 }
 
-// process_forward of the reference (render.cu:417-453); every operation rounded separately so the
-// image agrees bit for bit with the oracle.
+// process_forward of the reference (render.cu:417-453); every operation rounded separately, in the
+// oracle's order, so that the image agrees bit for bit with it.  The four weighted interpolations
+// share one correctly rounded reciprocal of their common denominator.
 __device__ __forceinline__ void blend_one(const Bary& b, const float* w, const AttrRec& a, PixelAcc& acc) {
-    float o = interp_rn(b, a.o[0], a.o[1], a.o[2], w[0], w[1], w[2]);
+    const float inv = __frcp_rn(fma_(b.z, w[2], fma_(b.y, w[1], mul(b.x, w[0]))));
+    auto weighted = [&](float a0, float a1, float a2) -> float {
+        float nom = mul(mul(b.x, a0), w[0]);
+        nom = fma_(mul(b.y, a1), w[1], nom);
+        nom = fma_(mul(b.z, a2), w[2], nom);
+        return mul(nom, inv);
+    };
+    float o = weighted(a.o[0], a.o[1], a.o[2]);
     o = fminf(fmaxf(o, 0.f), kMaxOpacity);
-    const float cr = interp_rn(b, a.c[0], a.c[3], a.c[6], w[0], w[1], w[2]);
-    const float cg = interp_rn(b, a.c[1], a.c[4], a.c[7], w[0], w[1], w[2]);
-    const float cb = interp_rn(b, a.c[2], a.c[5], a.c[8], w[0], w[1], w[2]);
-    const float zv = interp_rn(b, div(1.f, w[0]), div(1.f, w[1]), div(1.f, w[2]), 1.f, 1.f, 1.f);
+    const float cr = weighted(a.c[0], a.c[3], a.c[6]);
+    const float cg = weighted(a.c[1], a.c[4], a.c[7]);
+    const float cb = weighted(a.c[2], a.c[5], a.c[8]);
+    const float zv = interp_rn(b, a.iw[0], a.iw[1], a.iw[2], 1.f, 1.f, 1.f);
     const float ao = mul(acc.alpha, o);
     acc.depth = add(acc.depth, mul(ao, zv));
     acc.weight = add(acc.weight, ao);
@@ -258,6 +267,7 @@ __global__ void __launch_bounds__(MAXT) blend_forward_kernel(BlendParams P, floa
                 // fewer than a full batch found: the sweep saw every remaining fragment, nothing is left
                 if (found < bs) want = false;
             }
+            if (P.max_layers <= kBatchLayers) break;   // a single batch is all there can be: no second vote
         }
     } else {
         bool done = !c.active;
@@ -298,9 +308,27 @@ struct PixelGrad {
     float final_alpha, final_weight, final_depth;
 };
 
+// Approximate reciprocal (1 ulp, one MUFU instruction): gradients carry a 1e-4 tolerance and float
+// atomics already make their last bits run-dependent.
+__device__ __forceinline__ float rcp_fast(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
+// One fragment's contribution to its triangle's three vertices: (x, y, w, opacity, r, g, b) each.
+struct Contrib {
+    float v[3][7];
+    int vid[3];
+};
+
 // Packed per-vertex gradient accumulator: slot 0 = (d/dx, d/dy, d/dw, d/dopacity), slot 1 = (d/dr, d/dg, d/db, 0).
 __device__ __forceinline__ void red_add_v4(float4* addr, float a, float b, float c, float d) {
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+#ifdef TG_NO_RED   // timing experiment only: results are wrong without the reductions
+    if (a == 123456.f && b == c) *reinterpret_cast<volatile float*>(addr) = d;
+    return;
+#endif
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d));
 }
 
 // process_backward of the reference (render.cu:455-538) for one fragment of one pixel; adds this
@@ -308,23 +336,31 @@ __device__ __forceinline__ void red_add_v4(float4* addr, float a, float b, float
 // (util.h:299-355) share 1/den; vertex-position gradients follow the reference's expanded partial
 // derivatives (util.h:405-455) term by term: for small triangles their fp32 cancellation is
 // systematic and part of what "the same result" means.
+__device__ __forceinline__ void emit_contrib(const Contrib& c, float4* __restrict__ gpack) {
+#pragma unroll
+    for (int k = 0; k < 3; k++) {
+        red_add_v4(gpack + 2 * (size_t)c.vid[k], c.v[k][0], c.v[k][1], c.v[k][2], c.v[k][3]);
+        red_add_v4(gpack + 2 * (size_t)c.vid[k] + 1, c.v[k][4], c.v[k][5], c.v[k][6], 0.f);
+    }
+}
+
 __device__ __forceinline__ void backward_one(const float* w, const AttrRec& a, const Bary& b, float px, float py,
-                                             const PixelGrad& pg, BackState& st, float4* __restrict__ gpack) {
+                                             const PixelGrad& pg, BackState& st, Contrib& out) {
     const float bw0 = b.x * w[0], bw1 = b.y * w[1], bw2 = b.z * w[2];
     const float den = bw0 + bw1 + bw2;
     const bool ok = !(den * den < kEffZero);
-    const float inv = 1.f / den;
+    const float inv = rcp_fast(den);
     const float o_raw = (bw0 * a.o[0] + bw1 * a.o[1] + bw2 * a.o[2]) * inv;
     const float o = fminf(fmaxf(o_raw, 0.f), kMaxOpacity);
     const float cr = (bw0 * a.c[0] + bw1 * a.c[3] + bw2 * a.c[6]) * inv;
     const float cg = (bw0 * a.c[1] + bw1 * a.c[4] + bw2 * a.c[7]) * inv;
     const float cb = (bw0 * a.c[2] + bw1 * a.c[5] + bw2 * a.c[8]) * inv;
-    const float iw0 = 1.f / w[0], iw1 = 1.f / w[1], iw2 = 1.f / w[2];
+    const float iw0 = a.iw[0], iw1 = a.iw[1], iw2 = a.iw[2];
     const float denz = b.x + b.y + b.z;
     const bool okz = !(denz * denz < kEffZero);
-    const float invz = 1.f / denz;
+    const float invz = rcp_fast(denz);
     const float z = (b.x * iw0 + b.y * iw1 + b.z * iw2) * invz;
-    const float iom = 1.f / (1.f - o);
+    const float iom = rcp_fast(1.f - o);
 
     const float drgb_do = ((cr * st.alpha - st.sr) * pg.gr + (cg * st.alpha - st.sg) * pg.gg + (cb * st.alpha - st.sb) * pg.gb -
                            pg.ga * pg.final_alpha) * iom;
@@ -338,7 +374,7 @@ __device__ __forceinline__ void backward_one(const float* w, const AttrRec& a, c
     st.oa += ao;
     st.zoa += z * ao;
     const bool has_w = !(pg.final_weight < kEffZero);
-    const float inv_fw = has_w ? 1.f / pg.final_weight : 0.f;
+    const float inv_fw = has_w ? rcp_fast(pg.final_weight) : 0.f;
     const float dd_do = (dud_do - pg.final_depth * ddw_do) * inv_fw * pg.gd;
     const float d_do = drgb_do + (has_w ? dd_do : 0.f);
 
@@ -364,11 +400,11 @@ __device__ __forceinline__ void backward_one(const float* w, const AttrRec& a, c
     float gxy[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     const float d = ax * (by - cy) + bx * (-ay + cy) + cx * (ay - by);
     if (!(fabsf(d) < kEffZero)) {
-        const float iT = 1.f / ((bx - ax) * (cy - ay) - (by - ay) * (cx - ax));
+        const float iT = rcp_fast((bx - ax) * (cy - ay) - (by - ay) * (cx - ax));
         const float lx = ((bx - px) * (cy - py) - (by - py) * (cx - px)) * iT;
         const float ly = ((cx - px) * (ay - py) - (cy - py) * (ax - px)) * iT;
         const float lz = ((ax - px) * (by - py) - (ay - py) * (bx - px)) * iT;
-        const float id = 1.f / d;
+        const float id = rcp_fast(d);
         gxy[0] = (g0 * (lx * (-by + cy)) + g1 * (-cy - ly * (by - cy) + py) + g2 * (by - lz * (by - cy) - py)) * id;
         gxy[1] = (g0 * (lx * (bx - cx)) + g1 * (cx + ly * (bx - cx) - px) + g2 * (-bx + lz * (bx - cx) + px)) * id;
         gxy[2] = (g0 * (cy + lx * (ay - cy) - py) + g1 * (ly * (ay - cy)) + g2 * (-ay + lz * (ay - cy) + py)) * id;
@@ -376,12 +412,18 @@ __device__ __forceinline__ void backward_one(const float* w, const AttrRec& a, c
         gxy[4] = (g0 * (-by - lx * (ay - by) + py) + g1 * (ay - ly * (ay - by) - py) + g2 * (lz * (-ay + by))) * id;
         gxy[5] = (g0 * (bx + lx * (ax - bx) - px) + g1 * (-ax + ly * (ax - bx) + px) + g2 * (lz * (ax - bx))) * id;
     }
-    red_add_v4(gpack + 2 * (size_t)a.vid[0], gxy[0], gxy[1], gw0, uo * bw0);
-    red_add_v4(gpack + 2 * (size_t)a.vid[0] + 1, ur * bw0, ug * bw0, ub * bw0, 0.f);
-    red_add_v4(gpack + 2 * (size_t)a.vid[1], gxy[2], gxy[3], gw1, uo * bw1);
-    red_add_v4(gpack + 2 * (size_t)a.vid[1] + 1, ur * bw1, ug * bw1, ub * bw1, 0.f);
-    red_add_v4(gpack + 2 * (size_t)a.vid[2], gxy[4], gxy[5], gw2, uo * bw2);
-    red_add_v4(gpack + 2 * (size_t)a.vid[2] + 1, ur * bw2, ug * bw2, ub * bw2, 0.f);
+    const float gw[3] = {gw0, gw1, gw2}, bwk[3] = {bw0, bw1, bw2};
+#pragma unroll
+    for (int k = 0; k < 3; k++) {
+        out.vid[k] = a.vid[k];
+        out.v[k][0] = gxy[2 * k];
+        out.v[k][1] = gxy[2 * k + 1];
+        out.v[k][2] = gw[k];
+        out.v[k][3] = uo * bwk[k];
+        out.v[k][4] = ur * bwk[k];
+        out.v[k][5] = ug * bwk[k];
+        out.v[k][6] = ub * bwk[k];
+    }
 }
 
 struct BackwardIn {
@@ -420,13 +462,48 @@ __global__ void __launch_bounds__(MAXT) blend_backward_saved_kernel(BlendParams 
     BackState st;
     const int n = load_pixel_state(c, P, in, pg, st);
     const size_t plane = (size_t)P.W * P.H, index = (size_t)c.iy * P.W + c.ix;
-    for (int k = n - 1; k >= 0; --k) {
-        const int id = sel[(size_t)k * plane + index];
-        float m[9], w[3];
-        load_geo(P.geo, id, m, w);
-        const Bary b = apply_bary(m, c.px, c.py);
-        const AttrRec a = load_attr<true>(P.attr, id);
-        backward_one(w, a, b, c.px, c.py, pg, st, gpack);
+    const int lane = lane_id();
+    int nmax = n;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) nmax = max(nmax, __shfl_xor_sync(0xffffffffu, nmax, d));
+    // 2x2 pixel quads of the warp's 8x4 block: lanes L, L^1, L^8, L^9
+    const unsigned quad = 0x303u << (lane & ~9);
+    // ids are fetched one fragment ahead of their use
+    int id_next = (n > 0) ? sel[(size_t)(n - 1) * plane + index] : 0;
+    for (int s = 0; s < nmax; s++) {
+        const int k = n - 1 - s;
+        const bool has = k >= 0;
+        const int id = has ? id_next : -1 - lane;          // distinct negatives never match
+        if (k > 0) id_next = sel[(size_t)(k - 1) * plane + index];
+        Contrib ct;
+#pragma unroll
+        for (int j = 0; j < 3; j++) {
+            ct.vid[j] = 0;
+#pragma unroll
+            for (int q = 0; q < 7; q++) ct.v[j][q] = 0.f;
+        }
+        if (has) {
+            float m[9], w[3];
+            load_geo(P.geo, id, m, w);
+            const AttrRec a = load_attr<true>(P.attr, id);
+            const Bary b = apply_bary(m, c.px, c.py);
+            backward_one(w, a, b, c.px, c.py, pg, st, ct);
+        }
+        // Pixels of one quad that hold the same triangle are summed with two shuffle rounds and one
+        // lane issues the reductions: fewer, fuller vector atomics.
+        const unsigned peers = __match_any_sync(0xffffffffu, id);
+        const bool full4 = has && ((peers & quad) == quad);
+#pragma unroll
+        for (int j = 0; j < 3; j++) {
+#pragma unroll
+            for (int q = 0; q < 7; q++) {
+                float t = ct.v[j][q];
+                t += __shfl_xor_sync(0xffffffffu, t, 1);
+                t += __shfl_xor_sync(0xffffffffu, t, 8);
+                if (full4) ct.v[j][q] = t;
+            }
+        }
+        if (has && (!full4 || (lane & 9) == 0)) emit_contrib(ct, gpack);
     }
 }
 
@@ -459,7 +536,9 @@ __global__ void __launch_bounds__(MAXT) blend_backward_kernel(BlendParams P, Bac
                     load_geo(P.geo, id, m, w);
                     const Bary b = apply_bary(m, c.px, c.py);
                     const AttrRec a = load_attr<true>(P.attr, id);
-                    backward_one(w, a, b, c.px, c.py, pg, st, gpack);
+                    Contrib ct;
+                    backward_one(w, a, b, c.px, c.py, pg, st, ct);
+                    emit_contrib(ct, gpack);
                 }
                 if (n > 0) {
                     lastDepth = dl[n - 1];
@@ -493,7 +572,9 @@ __global__ void __launch_bounds__(MAXT) blend_backward_kernel(BlendParams P, Bac
                 const Bary b = apply_bary(g, c.px, c.py);
                 if (!covered(b)) continue;
                 const AttrRec a = load_attr<true>(P.attr, s_id[r]);
-                backward_one(g + 12, a, b, c.px, c.py, pg, st, gpack);
+                Contrib ct;
+                backward_one(g + 12, a, b, c.px, c.py, pg, st, ct);
+                emit_contrib(ct, gpack);
             }
         }
     }

@@ -76,10 +76,9 @@ struct __align__(16) Geo {
 struct __align__(16) Attr {
     float o[3];     // vertex opacities
     float c[9];     // vertex colours a.rgb b.rgb c.rgb
+    float iw[3];    // 1 / vertex w (correctly rounded), the values of the depth-map interpolation
     int vid[3];     // vertex ids
-    int pad;
     float xy[6];    // a.xy b.xy c.xy (backward: vertex-position gradients)
-    float pad2[2];
 };
 static_assert(sizeof(Geo) == 4 * TG_GEO_WORDS, "Geo layout");
 static_assert(sizeof(Attr) == 4 * TG_ATTR_WORDS, "Attr layout");
