@@ -1,5 +1,5 @@
 // Whole forward path behind one C entry point (stages 1-6 sequenced on the caller's stream).
-#include "tg_common.cuh"
+#include "tg_radix.cuh"
 
 namespace {
 
@@ -46,6 +46,21 @@ struct ForwardWorkspace {
     }
 };
 
+// One reusable event per (thread, device): marks "K has reached the host".
+int scratch_event(cudaEvent_t* out) {
+    constexpr int kMaxDevices = 64;
+    static thread_local cudaEvent_t events[kMaxDevices] = {};
+    int dev = 0;
+    TG_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) {
+        tg_host::set_error("device index %d outside the supported range", dev);
+        return TG_ERR_BAD_ARG;
+    }
+    if (events[dev] == nullptr) TG_CUDA(cudaEventCreateWithFlags(&events[dev], cudaEventDisableTiming));
+    *out = events[dev];
+    return TG_OK;
+}
+
 struct StageTimer {
     cudaEvent_t ev[6];
     int n = 0;
@@ -91,8 +106,20 @@ int tg_render_forward(const float* vertices, const int32_t* indices, const float
     info_host[0] = 0;
     info_host[1] = 0;
 
+    const int end_bit = 32 + ceil_log2(tiles);
+    const int passes = (end_bit + 7) / 8;
+    // pick the starting buffers so that the sorted ids land in the caller's array
+    uint32_t* ids_a = (passes & 1) ? ws.ids_tmp : (uint32_t*)sorted_ids;
+    uint32_t* ids_b = (passes & 1) ? (uint32_t*)sorted_ids : ws.ids_tmp;
+    TG_REQUIRE(list_capacity == 0 || sorted_ids != nullptr, "null sorted_ids");
+    cudaEvent_t k_ready;
+    if (int st = scratch_event(&k_ready)) return st;
+
     timer.mark();                                                    // [0] start of "init"
     TG_CUDA(cudaMemsetAsync(ws.status, 0, sizeof(uint32_t) * 4, s));
+    // look-back words, tickets and digit counters of the sort, sized for the whole list capacity
+    const size_t clear = tg_host::sort_scratch_clear_bytes(list_capacity, passes);
+    if (list_capacity > 0) TG_CUDA(cudaMemsetAsync(ws.sort_scratch, 0, clear, s));
     timer.mark();                                                    // [1] start of "bary_transforms" (preprocess)
     int st = tg_preprocess(vertices, indices, colors, opacities, T, W, H, tw, th, ws.tri_counts, nullptr, tri_geo,
                            tri_attr, stream);
@@ -101,26 +128,26 @@ int tg_render_forward(const float* vertices, const int32_t* indices, const float
     st = tg_scan(ws.tri_counts, ws.tri_offsets, T, ws.scan_scratch, ws.scan_scratch_bytes, ws.status, stream);
     if (st) return st;
     TG_CUDA(cudaMemcpyAsync(&info_host[0], ws.tri_offsets + T, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
-    TG_CUDA(cudaStreamSynchronize(s));
+    TG_CUDA(cudaEventRecord(k_ready, s));
+    // Keys are emitted while K travels to the host: the kernel drops entries beyond the capacity, and
+    // nothing that depends on them is launched before K has been checked.
+    if (list_capacity > 0) {
+        uint32_t* hist = (uint32_t*)ws.sort_scratch;
+        uint32_t* ctr = (uint32_t*)((char*)ws.sort_scratch + tg::kHistBytes);
+        const tg::HistArgs h = {hist, ctr + tg::kHistDoneWord, 0, end_bit, passes};
+        st = tg_host::emit_keys(vertices, indices, T, W, H, tw, th, ws.tri_offsets, ws.keys_a, ids_a, list_capacity, h, s);
+        if (st) return st;
+    }
+    TG_CUDA(cudaEventSynchronize(k_ready));
     const uint32_t K = info_host[0];
     if (K > list_capacity) {
         tg_host::set_error("K = %u exceeds the list capacity %u", K, list_capacity);
         return TG_ERR_CAPACITY;
     }
-    const int end_bit = 32 + ceil_log2(tiles);
-    const int passes = (end_bit + 7) / 8;
-    // pick the starting buffers so that the sorted ids land in the caller's array
-    uint32_t* ids_a = (passes & 1) ? ws.ids_tmp : (uint32_t*)sorted_ids;
-    uint32_t* ids_b = (passes & 1) ? (uint32_t*)sorted_ids : ws.ids_tmp;
-    if (K > 0) {
-        TG_REQUIRE(sorted_ids != nullptr, "null sorted_ids");
-        st = tg_emit_keys(vertices, indices, T, W, H, tw, th, ws.tri_offsets, ws.keys_a, ids_a, list_capacity, stream);
-        if (st) return st;
-    }
     timer.mark();                                                    // [3] start of "sorting"
     int in_b = 0;
-    st = tg_sort_pairs(ws.keys_a, ws.keys_b, ids_a, ids_b, K, 0, end_bit, ws.sort_scratch, ws.sort_scratch_bytes,
-                       ws.status, &in_b, stream);
+    st = tg_host::sort_pairs(ws.keys_a, ws.keys_b, ids_a, ids_b, K, 0, end_bit, ws.sort_scratch, ws.sort_scratch_bytes,
+                             ws.status, &in_b, true, s);
     if (st) return st;
     st = tg_tile_ranges(in_b ? ws.keys_b : ws.keys_a, K, tiles, offsets, stream);
     if (st) return st;

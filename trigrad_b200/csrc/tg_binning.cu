@@ -4,7 +4,7 @@
 
 #include <atomic>
 
-#include "tg_common.cuh"
+#include "tg_radix.cuh"
 
 namespace tg {
 
@@ -252,65 +252,79 @@ __device__ float tile_key(const TriXYZ& v, const Plane& pl, int tx, int ty, int 
     return md;
 }
 
-constexpr int kEmitSmall = 16;   // triangles touching more tiles than this are emitted by the whole warp
+// One CTA takes 256 consecutive triangles.  Phase 1 (a thread per triangle) gathers the vertices and
+// stages rectangle, depth plane and first output slot in shared memory.  Phase 2 (a thread per
+// OUTPUT entry) finds its triangle by binary search over the staged offsets, so that a triangle
+// touching many tiles is spread over the whole CTA and no lane idles behind a long neighbour.
+// When `hist.hist` is set the digits of the written keys are counted on the fly, which saves the
+// radix sort its own histogram pass over the keys.
+struct __align__(16) EmitTri {
+    float ax, ay, az, bx, by, bz, cx, cy, cz;
+    float A, B, C;
+    int x0, y0, ny, pad;
+};
+constexpr int kEmitThreads = 256;
 
-__global__ void __launch_bounds__(256) emit_keys_kernel(const float4* __restrict__ vertices,
-                                                        const int* __restrict__ indices, int T, int W, int H, int tw,
-                                                        int th, int tiles_x, int tiles_y,
-                                                        const uint32_t* __restrict__ tri_offsets,
-                                                        uint64_t* __restrict__ keys, uint32_t* __restrict__ ids,
-                                                        uint32_t capacity) {
-    const int t = blockIdx.x * blockDim.x + threadIdx.x;
-    TriXYZ v = {};
-    Rect r = {0, -1, 0, -1};
-    uint32_t base = 0, n = 0;
-    Plane pl = {0.f, 0.f, 0.f};
-    if (t < T) {
-        int ia = indices[3 * (size_t)t], ib = indices[3 * (size_t)t + 1], ic = indices[3 * (size_t)t + 2];
-        float4 a = vertices[ia], b = vertices[ib], c = vertices[ic];
-        v = {a.x, a.y, a.z, b.x, b.y, b.z, c.x, c.y, c.z};
+__global__ void __launch_bounds__(kEmitThreads) emit_keys_kernel(const float4* __restrict__ vertices,
+                                                                 const int* __restrict__ indices, int T, int W, int H,
+                                                                 int tw, int th, int tiles_x, int tiles_y,
+                                                                 const uint32_t* __restrict__ tri_offsets,
+                                                                 uint64_t* __restrict__ keys, uint32_t* __restrict__ ids,
+                                                                 uint32_t capacity, HistArgs hist) {
+    __shared__ EmitTri s_tri[kEmitThreads];
+    __shared__ uint32_t s_off[kEmitThreads + 1];
+    __shared__ uint32_t s_hist[kMaxPasses * kRadix];
+    __shared__ uint32_t s_warp_tot[kSortWarps];
+    __shared__ bool s_last;
+    const int tid = threadIdx.x;
+    const int t0 = blockIdx.x * kEmitThreads;
+    const int ntri = min(kEmitThreads, T - t0);
+    if (hist.hist)
+        for (int i = tid; i < hist.passes * kRadix; i += kEmitThreads) s_hist[i] = 0;
+    if (tid < ntri) {
+        const int t = t0 + tid;
+        const int ia = indices[3 * (size_t)t], ib = indices[3 * (size_t)t + 1], ic = indices[3 * (size_t)t + 2];
+        const float4 a = vertices[ia], b = vertices[ib], c = vertices[ic];
+        EmitTri e;
+        e.ax = a.x; e.ay = a.y; e.az = a.z; e.bx = b.x; e.by = b.y; e.bz = b.z; e.cx = c.x; e.cy = c.y; e.cz = c.z;
+        Rect r;
         if (tile_rect(a.x, a.y, b.x, b.y, c.x, c.y, W, H, tw, th, tiles_x, tiles_y, r)) {
-            n = (uint32_t)(r.x1 - r.x0 + 1) * (uint32_t)(r.y1 - r.y0 + 1);
-            base = tri_offsets[t];
-            if ((uint64_t)base + n > capacity) n = 0;   // defensive: host checks K <= capacity before launching
-            pl = depth_plane(a.x, a.y, a.z, b.x, b.y, b.z, c.x, c.y, c.z);
+            const Plane pl = depth_plane(a.x, a.y, a.z, b.x, b.y, b.z, c.x, c.y, c.z);
+            e.A = pl.A; e.B = pl.B; e.C = pl.C;
+        } else {
+            e.A = e.B = e.C = 0.f;
+        }
+        e.x0 = r.x0; e.y0 = r.y0; e.ny = r.y1 - r.y0 + 1; e.pad = 0;
+        s_tri[tid] = e;
+        s_off[tid] = tri_offsets[t];
+    }
+    if (tid == 0) s_off[ntri] = tri_offsets[t0 + ntri];
+    __syncthreads();
+    const uint32_t first = s_off[0], total = s_off[ntri] - first;
+    for (uint32_t e = tid; e < total; e += kEmitThreads) {
+        const uint32_t ge = first + e;
+        // largest i in [0, ntri) with s_off[i] <= ge (triangles without entries have equal offsets)
+        int lo = 0, hi = ntri;
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_off[mid] <= ge) lo = mid; else hi = mid;
+        }
+        const EmitTri& tr = s_tri[lo];
+        const uint32_t local = ge - s_off[lo];
+        const int tx = tr.x0 + (int)(local / (uint32_t)tr.ny), ty = tr.y0 + (int)(local % (uint32_t)tr.ny);
+        const TriXYZ v = {tr.ax, tr.ay, tr.az, tr.bx, tr.by, tr.bz, tr.cx, tr.cy, tr.cz};
+        const Plane pl = {tr.A, tr.B, tr.C};
+        const float depth = tile_key(v, pl, tx, ty, W, H, tw, th);
+        const uint64_t key = ((uint64_t)(uint32_t)(ty * tiles_x + tx) << 32) | float_to_ordered(depth);
+        if (ge < capacity) {                       // the host guarantees K <= capacity before the result is used
+            keys[ge] = key;
+            ids[ge] = (uint32_t)(t0 + lo);
+            if (hist.hist) hist_count(s_hist, key, hist);
         }
     }
-    if (n > 0 && n <= (uint32_t)kEmitSmall) {
-        const int ny = r.y1 - r.y0 + 1;
-        for (uint32_t i = 0; i < n; i++) {
-            int tx = r.x0 + (int)i / ny, ty = r.y0 + (int)i % ny;
-            float key = tile_key(v, pl, tx, ty, W, H, tw, th);
-            keys[base + i] = ((uint64_t)(uint32_t)(ty * tiles_x + tx) << 32) | float_to_ordered(key);
-            ids[base + i] = (uint32_t)t;
-        }
-    }
-    // large triangles: the warp walks the rectangle together
-    unsigned big = __ballot_sync(0xffffffffu, n > (uint32_t)kEmitSmall);
-    while (big) {
-        const int src = __ffs(big) - 1;
-        big &= big - 1;
-        TriXYZ bv;
-        bv.ax = __shfl_sync(0xffffffffu, v.ax, src); bv.ay = __shfl_sync(0xffffffffu, v.ay, src);
-        bv.az = __shfl_sync(0xffffffffu, v.az, src); bv.bx = __shfl_sync(0xffffffffu, v.bx, src);
-        bv.by = __shfl_sync(0xffffffffu, v.by, src); bv.bz = __shfl_sync(0xffffffffu, v.bz, src);
-        bv.cx = __shfl_sync(0xffffffffu, v.cx, src); bv.cy = __shfl_sync(0xffffffffu, v.cy, src);
-        bv.cz = __shfl_sync(0xffffffffu, v.cz, src);
-        Plane bp;
-        bp.A = __shfl_sync(0xffffffffu, pl.A, src);
-        bp.B = __shfl_sync(0xffffffffu, pl.B, src);
-        bp.C = __shfl_sync(0xffffffffu, pl.C, src);
-        const int bx0 = __shfl_sync(0xffffffffu, r.x0, src), by0 = __shfl_sync(0xffffffffu, r.y0, src);
-        const int by1 = __shfl_sync(0xffffffffu, r.y1, src);
-        const uint32_t bn = __shfl_sync(0xffffffffu, n, src), bbase = __shfl_sync(0xffffffffu, base, src);
-        const uint32_t bt = __shfl_sync(0xffffffffu, (uint32_t)t, src);
-        const int ny = by1 - by0 + 1;
-        for (uint32_t i = lane_id(); i < bn; i += 32) {
-            int tx = bx0 + (int)(i / (uint32_t)ny), ty = by0 + (int)(i % (uint32_t)ny);
-            float key = tile_key(bv, bp, tx, ty, W, H, tw, th);
-            keys[bbase + i] = ((uint64_t)(uint32_t)(ty * tiles_x + tx) << 32) | float_to_ordered(key);
-            ids[bbase + i] = bt;
-        }
+    if (hist.hist) {
+        __syncthreads();
+        hist_flush_and_finish(s_hist, s_warp_tot, &s_last, hist);
     }
 }
 
@@ -343,6 +357,27 @@ int cuda_fail(cudaError_t e, const char* what) {
     return TG_ERR_CUDA;
 }
 const char* last_error() { return g_err; }
+
+static int check_dims_internal(int T, int W, int H, int tw, int th) {
+    TG_REQUIRE(T >= 0, "T < 0");
+    TG_REQUIRE(W > 0 && H > 0, "image size must be positive");
+    TG_REQUIRE(tw > 0 && th > 0, "tile size must be positive");
+    TG_REQUIRE(tw * th <= 1024, "tile_width * tile_height must be <= 1024");
+    return TG_OK;
+}
+
+int emit_keys(const float* vertices, const int32_t* indices, int T, int W, int H, int tw, int th,
+              const uint32_t* tri_offsets, uint64_t* keys, uint32_t* ids, uint32_t capacity, const tg::HistArgs& hist,
+              cudaStream_t stream) {
+    if (int s = check_dims_internal(T, W, H, tw, th)) return s;
+    if (T == 0) return TG_OK;
+    TG_REQUIRE(vertices && indices && tri_offsets && keys && ids, "null pointer");
+    const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
+    tg::emit_keys_kernel<<<(T + tg::kEmitThreads - 1) / tg::kEmitThreads, tg::kEmitThreads, 0, stream>>>(
+        (const float4*)vertices, indices, T, W, H, tw, th, tiles_x, tiles_y, tri_offsets, keys, ids, capacity, hist);
+    TG_LAUNCH_CHECK("emit_keys_kernel");
+    return TG_OK;
+}
 static std::atomic<unsigned long long> g_launches{0};
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 }  // namespace tg_host
@@ -478,15 +513,9 @@ int tg_scan_static(const uint32_t* in, uint32_t* out, int n, uint32_t* status, t
 
 int tg_emit_keys(const float* vertices, const int32_t* indices, int T, int W, int H, int tw, int th,
                  const uint32_t* tri_offsets, uint64_t* keys, uint32_t* ids, uint32_t capacity, tg_stream_t stream) {
-    if (int s = check_dims(T, W, H, tw, th)) return s;
-    if (T == 0) return TG_OK;
-    TG_REQUIRE(vertices && indices && tri_offsets && keys && ids, "null pointer");
-    const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
-    tg::emit_keys_kernel<<<(T + 255) / 256, 256, 0, (cudaStream_t)stream>>>((const float4*)vertices, indices, T, W, H,
-                                                                            tw, th, tiles_x, tiles_y, tri_offsets, keys,
-                                                                            ids, capacity);
-    TG_LAUNCH_CHECK("emit_keys_kernel");
-    return TG_OK;
+    const tg::HistArgs no_hist = {nullptr, nullptr, 0, 0, 0};
+    return tg_host::emit_keys(vertices, indices, T, W, H, tw, th, tri_offsets, keys, ids, capacity, no_hist,
+                              (cudaStream_t)stream);
 }
 
 int tg_tile_ranges(const uint64_t* sorted_keys, uint32_t n, int tiles, int32_t* offsets, tg_stream_t stream) {

@@ -1,0 +1,89 @@
+// Radix-sort constants and the digit-histogram helpers shared by the sort kernels and by the key
+// emission kernel (which can count the digits of the keys it writes, saving one read of them).
+#pragma once
+#include "tg_common.cuh"
+
+namespace tg {
+
+constexpr int kRadixBits = 8;
+constexpr int kRadix = 1 << kRadixBits;
+constexpr int kMaxPasses = 8;
+constexpr int kSortThreads = 256;
+constexpr int kSortWarps = kSortThreads / 32;
+
+// scratch layout (bytes): [0, 8 KB) digit histograms / offsets [kMaxPasses][256] uint32,
+// [8 KB, 8 KB + 64) tickets[kMaxPasses] + histogram-done counter (word 8), then the look-back words
+// [passes][parts][256] uint64.
+constexpr size_t kHistBytes = (size_t)kMaxPasses * kRadix * sizeof(uint32_t);
+constexpr size_t kCtrBytes = 64;
+constexpr int kHistDoneWord = 8;
+
+// Exclusive scan of one value per thread over a CTA of 256 threads.
+__device__ __forceinline__ uint32_t block_exclusive_scan_256(uint32_t v, uint32_t* s_warp_tot /*[8]*/) {
+    uint32_t incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        uint32_t y = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane_id() >= (unsigned)d) incl += y;
+    }
+    const int warp = threadIdx.x >> 5;
+    __syncthreads();   // protect s_warp_tot from a previous use
+    if (lane_id() == 31) s_warp_tot[warp] = incl;
+    __syncthreads();
+    uint32_t off = 0;
+#pragma unroll
+    for (int w = 0; w < kSortWarps; w++) {
+        uint32_t x = s_warp_tot[w];
+        if (w < warp) off += x;
+    }
+    return off + incl - v;
+}
+
+struct HistArgs {
+    uint32_t* hist;           // [kMaxPasses][256] global counts, zeroed by the host; NULL = no histogram
+    uint32_t* done_counter;   // zeroed by the host
+    int begin_bit, end_bit, passes;
+};
+
+// Count the digits of one key into the CTA's shared histogram.
+__device__ __forceinline__ void hist_count(uint32_t* s_hist, uint64_t key, const HistArgs& h) {
+    for (int p = 0; p < h.passes; p++) {
+        const int shift = h.begin_bit + p * kRadixBits;
+        const int bits = min(kRadixBits, h.end_bit - shift);
+        atomicAdd(&s_hist[p * kRadix + ((uint32_t)(key >> shift) & ((1u << bits) - 1u))], 1u);
+    }
+}
+
+// Add the CTA's histogram to the global one; the last CTA to arrive turns the global counts into
+// exclusive digit offsets, per pass.  Call with all 256 threads of every CTA, after a barrier.
+__device__ __forceinline__ void hist_flush_and_finish(uint32_t* s_hist, uint32_t* s_warp_tot, bool* s_last,
+                                                      const HistArgs& h) {
+    for (int i = threadIdx.x; i < h.passes * kRadix; i += kSortThreads) {
+        const uint32_t c = s_hist[i];
+        if (c) atomicAdd(&h.hist[i], c);
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) *s_last = (atomicAdd(h.done_counter, 1u) == gridDim.x - 1);
+    __syncthreads();
+    if (!*s_last) return;
+    __threadfence();
+    for (int p = 0; p < h.passes; p++) {
+        const uint32_t c = __ldcg(&h.hist[p * kRadix + threadIdx.x]);
+        const uint32_t e = block_exclusive_scan_256(c, s_warp_tot);
+        h.hist[p * kRadix + threadIdx.x] = e;
+    }
+}
+
+}  // namespace tg
+
+namespace tg_host {
+// Internal (not part of the C ABI): the pieces tg_render_forward strings together.
+int emit_keys(const float* vertices, const int32_t* indices, int T, int W, int H, int tw, int th,
+              const uint32_t* tri_offsets, uint64_t* keys, uint32_t* ids, uint32_t capacity, const tg::HistArgs& hist,
+              cudaStream_t stream);
+int sort_pairs(uint64_t* keys_a, uint64_t* keys_b, uint32_t* vals_a, uint32_t* vals_b, uint32_t n, int begin_bit,
+               int end_bit, void* scratch, size_t scratch_bytes, uint32_t* status, int* result_in_b_host,
+               bool scratch_prepared, cudaStream_t stream);
+size_t sort_scratch_clear_bytes(uint32_t n, int passes);
+}  // namespace tg_host

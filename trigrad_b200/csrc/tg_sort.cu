@@ -7,87 +7,27 @@
 // (one thread per digit, bounded waits) and scatters keys and values through shared memory so
 // that global writes are contiguous runs per digit.  Every pass reads 12 B and writes 12 B per
 // pair: HBM-bound.
-#include "tg_common.cuh"
+#include "tg_radix.cuh"
 
 namespace tg {
 
-constexpr int kRadixBits = 8;
-constexpr int kRadix = 1 << kRadixBits;
-constexpr int kMaxPasses = 8;
-constexpr int kSortThreads = 256;
-constexpr int kSortWarps = kSortThreads / 32;
+// Pairs per thread: 16 (4096-pair tiles) amortises the per-tile histogram work.
 constexpr int kSortItems = 16;
-constexpr int kSortTile = kSortThreads * kSortItems;   // 4096 pairs per CTA
+constexpr int kSortTile = kSortThreads * kSortItems;
 constexpr uint32_t kSortSpinLimit = 1u << 22;
-
 constexpr uint64_t kFlagAggregate = 1ull << 32;
 constexpr uint64_t kFlagInclusive = 2ull << 32;
-
-// scratch layout (bytes): [0, 8 KB) digit histograms / offsets [kMaxPasses][256] uint32,
-// [8 KB, 8 KB + 64) tickets[kMaxPasses] + histogram-done counter, then the look-back words
-// [passes][parts][256] uint64.
-constexpr size_t kHistBytes = (size_t)kMaxPasses * kRadix * sizeof(uint32_t);
-constexpr size_t kCtrBytes = 64;
-
-__device__ __forceinline__ uint32_t block_exclusive_scan_256(uint32_t v, uint32_t* s_warp_tot /*[8]*/,
-                                                             uint32_t* block_total = nullptr) {
-    uint32_t incl = v;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-        uint32_t y = __shfl_up_sync(0xffffffffu, incl, d);
-        if (lane_id() >= (unsigned)d) incl += y;
-    }
-    const int warp = threadIdx.x >> 5;
-    __syncthreads();   // protect s_warp_tot from a previous use
-    if (lane_id() == 31) s_warp_tot[warp] = incl;
-    __syncthreads();
-    uint32_t off = 0, tot = 0;
-#pragma unroll
-    for (int w = 0; w < kSortWarps; w++) {
-        uint32_t x = s_warp_tot[w];
-        if (w < warp) off += x;
-        tot += x;
-    }
-    if (block_total) *block_total = tot;
-    return off + incl - v;
-}
-
 __global__ void __launch_bounds__(kSortThreads) sort_histogram_kernel(const uint64_t* __restrict__ keys, uint32_t n,
-                                                                      int begin_bit, int end_bit, int passes,
-                                                                      uint32_t* __restrict__ hist,
-                                                                      uint32_t* __restrict__ done_counter) {
+                                                                      HistArgs h) {
     __shared__ uint32_t s_hist[kMaxPasses * kRadix];
     __shared__ uint32_t s_warp_tot[kSortWarps];
     __shared__ bool s_last;
-    for (int i = threadIdx.x; i < passes * kRadix; i += kSortThreads) s_hist[i] = 0;
+    for (int i = threadIdx.x; i < h.passes * kRadix; i += kSortThreads) s_hist[i] = 0;
     __syncthreads();
     const uint32_t stride = gridDim.x * kSortThreads;
-    for (uint32_t i = blockIdx.x * kSortThreads + threadIdx.x; i < n; i += stride) {
-        const uint64_t k = keys[i];
-        for (int p = 0; p < passes; p++) {
-            const int shift = begin_bit + p * kRadixBits;
-            const int bits = min(kRadixBits, end_bit - shift);
-            const uint32_t d = (uint32_t)(k >> shift) & ((1u << bits) - 1u);
-            atomicAdd(&s_hist[p * kRadix + d], 1u);
-        }
-    }
+    for (uint32_t i = blockIdx.x * kSortThreads + threadIdx.x; i < n; i += stride) hist_count(s_hist, keys[i], h);
     __syncthreads();
-    for (int i = threadIdx.x; i < passes * kRadix; i += kSortThreads) {
-        const uint32_t c = s_hist[i];
-        if (c) atomicAdd(&hist[i], c);
-    }
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) s_last = (atomicAdd(done_counter, 1u) == gridDim.x - 1);
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    // last CTA: counts -> exclusive global digit offsets, per pass
-    for (int p = 0; p < passes; p++) {
-        const uint32_t c = __ldcg(&hist[p * kRadix + threadIdx.x]);
-        const uint32_t e = block_exclusive_scan_256(c, s_warp_tot);
-        hist[p * kRadix + threadIdx.x] = e;
-    }
+    hist_flush_and_finish(s_hist, s_warp_tot, &s_last, h);
 }
 
 __device__ __forceinline__ uint64_t ld_word(const uint64_t* p) { return *(const volatile uint64_t*)p; }
@@ -174,11 +114,11 @@ __global__ void __launch_bounds__(kSortThreads) onesweep_pass_kernel(
     {
         uint64_t* mine = lookback + (size_t)p * kRadix + tid;
         uint32_t excl = 0;
+        bool failed = false;
         if (p == 0) {
             st_word(mine, kFlagInclusive | cta_count);
         } else {
             st_word(mine, kFlagAggregate | cta_count);
-            bool failed = false;
             for (int64_t q = (int64_t)p - 1; q >= 0; --q) {
                 const uint64_t* w = lookback + (size_t)q * kRadix + tid;
                 uint64_t word = 0;
@@ -192,9 +132,9 @@ __global__ void __launch_bounds__(kSortThreads) onesweep_pass_kernel(
                 excl += (uint32_t)word;
                 if ((word >> 32) == 2u) break;
             }
-            if (failed) { sm.fail = 1; atomicExch(status, 2u); }
             st_word(mine, kFlagInclusive | (uint64_t)(excl + cta_count));
         }
+        if (failed) { sm.fail = 1; atomicExch(status, 2u); }
         sm.digit_start[tid] = dstart;
         sm.bin_offset[tid] = digit_offsets[tid] + excl - dstart;   // modulo 2^32 on purpose
     }
@@ -225,18 +165,21 @@ __global__ void __launch_bounds__(kSortThreads) onesweep_pass_kernel(
 
 }  // namespace tg
 
-extern "C" {
+namespace tg_host {
 
 static inline int sort_passes(int begin_bit, int end_bit) { return (end_bit - begin_bit + tg::kRadixBits - 1) / tg::kRadixBits; }
+static inline size_t sort_parts(uint32_t n) { return ((size_t)n + tg::kSortTile - 1) / tg::kSortTile; }
 
-size_t tg_sort_scratch_bytes(uint32_t n) {
-    const size_t parts = ((size_t)n + tg::kSortTile - 1) / tg::kSortTile;
-    return tg::kHistBytes + tg::kCtrBytes + (size_t)tg::kMaxPasses * (parts ? parts : 1) * tg::kRadix * sizeof(uint64_t);
+size_t sort_scratch_clear_bytes(uint32_t n, int passes) {
+    return tg::kHistBytes + tg::kCtrBytes + (size_t)passes * sort_parts(n) * tg::kRadix * sizeof(uint64_t);
 }
 
-int tg_sort_pairs(uint64_t* keys_a, uint64_t* keys_b, uint32_t* vals_a, uint32_t* vals_b, uint32_t n, int begin_bit,
-                  int end_bit, void* scratch, size_t scratch_bytes, uint32_t* status, int* result_in_b_host,
-                  tg_stream_t stream) {
+// scratch_prepared: the caller has zeroed sort_scratch_clear_bytes(>= n) bytes and filled the digit
+// offsets (the key-emission kernel counts digits as it writes keys); then no clearing and no
+// histogram pass are needed here.
+int sort_pairs(uint64_t* keys_a, uint64_t* keys_b, uint32_t* vals_a, uint32_t* vals_b, uint32_t n, int begin_bit,
+               int end_bit, void* scratch, size_t scratch_bytes, uint32_t* status, int* result_in_b_host,
+               bool scratch_prepared, cudaStream_t s) {
     TG_REQUIRE(begin_bit >= 0 && end_bit <= 64 && begin_bit < end_bit, "bit range");
     TG_REQUIRE(n < 0x80000000u, "n must stay below 2^31");
     const int passes = sort_passes(begin_bit, end_bit);
@@ -245,18 +188,24 @@ int tg_sort_pairs(uint64_t* keys_a, uint64_t* keys_b, uint32_t* vals_a, uint32_t
     if (n == 0) return TG_OK;
     TG_REQUIRE(keys_a && keys_b && vals_a && vals_b && scratch && status, "null pointer");
     TG_REQUIRE(((uintptr_t)scratch & 15) == 0, "scratch must be 16-byte aligned");
-    const size_t parts = ((size_t)n + tg::kSortTile - 1) / tg::kSortTile;
-    const size_t need = tg::kHistBytes + tg::kCtrBytes + (size_t)passes * parts * tg::kRadix * sizeof(uint64_t);
+    const size_t parts = sort_parts(n);
+    const size_t need = sort_scratch_clear_bytes(n, passes);
     if (scratch_bytes < need) {
-        tg_host::set_error("sort scratch: need %zu bytes, got %zu", need, scratch_bytes);
+        set_error("sort scratch: need %zu bytes, got %zu", need, scratch_bytes);
         return TG_ERR_WORKSPACE;
     }
-    cudaStream_t s = (cudaStream_t)stream;
     uint32_t* hist = (uint32_t*)scratch;
     uint32_t* ctr = (uint32_t*)((char*)scratch + tg::kHistBytes);   // [0..7] tickets, [8] histogram-done
     uint64_t* lookback = (uint64_t*)((char*)scratch + tg::kHistBytes + tg::kCtrBytes);
-    TG_CUDA(cudaMemsetAsync(scratch, 0, need, s));
-
+    if (!scratch_prepared) {
+        TG_CUDA(cudaMemsetAsync(scratch, 0, need, s));
+        int hist_grid = (int)((n + tg::kSortThreads * 16 - 1) / (tg::kSortThreads * 16));
+        if (hist_grid > 148 * 8) hist_grid = 148 * 8;
+        if (hist_grid < 1) hist_grid = 1;
+        const tg::HistArgs h = {hist, ctr + tg::kHistDoneWord, begin_bit, end_bit, passes};
+        tg::sort_histogram_kernel<<<hist_grid, tg::kSortThreads, 0, s>>>(keys_a, n, h);
+        TG_LAUNCH_CHECK("sort_histogram_kernel");
+    }
     static thread_local int smem_set_device = -1;
     int dev = 0;
     TG_CUDA(cudaGetDevice(&dev));
@@ -265,25 +214,33 @@ int tg_sort_pairs(uint64_t* keys_a, uint64_t* keys_b, uint32_t* vals_a, uint32_t
                                      (int)sizeof(tg::SortSmem)));
         smem_set_device = dev;
     }
-    int hist_grid = (int)((n + tg::kSortThreads * 16 - 1) / (tg::kSortThreads * 16));
-    if (hist_grid > 148 * 8) hist_grid = 148 * 8;
-    if (hist_grid < 1) hist_grid = 1;
-    tg::sort_histogram_kernel<<<hist_grid, tg::kSortThreads, 0, s>>>(keys_a, n, begin_bit, end_bit, passes, hist, ctr + 8);
-    TG_LAUNCH_CHECK("sort_histogram_kernel");
     uint64_t* kin = keys_a; uint64_t* kout = keys_b;
     uint32_t* vin = vals_a; uint32_t* vout = vals_b;
     for (int p = 0; p < passes; p++) {
         const int shift = begin_bit + p * tg::kRadixBits;
         const int bits = (end_bit - shift < tg::kRadixBits) ? (end_bit - shift) : tg::kRadixBits;
+        uint64_t* lb = lookback + (size_t)p * parts * tg::kRadix;
         tg::onesweep_pass_kernel<<<(unsigned)parts, tg::kSortThreads, sizeof(tg::SortSmem), s>>>(
-            kin, vin, kout, vout, n, shift, bits, hist + p * tg::kRadix, ctr + p, lookback + (size_t)p * parts * tg::kRadix,
-            status);
+            kin, vin, kout, vout, n, shift, bits, hist + p * tg::kRadix, ctr + p, lb, status);
         TG_LAUNCH_CHECK("onesweep_pass_kernel");
         uint64_t* tk = kin; kin = kout; kout = tk;
         uint32_t* tv = vin; vin = vout; vout = tv;
     }
     if (result_in_b_host) *result_in_b_host = passes & 1;
     return TG_OK;
+}
+
+}  // namespace tg_host
+
+extern "C" {
+
+size_t tg_sort_scratch_bytes(uint32_t n) { return tg_host::sort_scratch_clear_bytes(n, tg::kMaxPasses); }
+
+int tg_sort_pairs(uint64_t* keys_a, uint64_t* keys_b, uint32_t* vals_a, uint32_t* vals_b, uint32_t n, int begin_bit,
+                  int end_bit, void* scratch, size_t scratch_bytes, uint32_t* status, int* result_in_b_host,
+                  tg_stream_t stream) {
+    return tg_host::sort_pairs(keys_a, keys_b, vals_a, vals_b, n, begin_bit, end_bit, scratch, scratch_bytes, status,
+                               result_in_b_host, false, (cudaStream_t)stream);
 }
 
 }  // extern "C"
