@@ -3,9 +3,10 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg3|cfg2|cfg1|cfg5]
 
 Workload (default): BASELINE config 3 - 200 000 seeded random triangles, 1920x1080, 16x16 tiles, fp32,
-forward + backward of mean((image - target)^2).  One step = one view through the whole path.  With
-N > 1 GPUs (one process per GPU under torchrun) every rank renders its own view of the same mesh per
-step and the vertex/colour/opacity gradients are summed with one NCCL all-reduce (weak scaling).
+forward + backward of mean((image - target)^2).  One step = a batch of views of the mesh (default 8 per GPU, each with its
+own target image) through the whole path, gradients summed.  With N > 1 GPUs (one process per GPU under
+torchrun) every rank renders its own views and the summed vertex/colour/opacity gradients are combined
+with one NCCL all-reduce per step (weak scaling: per-GPU work is fixed).
 
 Prints ONE JSON line (rank 0).  `value` is fwd+bwd Mpix/s with inputs resident in HBM, timed with CUDA
 events per step with an L2 flush between steps; `e2e` is the same through ``trigrad_b200.render`` from
@@ -194,6 +195,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg3")
+    ap.add_argument("--views-per-gpu", type=int, default=8,
+                    help="views of the mesh rendered per GPU per step (a batch of views; gradients are summed)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
 
@@ -222,23 +225,26 @@ def main() -> None:
     scene, wname = make_scene(args.workload)
     W, H = scene.width, scene.height
     T, V = scene.num_triangles, scene.num_vertices
-    verts_np = view_vertices(scene.vertices, rank)
-    target_np = scene.target()
+    B = max(1, args.views_per_gpu)
+    # rank r renders views [r*B, (r+1)*B) of the same mesh; every view has its own target image
+    views_np = [view_vertices(scene.vertices, rank * B + b) for b in range(B)]
+    rng = np.random.default_rng(3 + rank)
+    targets_np = [scene.target() if b == 0 else rng.random((H, W, 4), dtype=np.float32) for b in range(B)]
+    verts_np = views_np[0]
 
-    v = torch.from_numpy(verts_np).to(dev)
     i = torch.from_numpy(scene.indices).to(dev)
     c = torch.from_numpy(scene.colors).to(dev)
     o = torch.from_numpy(scene.opacities).to(dev)
-    target = torch.from_numpy(target_np).to(dev)
+    dv = [torch.from_numpy(x).to(dev) for x in views_np]
+    dt = [torch.from_numpy(x).to(dev) for x in targets_np]
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)    # > L2 (126 MB)
-    grads = Vw.GradBuffer.allocate(V, dev)
-    gV4 = torch.zeros((V, 4), dtype=torch.float32, device=dev)
+    grads = Vw.GradBuffer.allocate(V, dev, position_components=4)
 
     lib = N.lib()
     inv_n = 1.0 / float(W * H * 4)
 
-    def step():
-        """fwd + bwd of one view through the public API, gradients into the all-reduce buffer."""
+    def render_view(v, target):
+        """fwd + bwd of one view through the public API; gradients added into the all-reduce buffer."""
         vv = v.detach().requires_grad_(True)
         cc = c.detach().requires_grad_(True)
         oo = o.detach().requires_grad_(True)
@@ -249,12 +255,21 @@ def main() -> None:
         loss = torch.dot(flat, flat) * inv_n
         g.mul_(2.0 * inv_n)
         gv, gc, go = torch.autograd.grad(image, (vv, cc, oo), grad_outputs=g)
+        grads.points.add_(gv)
+        grads.colors.add_(gc)
+        grads.opacities.add_(go)
+        return loss
+
+    def step(vs, ts):
+        """One step: B views back to back, then (N > 1) one all-reduce of the summed gradients."""
+        grads.zero_()
+        loss = None
+        for v, t in zip(vs, ts):
+            l = render_view(v, t)
+            loss = l if loss is None else loss + l
         if world > 1:
-            grads.points.copy_(gv[:, [0, 1, 3]])
-            grads.colors.copy_(gc)
-            grads.opacities.copy_(go)
             Vw.allreduce_gradients(grads)
-        return loss, gv, gc, go
+        return loss
 
     def barrier():
         if world > 1:
@@ -262,7 +277,7 @@ def main() -> None:
         torch.cuda.synchronize()
 
     for _ in range(max(args.warmup, 3)):
-        step()
+        step(dv, dt)
     barrier()
 
     # ---- timed region: K steps, CUDA events per step, L2 flushed between steps -----------------------
@@ -275,7 +290,7 @@ def main() -> None:
         for k in range(args.steps):
             flush.zero_()
             starts[k].record()
-            step()
+            step(dv, dt)
             stops[k].record()
         barrier()
         t_wall = time.perf_counter() - t_wall0
@@ -285,41 +300,52 @@ def main() -> None:
     if world > 1:
         dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
     ms_per_step = float(total_ms.item()) / args.steps
-    value = W * H * world / (ms_per_step * 1e-3) / 1e6
+    value = W * H * B * world / (ms_per_step * 1e-3) / 1e6
 
     # ---- end to end from host buffers through the public API -----------------------------------------
-    hv = torch.from_numpy(verts_np).pin_memory()
-    hi = torch.from_numpy(scene.indices).pin_memory()
-    hc = torch.from_numpy(scene.colors).pin_memory()
-    ho = torch.from_numpy(scene.opacities).pin_memory()
-    ht = torch.from_numpy(target_np).pin_memory()
-    out_gv = torch.empty((V, 4), dtype=torch.float32).pin_memory()
-    out_gc = torch.empty((V, 3), dtype=torch.float32).pin_memory()
-    out_go = torch.empty((V,), dtype=torch.float32).pin_memory()
+    # Every step copies all of its inputs from pinned host memory (shared mesh attributes once, per-view
+    # vertices and target for each view) and copies the loss and the summed gradients back.  The copies of
+    # view b+1 run on a second stream while view b renders.
+    hi, hc, ho = (torch.from_numpy(x).pin_memory() for x in (scene.indices, scene.colors, scene.opacities))
+    hv = [torch.from_numpy(x).pin_memory() for x in views_np]
+    ht = [torch.from_numpy(x).pin_memory() for x in targets_np]
+    out_g = torch.empty_like(grads.flat, device="cpu").pin_memory()
     out_loss = torch.empty((), dtype=torch.float32).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in (hv, hi, hc, ho, ht))
-    d2h = sum(t.numel() * t.element_size() for t in (out_gv, out_gc, out_go, out_loss))
+    h2d = sum(t.numel() * t.element_size() for t in [hi, hc, ho] + hv + ht)
+    d2h = out_g.numel() * 4 + 4
+    copy_stream = torch.cuda.Stream(device=dev)
+    main_stream = torch.cuda.current_stream(dev)
 
     def e2e_step():
-        nonlocal v, i, c, o, target
-        v = hv.to(dev, non_blocking=True)
-        i = hi.to(dev, non_blocking=True)
-        c = hc.to(dev, non_blocking=True)
-        o = ho.to(dev, non_blocking=True)
-        target = ht.to(dev, non_blocking=True)
-        loss, gv, gc, go = step()
+        nonlocal i, c, o
+        staged = []
+        with torch.cuda.stream(copy_stream):
+            i = hi.to(dev, non_blocking=True)
+            c = hc.to(dev, non_blocking=True)
+            o = ho.to(dev, non_blocking=True)
+            for b in range(B):
+                vb, tb = hv[b].to(dev, non_blocking=True), ht[b].to(dev, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(copy_stream)
+                staged.append((vb, tb, ev))
+        grads.zero_()
+        loss = None
+        for vb, tb, ev in staged:
+            main_stream.wait_event(ev)
+            vb.record_stream(main_stream)
+            tb.record_stream(main_stream)
+            l = render_view(vb, tb)
+            loss = l if loss is None else loss + l
+        for t in (i, c, o):
+            t.record_stream(main_stream)
         if world > 1:
-            gv, gc, go = grads.points, grads.colors, grads.opacities
-            out_gv[:, :3].copy_(gv, non_blocking=True)
-        else:
-            out_gv.copy_(gv, non_blocking=True)
-        out_gc.copy_(gc, non_blocking=True)
-        out_go.copy_(go, non_blocking=True)
+            Vw.allreduce_gradients(grads)
+        out_g.copy_(grads.flat, non_blocking=True)
         out_loss.copy_(loss, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        main_stream.synchronize()
 
-    e2e_steps = max(5, min(args.steps, 50))
-    for _ in range(3):
+    e2e_steps = max(3, min(args.steps, 20))
+    for _ in range(2):
         e2e_step()
     barrier()
     t0 = time.perf_counter()
@@ -329,7 +355,7 @@ def main() -> None:
     e2e_dt = torch.tensor([(time.perf_counter() - t0) / e2e_steps], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(e2e_dt, op=dist.ReduceOp.MAX)
-    e2e_value = W * H * world / float(e2e_dt.item()) / 1e6
+    e2e_value = W * H * B * world / float(e2e_dt.item()) / 1e6
 
     # ---- per-kernel timing for the roofline (stage entry points, CUDA events, L2 flushed) ------------
     stages = measure_stages(torch, St, scene, verts_np, flush, reps=max(5, min(20, args.steps)))
@@ -347,9 +373,10 @@ def main() -> None:
         "data": "synthetic",
         "config": {"workload": wname, "triangles": T, "vertices": V, "width": W, "height": H,
                    "tile": [scene.tile_width, scene.tile_height], "per_pixel_sort": True, "max_layers": 32,
-                   "views_per_gpu_per_step": 1, "K_pairs": stages["_K"], "l2": "256 MB buffer rewritten between timed steps",
-                   "exchange": "none" if world == 1 else "one NCCL all_reduce of 7V fp32 gradients per step"},
-        "triangles_per_s": T * world / (ms_per_step * 1e-3),
+                   "views_per_gpu_per_step": B, "K_pairs": stages["_K"], "l2": "256 MB buffer rewritten between timed steps",
+                   "exchange": "none" if world == 1 else "one NCCL all_reduce of 8V fp32 gradients per step"},
+        "triangles_per_s": T * B * world / (ms_per_step * 1e-3),
+        "ms_per_view": ms_per_step / B,
         "wall_s_timed_region": t_wall,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": float(e2e_dt.item()) * 1e3},

@@ -40,15 +40,16 @@ class GradBuffer:
     """One contiguous fp32 buffer holding the three gradients, with typed views into it."""
 
     flat: torch.Tensor
-    points: torch.Tensor     # (V,3) view
+    points: torch.Tensor     # (V,3) or (V,4) view
     colors: torch.Tensor     # (V,3) view
     opacities: torch.Tensor  # (V,)  view
 
     @staticmethod
-    def allocate(num_vertices: int, device) -> "GradBuffer":
-        V = num_vertices
-        flat = torch.zeros(7 * V, dtype=torch.float32, device=device)
-        return GradBuffer(flat, flat[:3 * V].view(V, 3), flat[3 * V:6 * V].view(V, 3), flat[6 * V:])
+    def allocate(num_vertices: int, device, position_components: int = 3) -> "GradBuffer":
+        """position_components = 3 for world-space positions, 4 for render-space (x, y, z, w) vertices."""
+        V, p = num_vertices, position_components
+        flat = torch.zeros((p + 4) * V, dtype=torch.float32, device=device)
+        return GradBuffer(flat, flat[:p * V].view(V, p), flat[p * V:(p + 3) * V].view(V, 3), flat[(p + 3) * V:])
 
     def zero_(self) -> None:
         self.flat.zero_()
