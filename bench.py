@@ -195,6 +195,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg3")
+    ap.add_argument("--streams", type=int, default=2,
+                    help="CUDA streams the views of a step are spread over (independent views overlap on the GPU)")
     ap.add_argument("--views-per-gpu", type=int, default=8,
                     help="views of the mesh rendered per GPU per step (a batch of views; gradients are summed)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -239,34 +241,68 @@ def main() -> None:
     dt = [torch.from_numpy(x).to(dev) for x in targets_np]
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)    # > L2 (126 MB)
     grads = Vw.GradBuffer.allocate(V, dev, position_components=4)
+    n_streams = max(1, min(args.streams, B))
+    side_streams = [torch.cuda.Stream(device=dev) for _ in range(n_streams - 1)]
+    side_grads = [Vw.GradBuffer.allocate(V, dev, position_components=4) for _ in side_streams]
 
     lib = N.lib()
     inv_n = 1.0 / float(W * H * 4)
 
-    def render_view(v, target):
-        """fwd + bwd of one view through the public API; gradients added into the all-reduce buffer."""
+    def render_view(v, target, grads=grads):
+        """fwd + bwd of one view through the public API; gradients added into the given buffer."""
         vv = v.detach().requires_grad_(True)
         cc = c.detach().requires_grad_(True)
         oo = o.detach().requires_grad_(True)
         image, _ = trigrad_b200.render(vv, i, cc, oo, W, H, scene.tile_width, scene.tile_height)
-        # mean((image - target)^2) and its gradient, written out by hand (three elementwise / reduce kernels)
+        # mean((image - target)^2) and its gradient by hand: d loss / d image = 2 (image - target) / n.  The
+        # constant factor 2/n is applied once per step to the summed gradients instead of to every image.
         g = image.detach() - target
         flat = g.view(-1)
-        loss = torch.dot(flat, flat) * inv_n
-        g.mul_(2.0 * inv_n)
+        loss = torch.dot(flat, flat)
         gv, gc, go = torch.autograd.grad(image, (vv, cc, oo), grad_outputs=g)
         grads.points.add_(gv)
         grads.colors.add_(gc)
         grads.opacities.add_(go)
         return loss
 
-    def step(vs, ts):
-        """One step: B views back to back, then (N > 1) one all-reduce of the summed gradients."""
+    def run_views(items):
+        """Render (vertices, target, ready_event) items, spread round-robin over the streams; returns the summed loss.
+
+        Views are independent, so view b+1's binning and sorting (small, latency-bound kernels) overlap with
+        view b's compositing on another stream.  Each stream sums into its own gradient buffer.
+        """
+        main = torch.cuda.current_stream(dev)
         grads.zero_()
-        loss = None
-        for v, t in zip(vs, ts):
-            l = render_view(v, t)
-            loss = l if loss is None else loss + l
+        losses = []
+        start = torch.cuda.Event()
+        start.record(main)
+        for si, (st, gb) in enumerate(zip(side_streams, side_grads)):
+            st.wait_event(start)
+            with torch.cuda.stream(st):
+                gb.zero_()
+        for b, (v, t, ready) in enumerate(items):
+            si = b % n_streams
+            stream = main if si == 0 else side_streams[si - 1]
+            with torch.cuda.stream(stream):
+                if ready is not None:
+                    stream.wait_event(ready)
+                    v.record_stream(stream)
+                    t.record_stream(stream)
+                losses.append(render_view(v, t, grads if si == 0 else side_grads[si - 1]))
+        for st, gb in zip(side_streams, side_grads):
+            done = torch.cuda.Event()
+            done.record(st)
+            main.wait_event(done)
+            grads.flat.add_(gb.flat)
+        loss = losses[0]
+        for l in losses[1:]:
+            loss = loss + l
+        grads.flat.mul_(2.0 * inv_n)
+        return loss * inv_n
+
+    def step(vs, ts):
+        """One step: B views, then (N > 1) one all-reduce of the summed gradients."""
+        loss = run_views([(v, t, None) for v, t in zip(vs, ts)])
         if world > 1:
             Vw.allreduce_gradients(grads)
         return loss
@@ -328,16 +364,11 @@ def main() -> None:
                 ev = torch.cuda.Event()
                 ev.record(copy_stream)
                 staged.append((vb, tb, ev))
-        grads.zero_()
-        loss = None
-        for vb, tb, ev in staged:
-            main_stream.wait_event(ev)
-            vb.record_stream(main_stream)
-            tb.record_stream(main_stream)
-            l = render_view(vb, tb)
-            loss = l if loss is None else loss + l
+        loss = run_views(staged)        # each view waits for its own copies (queued after the shared ones)
         for t in (i, c, o):
             t.record_stream(main_stream)
+            for st in side_streams:
+                t.record_stream(st)
         if world > 1:
             Vw.allreduce_gradients(grads)
         out_g.copy_(grads.flat, non_blocking=True)
@@ -373,7 +404,7 @@ def main() -> None:
         "data": "synthetic",
         "config": {"workload": wname, "triangles": T, "vertices": V, "width": W, "height": H,
                    "tile": [scene.tile_width, scene.tile_height], "per_pixel_sort": True, "max_layers": 32,
-                   "views_per_gpu_per_step": B, "K_pairs": stages["_K"], "l2": "256 MB buffer rewritten between timed steps",
+                   "views_per_gpu_per_step": B, "streams": n_streams, "K_pairs": stages["_K"], "l2": "256 MB buffer rewritten between timed steps",
                    "exchange": "none" if world == 1 else "one NCCL all_reduce of 8V fp32 gradients per step"},
         "triangles_per_s": T * B * world / (ms_per_step * 1e-3),
         "ms_per_view": ms_per_step / B,

@@ -61,6 +61,10 @@ def test_scratch_size_queries():
     assert lib.tg_scan_scratch_bytes(0) >= 8
     assert lib.tg_scan_scratch_bytes(10_000_000) > lib.tg_scan_scratch_bytes(1000)
     assert lib.tg_sort_scratch_bytes(1 << 20) > lib.tg_sort_scratch_bytes(1)
+    assert lib.tg_backward_scratch_bytes(1000) >= 32 * 1000
+    # saved per-pixel selection: only in per-pixel mode with at most one batch of 32 layers
+    assert lib.tg_selection_planes(1, 32) == 32 and lib.tg_selection_planes(1, 7) == 7
+    assert lib.tg_selection_planes(1, 33) == 0 and lib.tg_selection_planes(0, 32) == 0
     a = lib.tg_forward_workspace_bytes(1000, 64, 5000)
     b = lib.tg_forward_workspace_bytes(1000, 64, 50000)
     assert b > a > 0

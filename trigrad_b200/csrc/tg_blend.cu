@@ -106,10 +106,16 @@ struct TileCtx {
     WarpRect rect;
 };
 
-__device__ __forceinline__ TileCtx tile_context(const BlendParams& P) {
+// Pixel-centre coordinates need double arithmetic (one rounding, reference render.cu:561-562); the
+// tile_w + tile_h distinct values of a tile are computed once by its first threads and shared.
+constexpr int kMaxTileCoords = 1026;
+
+__device__ __forceinline__ TileCtx tile_context(const BlendParams& P, float* s_coord) {
     TileCtx c;
     c.tile = blockIdx.x;
     const int tx = c.tile % P.tiles_x, ty = c.tile / P.tiles_x;
+    for (int i = threadIdx.x; i < P.tw + P.th; i += blockDim.x)
+        s_coord[i] = (i < P.tw) ? pixel_coord(tx * P.tw + i, P.W) : pixel_coord(ty * P.th + (i - P.tw), P.H);
     int lx, ly;
     if ((P.tw & 7) == 0 && (P.th & 3) == 0) {
         // a warp owns an 8x4 block of the tile: compact footprint, fewer records survive its cull
@@ -125,8 +131,9 @@ __device__ __forceinline__ TileCtx tile_context(const BlendParams& P) {
     c.active = (int)threadIdx.x < P.tw * P.th && c.ix < P.W && c.iy < P.H;
     c.start = P.offsets[c.tile];
     c.end = P.offsets[c.tile + 1];
-    c.px = pixel_coord(c.ix, P.W);
-    c.py = pixel_coord(c.iy, P.H);
+    __syncthreads();
+    c.px = s_coord[min(lx, P.tw - 1)];
+    c.py = s_coord[P.tw + min(ly, P.th - 1)];
     float x0 = c.active ? c.px : INFINITY, x1 = c.active ? c.px : -INFINITY;
     float y0 = c.active ? c.py : INFINITY, y1 = c.active ? c.py : -INFINITY;
 #pragma unroll
@@ -234,7 +241,8 @@ __global__ void __launch_bounds__(MAXT) blend_forward_kernel(BlendParams P, floa
                                                              int* __restrict__ ends, int* __restrict__ sel) {
     __shared__ float4 s_geo[kChunk * 4];
     __shared__ int s_id[kChunk];
-    const TileCtx c = tile_context(P);
+    __shared__ float s_coord[kMaxTileCoords];
+    const TileCtx c = tile_context(P, s_coord);
     PixelAcc acc;
 
     if (SORT) {
@@ -457,7 +465,8 @@ template <int MAXT>
 __global__ void __launch_bounds__(MAXT) blend_backward_saved_kernel(BlendParams P, BackwardIn in,
                                                                     const int* __restrict__ sel,
                                                                     float4* __restrict__ gpack) {
-    const TileCtx c = tile_context(P);
+    __shared__ float s_coord[kMaxTileCoords];
+    const TileCtx c = tile_context(P, s_coord);
     PixelGrad pg;
     BackState st;
     const int n = load_pixel_state(c, P, in, pg, st);
@@ -512,7 +521,8 @@ template <bool SORT, int MAXT>
 __global__ void __launch_bounds__(MAXT) blend_backward_kernel(BlendParams P, BackwardIn in, float4* __restrict__ gpack) {
     __shared__ float4 s_geo[kChunk * 4];
     __shared__ int s_id[kChunk];
-    const TileCtx c = tile_context(P);
+    __shared__ float s_coord[kMaxTileCoords];
+    const TileCtx c = tile_context(P, s_coord);
     PixelGrad pg;
     BackState st;
     const int limit = load_pixel_state(c, P, in, pg, st);
