@@ -18,7 +18,8 @@ constexpr size_t kHistBytes = (size_t)kMaxPasses * kRadix * sizeof(uint32_t);
 constexpr size_t kCtrBytes = 64;
 constexpr int kHistDoneWord = 8;
 
-// Exclusive scan of one value per thread over a CTA of 256 threads.
+// Exclusive scan of one value per thread over the first 256 threads of a CTA (all threads of the CTA
+// must call it; threads beyond 256 pass 0 and ignore the result).
 __device__ __forceinline__ uint32_t block_exclusive_scan_256(uint32_t v, uint32_t* s_warp_tot /*[8]*/) {
     uint32_t incl = v;
 #pragma unroll
@@ -28,7 +29,7 @@ __device__ __forceinline__ uint32_t block_exclusive_scan_256(uint32_t v, uint32_
     }
     const int warp = threadIdx.x >> 5;
     __syncthreads();   // protect s_warp_tot from a previous use
-    if (lane_id() == 31) s_warp_tot[warp] = incl;
+    if (lane_id() == 31 && warp < kSortWarps) s_warp_tot[warp] = incl;
     __syncthreads();
     uint32_t off = 0;
 #pragma unroll

@@ -1,22 +1,39 @@
 // Stage 4: onesweep least-significant-digit radix sort of (uint64 key, uint32 value) pairs.
 //
-// One histogram kernel counts every 8-bit digit of every pass in a single read of the keys and
-// turns the counts into global digit offsets.  Then one kernel per pass: each CTA takes a tile of
-// kSortTile pairs (ticket order), ranks them stably by the pass digit (warp match-any ranking),
-// publishes its per-digit counts, obtains the counts of all earlier tiles by decoupled look-back
-// (one thread per digit, bounded waits) and scatters keys and values through shared memory so
-// that global writes are contiguous runs per digit.  Every pass reads 12 B and writes 12 B per
-// pair: HBM-bound.
+// The digits of every pass are counted in a single read of the keys (here, or on the fly by the
+// key-emission kernel) and turned into global digit offsets.  Then one kernel per pass: each CTA
+// takes a tile of pairs (ticket order), ranks them stably by the pass digit (per-warp ballots, one
+// per digit bit), publishes its per-digit counts, obtains the counts of all earlier tiles by
+// decoupled look-back (one thread per digit, bounded waits) and scatters keys and values through
+// shared memory so that global writes are contiguous runs per digit.  Every pass reads 12 B and
+// writes 12 B per pair: HBM-bound.
 #include "tg_radix.cuh"
+
+#ifndef TG_SORT_THREADS
+#define TG_SORT_THREADS 256
+#endif
+#ifndef TG_SORT_ITEMS
+#define TG_SORT_ITEMS 16
+#endif
+#ifndef TG_SORT_MIN_CTAS
+#define TG_SORT_MIN_CTAS 3
+#endif
 
 namespace tg {
 
-// Pairs per thread: 16 (4096-pair tiles) amortises the per-tile histogram work.
-constexpr int kSortItems = 16;
-constexpr int kSortTile = kSortThreads * kSortItems;
+// Tile shape of a pass.  Measured on a B200 at 2^27 pairs (GB/s of algorithmic traffic): 256 threads x 16
+// pairs 2551, 512x12 2396, 512x8 2254, 256x8 2014, 512x6 2069, 1024x4 1608 - more pairs per thread (fewer,
+// larger tiles: less look-back and per-tile overhead) beats more resident warps.
+constexpr int kPassThreads = TG_SORT_THREADS;
+constexpr int kPassWarps = kPassThreads / 32;
+constexpr int kPassItems = TG_SORT_ITEMS;
+constexpr int kSortTile = kPassThreads * kPassItems;
 constexpr uint32_t kSortSpinLimit = 1u << 22;
 constexpr uint64_t kFlagAggregate = 1ull << 32;
 constexpr uint64_t kFlagInclusive = 2ull << 32;
+static_assert(kPassThreads >= kRadix && kPassThreads % 32 == 0, "one thread per digit is needed");
+static_assert(32 * kPassItems <= 65535, "per-warp digit counters are 16 bit");
+
 __global__ void __launch_bounds__(kSortThreads) sort_histogram_kernel(const uint64_t* __restrict__ keys, uint32_t n,
                                                                       HistArgs h) {
     __shared__ uint32_t s_hist[kMaxPasses * kRadix];
@@ -36,15 +53,15 @@ __device__ __forceinline__ void st_word(uint64_t* p, uint64_t v) { *(volatile ui
 struct SortSmem {
     uint64_t keys[kSortTile];
     uint32_t vals[kSortTile];
-    uint32_t warp_hist[kSortWarps][kRadix];
+    uint16_t warp_hist[kPassWarps][kRadix];   // per-warp digit counts, then offsets of the warp inside the digit
     uint32_t digit_start[kRadix];
     uint32_t bin_offset[kRadix];
-    uint32_t warp_tot[kSortWarps];
+    uint32_t warp_tot[8];
     uint32_t part;
     uint32_t fail;
 };
 
-__global__ void __launch_bounds__(kSortThreads) onesweep_pass_kernel(
+__global__ void __launch_bounds__(kPassThreads, TG_SORT_MIN_CTAS) onesweep_pass_kernel(
     const uint64_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in, uint64_t* __restrict__ keys_out,
     uint32_t* __restrict__ vals_out, uint32_t n, int shift, int bits, const uint32_t* __restrict__ digit_offsets,
     uint32_t* __restrict__ ticket, uint64_t* __restrict__ lookback /*[parts][256]*/, uint32_t* __restrict__ status) {
@@ -55,20 +72,20 @@ __global__ void __launch_bounds__(kSortThreads) onesweep_pass_kernel(
     const uint32_t digit_mask = (1u << bits) - 1u;
 
     if (tid == 0) { sm.part = atomicAdd(ticket, 1u); sm.fail = 0; }
-    for (int i = tid; i < kSortWarps * kRadix; i += kSortThreads) (&sm.warp_hist[0][0])[i] = 0;
+    for (int i = tid; i < kPassWarps * kRadix / 2; i += kPassThreads) reinterpret_cast<uint32_t*>(&sm.warp_hist[0][0])[i] = 0;
     __syncthreads();
     const uint32_t p = sm.part;
     const uint64_t tile_base = (uint64_t)p * kSortTile;
     if (tile_base >= n) return;
     const uint32_t valid = (uint32_t)min((uint64_t)kSortTile, (uint64_t)n - tile_base);
 
-    // warp-striped load: warp w owns [w*512, (w+1)*512), lane l takes items i*32 + l
-    uint64_t key[kSortItems];
-    uint32_t val[kSortItems];
-    uint16_t rank[kSortItems];
-    const uint32_t warp_base = warp * (32 * kSortItems);
+    // warp-striped load: warp w owns a contiguous run of 32*kPassItems pairs, lane l takes items i*32 + l
+    uint64_t key[kPassItems];
+    uint32_t val[kPassItems];
+    uint16_t rank[kPassItems];
+    const uint32_t warp_base = warp * (32 * kPassItems);
 #pragma unroll
-    for (int i = 0; i < kSortItems; i++) {
+    for (int i = 0; i < kPassItems; i++) {
         const uint32_t idx = warp_base + i * 32 + lane;
         if (idx < valid) {
             key[i] = keys_in[tile_base + idx];
@@ -78,19 +95,27 @@ __global__ void __launch_bounds__(kSortThreads) onesweep_pass_kernel(
             val[i] = 0;
         }
     }
-    // stable ranking inside the warp, digit by digit group
+    // Stable ranking inside the warp.  The lanes holding the same digit are found with one ballot per
+    // digit bit (match.any costs several times more on this part when the digits of a warp are mostly
+    // distinct).  Slots past the end of the input take the largest digit: they sit at the end of the last
+    // tile, so they rank behind every real key and only inflate a count nobody reads.
     const unsigned lt_mask = (1u << lane) - 1u;
 #pragma unroll
-    for (int i = 0; i < kSortItems; i++) {
+    for (int i = 0; i < kPassItems; i++) {
         const uint32_t idx = warp_base + i * 32 + lane;
         const bool ok = idx < valid;
-        const uint32_t d = ok ? ((uint32_t)(key[i] >> shift) & digit_mask) : (uint32_t)kRadix;
-        const unsigned peers = __match_any_sync(0xffffffffu, d);
+        const uint32_t d = ok ? ((uint32_t)(key[i] >> shift) & digit_mask) : digit_mask;
+        unsigned peers = 0xffffffffu;
+        for (int b = 0; b < bits; b++) {
+            const bool bit = (d >> b) & 1u;
+            const unsigned v = __ballot_sync(0xffffffffu, bit);
+            peers &= bit ? v : ~v;
+        }
         const int leader = __ffs(peers) - 1;
         uint32_t old = 0;
-        if ((int)lane == leader && ok) {
+        if ((int)lane == leader) {
             old = sm.warp_hist[warp][d];
-            sm.warp_hist[warp][d] = old + __popc(peers);
+            sm.warp_hist[warp][d] = (uint16_t)(old + __popc(peers));
         }
         old = __shfl_sync(0xffffffffu, old, leader);
         rank[i] = (uint16_t)(old + __popc(peers & lt_mask));
@@ -98,20 +123,20 @@ __global__ void __launch_bounds__(kSortThreads) onesweep_pass_kernel(
     }
     __syncthreads();
 
-    // per digit (thread d): offsets of each warp inside the digit, CTA count, CTA start, look-back
+    // per digit (thread d < 256): offsets of each warp inside the digit, CTA count, CTA start, look-back
     uint32_t cta_count = 0;
-    {
+    if (tid < kRadix) {
         uint32_t run = 0;
 #pragma unroll
-        for (int w = 0; w < kSortWarps; w++) {
+        for (int w = 0; w < kPassWarps; w++) {
             const uint32_t c = sm.warp_hist[w][tid];
-            sm.warp_hist[w][tid] = run;
+            sm.warp_hist[w][tid] = (uint16_t)run;
             run += c;
         }
         cta_count = run;
     }
-    const uint32_t dstart = block_exclusive_scan_256(cta_count, sm.warp_tot);
-    {
+    const uint32_t dstart = block_exclusive_scan_256(cta_count, sm.warp_tot);   // threads >= 256 contribute 0
+    if (tid < kRadix) {
         uint64_t* mine = lookback + (size_t)p * kRadix + tid;
         uint32_t excl = 0;
         bool failed = false;
@@ -143,7 +168,7 @@ __global__ void __launch_bounds__(kSortThreads) onesweep_pass_kernel(
 
     // scatter into CTA-sorted order in shared memory
 #pragma unroll
-    for (int i = 0; i < kSortItems; i++) {
+    for (int i = 0; i < kPassItems; i++) {
         const uint32_t idx = warp_base + i * 32 + lane;
         if (idx < valid) {
             const uint32_t d = (uint32_t)(key[i] >> shift) & digit_mask;
@@ -154,7 +179,7 @@ __global__ void __launch_bounds__(kSortThreads) onesweep_pass_kernel(
     }
     __syncthreads();
     // coalesced runs out to global memory
-    for (uint32_t k = tid; k < valid; k += kSortThreads) {
+    for (uint32_t k = tid; k < valid; k += kPassThreads) {
         const uint64_t kk = sm.keys[k];
         const uint32_t d = (uint32_t)(kk >> shift) & digit_mask;
         const uint32_t dst = sm.bin_offset[d] + k;
@@ -220,7 +245,7 @@ int sort_pairs(uint64_t* keys_a, uint64_t* keys_b, uint32_t* vals_a, uint32_t* v
         const int shift = begin_bit + p * tg::kRadixBits;
         const int bits = (end_bit - shift < tg::kRadixBits) ? (end_bit - shift) : tg::kRadixBits;
         uint64_t* lb = lookback + (size_t)p * parts * tg::kRadix;
-        tg::onesweep_pass_kernel<<<(unsigned)parts, tg::kSortThreads, sizeof(tg::SortSmem), s>>>(
+        tg::onesweep_pass_kernel<<<(unsigned)parts, tg::kPassThreads, sizeof(tg::SortSmem), s>>>(
             kin, vin, kout, vout, n, shift, bits, hist + p * tg::kRadix, ctr + p, lb, status);
         TG_LAUNCH_CHECK("onesweep_pass_kernel");
         uint64_t* tk = kin; kin = kout; kout = tk;
