@@ -52,6 +52,9 @@ SCENES = {
     "edge": edge_case_scene,
     "odd_tiles": lambda: S.random_triangles(3000, 333, 217, 0.05, 0.6, name="odd"),
 }
+# depth complexity far above 32 in the centre: exercises the full-batch depth cut of the selection sweep
+SCENES["deep_overlap"] = lambda: S.random_triangles(12_000, 256, 160, 0.08, 0.5, centroid="gauss", centroid_sigma=0.2,
+                                                    name="deep_overlap")
 SCENES["odd_tiles_5x7"] = lambda: (lambda s: (setattr(s, "tile_width", 5), setattr(s, "tile_height", 7), s)[2])(
     S.random_triangles(3000, 333, 217, 0.05, 0.6, name="odd57"))
 SCENES["big_tile_32x32"] = lambda: (lambda s: (setattr(s, "tile_width", 32), setattr(s, "tile_height", 32), s)[2])(

@@ -171,11 +171,21 @@ __device__ __forceinline__ void stage_chunk(const BlendParams& P, int first, int
     }
 }
 
-// Bit mask (64 records) of the staged records that may cover a pixel of this warp.
-__device__ __forceinline__ unsigned long long warp_cull(const float4* s_geo, int n, const WarpRect& R) {
+// Bit mask (64 records) of the staged records that may matter to this warp: the triangle may cover one
+// of its pixels (corner test) and, when `depth_cut` is finite, its depth lower bound is below the cut
+// (every lane already holds a full batch of nearer fragments otherwise).
+__device__ __forceinline__ unsigned long long warp_cull(const float4* s_geo, int n, const WarpRect& R,
+                                                        float depth_cut = INFINITY) {
     const int lane = lane_id();
-    const bool k0 = lane < n && rect_may_cover(reinterpret_cast<const float*>(s_geo + 4 * lane), R);
-    const bool k1 = lane + 32 < n && rect_may_cover(reinterpret_cast<const float*>(s_geo + 4 * (lane + 32)), R);
+    bool k0 = false, k1 = false;
+    if (lane < n) {
+        const float* g = reinterpret_cast<const float*>(s_geo + 4 * lane);
+        k0 = g[15] < depth_cut && rect_may_cover(g, R);
+    }
+    if (lane + 32 < n) {
+        const float* g = reinterpret_cast<const float*>(s_geo + 4 * (lane + 32));
+        k1 = g[15] < depth_cut && rect_may_cover(g, R);
+    }
     const unsigned m0 = __ballot_sync(0xffffffffu, k0), m1 = __ballot_sync(0xffffffffu, k1);
     return (unsigned long long)m0 | ((unsigned long long)m1 << 32);
 }
@@ -193,7 +203,12 @@ __device__ __forceinline__ int select_sweep(const BlendParams& P, const TileCtx&
         stage_chunk(P, first, n, s_geo, s_id);
         __syncthreads();
         if (!warp_go) continue;
-        unsigned long long mask = warp_cull(s_geo, n, c.rect);
+        // Once every collecting lane of the warp holds a full batch, a record whose depth lower bound is
+        // not below the farthest kept depth of any lane cannot enter any lane's batch (ties lose).
+        float cut = go ? ((found == bs) ? dl[bs - 1] : INFINITY) : -INFINITY;
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) cut = fmaxf(cut, __shfl_xor_sync(0xffffffffu, cut, d));
+        unsigned long long mask = warp_cull(s_geo, n, c.rect, cut);
         while (mask) {
             const int r = __ffsll((long long)mask) - 1;
             mask &= mask - 1;
