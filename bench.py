@@ -48,7 +48,19 @@ def make_scene(name: str):
         return S.config1_icosphere(), "cfg1_icosphere1280_256x256"
     if name == "cfg5":
         return S.config5_overlap(), "cfg5_overlap2M_3840x2160"
+    if name == "cfg4":
+        mesh = S.displaced_sphere(8)
+        pvs = S.camera_ring(64)
+        sc = S.config4_view(mesh, pvs[0], name="cfg4_sphere1M_view0")
+        sc.meta["mesh"], sc.meta["pvs"] = mesh, pvs
+        return sc, "cfg4_displaced_sphere_1.3M_tris_64_cameras_1920x1080"
     raise SystemExit(f"unknown workload {name}")
+
+
+def S_project(scene, pv: np.ndarray) -> np.ndarray:
+    from trigrad_b200 import scenes as S
+
+    return S.project_numpy(scene.meta["mesh"].points, pv)
 
 
 def view_vertices(vertices: np.ndarray, k: int) -> np.ndarray:
@@ -228,11 +240,20 @@ def main() -> None:
     W, H = scene.width, scene.height
     T, V = scene.num_triangles, scene.num_vertices
     B = max(1, args.views_per_gpu)
-    # rank r renders views [r*B, (r+1)*B) of the same mesh; every view has its own target image
-    views_np = [view_vertices(scene.vertices, rank * B + b) for b in range(B)]
+    # rank r renders views [r*B, (r+1)*B) of the same mesh; every view has its own target image.
+    # Random-triangle scenes: a view is the NDC vertex array rotated in the image plane.  Camera-ring scene
+    # (cfg4): a view is a 4x4 projection*view matrix and the world -> NDC projection runs in torch (outside
+    # the hot path, as in the reference viewer), so the gradients are world-space.
+    camera_ring = "mesh" in scene.meta
+    if camera_ring:
+        views_np = [scene.meta["pvs"][(rank * B + b) % 64] for b in range(B)]
+        points = torch.from_numpy(scene.meta["mesh"].points).to(dev)
+    else:
+        views_np = [view_vertices(scene.vertices, rank * B + b) for b in range(B)]
+        points = None
     rng = np.random.default_rng(3 + rank)
     targets_np = [scene.target() if b == 0 else rng.random((H, W, 4), dtype=np.float32) for b in range(B)]
-    verts_np = views_np[0]
+    verts_np = S_project(scene, views_np[0]) if camera_ring else views_np[0]
 
     i = torch.from_numpy(scene.indices).to(dev)
     c = torch.from_numpy(scene.colors).to(dev)
@@ -240,20 +261,26 @@ def main() -> None:
     dv = [torch.from_numpy(x).to(dev) for x in views_np]
     dt = [torch.from_numpy(x).to(dev) for x in targets_np]
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)    # > L2 (126 MB)
-    grads = Vw.GradBuffer.allocate(V, dev, position_components=4)
+    pos_comp = 3 if camera_ring else 4
+    grads = Vw.GradBuffer.allocate(V, dev, position_components=pos_comp)
     n_streams = max(1, min(args.streams, B))
     side_streams = [torch.cuda.Stream(device=dev) for _ in range(n_streams - 1)]
-    side_grads = [Vw.GradBuffer.allocate(V, dev, position_components=4) for _ in side_streams]
+    side_grads = [Vw.GradBuffer.allocate(V, dev, position_components=pos_comp) for _ in side_streams]
 
     lib = N.lib()
     inv_n = 1.0 / float(W * H * 4)
 
     def render_view(v, target, grads=grads):
         """fwd + bwd of one view through the public API; gradients added into the given buffer."""
-        vv = v.detach().requires_grad_(True)
         cc = c.detach().requires_grad_(True)
         oo = o.detach().requires_grad_(True)
-        image, _ = trigrad_b200.render(vv, i, cc, oo, W, H, scene.tile_width, scene.tile_height)
+        if camera_ring:
+            vv = points.detach().requires_grad_(True)
+            verts = Vw.project(vv, v)
+        else:
+            vv = v.detach().requires_grad_(True)
+            verts = vv
+        image, _ = trigrad_b200.render(verts, i, cc, oo, W, H, scene.tile_width, scene.tile_height)
         # mean((image - target)^2) and its gradient by hand: d loss / d image = 2 (image - target) / n.  The
         # constant factor 2/n is applied once per step to the summed gradients instead of to every image.
         g = image.detach() - target
@@ -343,19 +370,22 @@ def main() -> None:
     # vertices and target for each view) and copies the loss and the summed gradients back.  The copies of
     # view b+1 run on a second stream while view b renders.
     hi, hc, ho = (torch.from_numpy(x).pin_memory() for x in (scene.indices, scene.colors, scene.opacities))
+    hp = torch.from_numpy(scene.meta["mesh"].points).pin_memory() if camera_ring else None
     hv = [torch.from_numpy(x).pin_memory() for x in views_np]
     ht = [torch.from_numpy(x).pin_memory() for x in targets_np]
     out_g = torch.empty_like(grads.flat, device="cpu").pin_memory()
     out_loss = torch.empty((), dtype=torch.float32).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in [hi, hc, ho] + hv + ht)
+    h2d = sum(t.numel() * t.element_size() for t in [hi, hc, ho] + hv + ht + ([hp] if camera_ring else []))
     d2h = out_g.numel() * 4 + 4
     copy_stream = torch.cuda.Stream(device=dev)
     main_stream = torch.cuda.current_stream(dev)
 
     def e2e_step():
-        nonlocal i, c, o
+        nonlocal i, c, o, points
         staged = []
         with torch.cuda.stream(copy_stream):
+            if camera_ring:
+                points = hp.to(dev, non_blocking=True)
             i = hi.to(dev, non_blocking=True)
             c = hc.to(dev, non_blocking=True)
             o = ho.to(dev, non_blocking=True)
@@ -365,7 +395,7 @@ def main() -> None:
                 ev.record(copy_stream)
                 staged.append((vb, tb, ev))
         loss = run_views(staged)        # each view waits for its own copies (queued after the shared ones)
-        for t in (i, c, o):
+        for t in (i, c, o) + ((points,) if camera_ring else ()):
             t.record_stream(main_stream)
             for st in side_streams:
                 t.record_stream(st)
@@ -405,7 +435,7 @@ def main() -> None:
         "config": {"workload": wname, "triangles": T, "vertices": V, "width": W, "height": H,
                    "tile": [scene.tile_width, scene.tile_height], "per_pixel_sort": True, "max_layers": 32,
                    "views_per_gpu_per_step": B, "streams": n_streams, "K_pairs": stages["_K"], "l2": "256 MB buffer rewritten between timed steps",
-                   "exchange": "none" if world == 1 else "one NCCL all_reduce of 8V fp32 gradients per step"},
+                   "exchange": "none" if world == 1 else f"one NCCL all_reduce of {pos_comp + 4}V fp32 gradients per step"},
         "triangles_per_s": T * B * world / (ms_per_step * 1e-3),
         "ms_per_view": ms_per_step / B,
         "wall_s_timed_region": t_wall,
