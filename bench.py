@@ -271,36 +271,34 @@ def main() -> None:
     inv_n = 1.0 / float(W * H * 4)
 
     def render_view(v, target, grads=grads):
-        """fwd + bwd of one view through the public API; gradients added into the given buffer."""
-        cc = c.detach().requires_grad_(True)
-        oo = o.detach().requires_grad_(True)
+        """fwd + bwd of one view; gradients and loss are added into the given buffer.
+
+        Random-triangle scenes go through ``views.l2_view_step`` (forward, then the backward with the
+        mean-squared-error gradient formed inside the kernel).  The camera-ring scene adds the world -> NDC
+        projection and its VJP in torch around the same two calls.
+        """
         if camera_ring:
-            vv = points.detach().requires_grad_(True)
-            verts = Vw.project(vv, v)
+            p = points.detach().requires_grad_(True)
+            verts = Vw.project(p, v)
+            gverts = torch.zeros_like(verts)
+            Vw.l2_view_step(verts.detach(), i, c, o, target, W, H, gverts, grads.colors, grads.opacities, grads.loss,
+                            scene.tile_width, scene.tile_height)
+            (gp,) = torch.autograd.grad(verts, p, grad_outputs=gverts)
+            grads.points.add_(gp)
         else:
-            vv = v.detach().requires_grad_(True)
-            verts = vv
-        image, _ = trigrad_b200.render(verts, i, cc, oo, W, H, scene.tile_width, scene.tile_height)
-        # mean((image - target)^2) and its gradient by hand: d loss / d image = 2 (image - target) / n.  The
-        # constant factor 2/n is applied once per step to the summed gradients instead of to every image.
-        g = image.detach() - target
-        flat = g.view(-1)
-        loss = torch.dot(flat, flat)
-        gv, gc, go = torch.autograd.grad(image, (vv, cc, oo), grad_outputs=g)
-        grads.points.add_(gv)
-        grads.colors.add_(gc)
-        grads.opacities.add_(go)
-        return loss
+            Vw.l2_view_step(v, i, c, o, target, W, H, grads.points, grads.colors, grads.opacities, grads.loss,
+                            scene.tile_width, scene.tile_height)
+        return None
 
     def run_views(items):
-        """Render (vertices, target, ready_event) items, spread round-robin over the streams; returns the summed loss.
+        """Render (vertices, target, ready_event) items, spread round-robin over the streams; returns the summed loss
+        (a view into the gradient buffer).
 
         Views are independent, so view b+1's binning and sorting (small, latency-bound kernels) overlap with
         view b's compositing on another stream.  Each stream sums into its own gradient buffer.
         """
         main = torch.cuda.current_stream(dev)
         grads.zero_()
-        losses = []
         start = torch.cuda.Event()
         start.record(main)
         for si, (st, gb) in enumerate(zip(side_streams, side_grads)):
@@ -315,17 +313,13 @@ def main() -> None:
                     stream.wait_event(ready)
                     v.record_stream(stream)
                     t.record_stream(stream)
-                losses.append(render_view(v, t, grads if si == 0 else side_grads[si - 1]))
+                render_view(v, t, grads if si == 0 else side_grads[si - 1])
         for st, gb in zip(side_streams, side_grads):
             done = torch.cuda.Event()
             done.record(st)
             main.wait_event(done)
             grads.flat.add_(gb.flat)
-        loss = losses[0]
-        for l in losses[1:]:
-            loss = loss + l
-        grads.flat.mul_(2.0 * inv_n)
-        return loss * inv_n
+        return grads.loss
 
     def step(vs, ts):
         """One step: B views, then (N > 1) one all-reduce of the summed gradients."""
@@ -373,10 +367,9 @@ def main() -> None:
     hp = torch.from_numpy(scene.meta["mesh"].points).pin_memory() if camera_ring else None
     hv = [torch.from_numpy(x).pin_memory() for x in views_np]
     ht = [torch.from_numpy(x).pin_memory() for x in targets_np]
-    out_g = torch.empty_like(grads.flat, device="cpu").pin_memory()
-    out_loss = torch.empty((), dtype=torch.float32).pin_memory()
+    out_g = torch.empty_like(grads.flat, device="cpu").pin_memory()      # gradients and, last element, the loss
     h2d = sum(t.numel() * t.element_size() for t in [hi, hc, ho] + hv + ht + ([hp] if camera_ring else []))
-    d2h = out_g.numel() * 4 + 4
+    d2h = out_g.numel() * 4
     copy_stream = torch.cuda.Stream(device=dev)
     main_stream = torch.cuda.current_stream(dev)
 
@@ -402,7 +395,6 @@ def main() -> None:
         if world > 1:
             Vw.allreduce_gradients(grads)
         out_g.copy_(grads.flat, non_blocking=True)
-        out_loss.copy_(loss, non_blocking=True)
         main_stream.synchronize()
 
     e2e_steps = max(3, min(args.steps, 20))

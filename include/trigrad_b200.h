@@ -139,6 +139,21 @@ int tg_blend_backward(const float* tri_geo, const float* tri_attr, const int32_t
                       float* grad_colors, float* grad_opacities, int accumulate, void* scratch, size_t scratch_bytes,
                       tg_stream_t stream);
 
+/* Backward of the mean-squared-error loss  loss = loss_scale * sum((image - target)^2)  fused into stage 7:
+ * the upstream gradient grad_scale * (image - target) is formed per pixel inside the kernel (depth-map
+ * gradient zero), so no gradient image is written or read, and the loss value is reduced on the way.
+ * For mean(): loss_scale = 1/(4 W H), grad_scale = 2/(4 W H).  *loss_out (device) is overwritten, or added
+ * to when accumulate != 0.  Needs the selection saved by the forward pass (default mode); otherwise form
+ * the gradient image yourself and call tg_blend_backward.  The reference has no counterpart: its users
+ * write the loss in torch (notebooks/renderer.ipynb:529-548).
+ */
+int tg_blend_backward_l2(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids, const int32_t* offsets,
+                         int V, int W, int H, int tile_w, int tile_h, int per_pixel_sort, int max_layers,
+                         const float* target, float grad_scale, float loss_scale, float* loss_out, const float* image,
+                         const float* depthmap, const float* final_weights, const int32_t* ends, const int32_t* selection,
+                         float* grad_vertices, float* grad_colors, float* grad_opacities, int accumulate, void* scratch,
+                         size_t scratch_bytes, tg_stream_t stream);
+
 /* ---- whole forward path -------------------------------------------------------------------------
  * Replaces render_forward (src/trigrad/render.cu:713-763).  Runs stages 1-6 on `stream`.
  *   selection    as for tg_blend_forward (may be NULL)

@@ -142,6 +142,38 @@ def test_non_contiguous_inputs():
     assert torch.equal(a, b)
 
 
+def test_fused_l2_view_step_matches_autograd():
+    """views.l2_view_step (forward + loss-fused backward, accumulating) against render() + torch autograd."""
+    from trigrad_b200 import views
+    sc = S.config2_random10k()
+    V = sc.num_vertices
+    gV = torch.zeros((V, 4), device="cuda")
+    gC = torch.zeros((V, 3), device="cuda")
+    gO = torch.zeros((V,), device="cuda")
+    loss = torch.zeros((), device="cuda")
+    refs = [torch.zeros_like(gV), torch.zeros_like(gC), torch.zeros_like(gO)]
+    ref_loss = 0.0
+    rng = np.random.default_rng(17)
+    for k in range(2):                                     # two views: accumulation across calls
+        verts = sc.vertices.copy()
+        verts[:, 0] += 0.01 * k
+        target = Hh.cuda(rng.random((sc.height, sc.width, 4), dtype=np.float32))
+        v, i, c, o = Hh.cuda(verts), Hh.cuda(sc.indices), Hh.cuda(sc.colors), Hh.cuda(sc.opacities)
+        img = views.l2_view_step(v, i, c, o, target, sc.width, sc.height, gV, gC, gO, loss)
+        vv, cc, oo = v.clone().requires_grad_(), c.clone().requires_grad_(), o.clone().requires_grad_()
+        image, _ = trigrad_b200.render(vv, i, cc, oo, sc.width, sc.height)
+        assert torch.equal(image, img)
+        l = torch.mean((image - target) ** 2)
+        g = torch.autograd.grad(l, (vv, cc, oo))
+        for r, x in zip(refs, g):
+            r += x
+        ref_loss += float(l)
+    torch.cuda.synchronize()
+    assert abs(float(loss) - ref_loss) <= 1e-5 * ref_loss
+    for a, b in zip((gV, gC, gO), refs):
+        assert Hh.rel_l2(a.cpu().numpy(), b.cpu().numpy()) <= 1e-5
+
+
 def _reference():
     import build_ref
     try:

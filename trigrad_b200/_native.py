@@ -35,6 +35,8 @@ SIGNATURES = {
     "tg_backward_scratch_bytes": (_sz, [_i]),
     "tg_blend_backward": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                _vp, _vp, _i, _vp, _sz, _vp]),
+    "tg_blend_backward_l2": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _f, _f, _vp, _vp, _vp, _vp, _vp, _vp,
+                                  _vp, _vp, _vp, _i, _vp, _sz, _vp]),
     "tg_forward_workspace_bytes": (_sz, [_i, _i, _u32]),
     "tg_render_forward": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                _u32, _vp, _vp, _sz, _vp, _vp, _vp]),

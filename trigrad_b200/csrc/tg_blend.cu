@@ -456,18 +456,36 @@ struct BackwardIn {
     const float* depthmap;
     const float* final_w;
     const int* ends;
+    // fused mean-squared-error loss: when l2_target is set, the upstream gradient of the image is
+    // l2_grad_scale * (image - target), the depth-map gradient is zero and the squared differences are
+    // summed into l2_partials[64] (no gradient image is ever materialised)
+    const float4* l2_target;
+    float l2_grad_scale;
+    float* l2_partials;
 };
+constexpr int kLossPartials = 64;
 
 __device__ __forceinline__ int load_pixel_state(const TileCtx& c, const BlendParams& P, const BackwardIn& in,
-                                                PixelGrad& pg, BackState& st) {
+                                                PixelGrad& pg, BackState& st, float* sq_diff = nullptr) {
     pg = PixelGrad{};
     st.alpha = 1.f;
+    if (sq_diff) *sq_diff = 0.f;
     if (!c.active) return 0;
     const size_t index = (size_t)c.iy * P.W + c.ix;
-    const float4 gi = in.gimage[index];
-    pg.gr = gi.x; pg.gg = gi.y; pg.gb = gi.z; pg.ga = gi.w;
-    pg.gd = in.gdepth[index];
-    pg.final_alpha = in.image[index].w;
+    const float4 img = in.image[index];
+    if (in.l2_target) {
+        const float4 t = in.l2_target[index];
+        const float dr = img.x - t.x, dg = img.y - t.y, db = img.z - t.z, da = img.w - t.w;
+        pg.gr = in.l2_grad_scale * dr; pg.gg = in.l2_grad_scale * dg; pg.gb = in.l2_grad_scale * db;
+        pg.ga = in.l2_grad_scale * da;
+        pg.gd = 0.f;
+        if (sq_diff) *sq_diff = dr * dr + dg * dg + db * db + da * da;
+    } else {
+        const float4 gi = in.gimage[index];
+        pg.gr = gi.x; pg.gg = gi.y; pg.gb = gi.z; pg.ga = gi.w;
+        pg.gd = in.gdepth[index];
+    }
+    pg.final_alpha = img.w;
     pg.final_weight = in.final_w[index];
     pg.final_depth = in.depthmap[index];
     st.alpha = pg.final_alpha;
@@ -477,16 +495,23 @@ __device__ __forceinline__ int load_pixel_state(const TileCtx& c, const BlendPar
 // Default mode with the per-pixel fragment ids saved by the forward pass: no list search, no shared
 // memory, no barriers - every thread walks its own fragments last to first.
 template <int MAXT>
-__global__ void __launch_bounds__(MAXT) blend_backward_saved_kernel(BlendParams P, BackwardIn in,
+__global__ void __launch_bounds__(MAXT, MAXT <= 256 ? 4 : 1) blend_backward_saved_kernel(BlendParams P, BackwardIn in,
                                                                     const int* __restrict__ sel,
                                                                     float4* __restrict__ gpack) {
     __shared__ float s_coord[kMaxTileCoords];
     const TileCtx c = tile_context(P, s_coord);
     PixelGrad pg;
     BackState st;
-    const int n = load_pixel_state(c, P, in, pg, st);
+    float sq = 0.f;
+    const int n = load_pixel_state(c, P, in, pg, st, &sq);
     const size_t plane = (size_t)P.W * P.H, index = (size_t)c.iy * P.W + c.ix;
     const int lane = lane_id();
+    if (in.l2_target) {
+        // loss: warp sum, then one atomic per warp into one of 64 partial sums (spread addresses)
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, d);
+        if (lane == 0 && sq != 0.f) atomicAdd(in.l2_partials + ((blockIdx.x * 8 + (threadIdx.x >> 5)) & (kLossPartials - 1)), sq);
+    }
     int nmax = n;
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) nmax = max(nmax, __shfl_xor_sync(0xffffffffu, nmax, d));
@@ -608,7 +633,15 @@ __global__ void __launch_bounds__(MAXT) blend_backward_kernel(BlendParams P, Bac
 // Packed accumulator -> the three gradient tensors of the reference (render.cu:789-791).
 __global__ void __launch_bounds__(256) unpack_gradients_kernel(const float4* __restrict__ gpack, int V,
                                                                float4* __restrict__ gV, float* __restrict__ gC,
-                                                               float* __restrict__ gO, int accumulate) {
+                                                               float* __restrict__ gO, int accumulate,
+                                                               const float* __restrict__ l2_partials, float l2_loss_scale,
+                                                               float* __restrict__ l2_loss_out) {
+    if (l2_loss_out && blockIdx.x == 0 && threadIdx.x < 32) {
+        float x = l2_partials[threadIdx.x] + l2_partials[threadIdx.x + 32];
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) x += __shfl_xor_sync(0xffffffffu, x, d);
+        if (threadIdx.x == 0) *l2_loss_out = (accumulate ? *l2_loss_out : 0.f) + x * l2_loss_scale;
+    }
     const int v = blockIdx.x * blockDim.x + threadIdx.x;
     if (v >= V) return;
     const float4 a = gpack[2 * (size_t)v], b = gpack[2 * (size_t)v + 1];
@@ -673,33 +706,40 @@ int tg_blend_forward(const float* tri_geo, const float* tri_attr, const int32_t*
     return TG_OK;
 }
 
-size_t tg_backward_scratch_bytes(int V) { return (size_t)(V > 0 ? V : 0) * 32 + 32; }
+size_t tg_backward_scratch_bytes(int V) { return (size_t)(V > 0 ? V : 0) * 32 + 512; }
 
-int tg_blend_backward(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids, const int32_t* offsets,
-                      int V, int W, int H, int tw, int th, int per_pixel_sort, int max_layers, const float* grad_image,
-                      const float* grad_depthmap, const float* image, const float* depthmap, const float* final_weights,
-                      const int32_t* ends, const int32_t* selection, float* grad_vertices, float* grad_colors,
-                      float* grad_opacities, int accumulate, void* scratch, size_t scratch_bytes, tg_stream_t stream) {
+static int backward_impl(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids, const int32_t* offsets,
+                         int V, int W, int H, int tw, int th, int per_pixel_sort, int max_layers,
+                         const float* grad_image, const float* grad_depthmap, const float* l2_target, float l2_grad_scale,
+                         float l2_loss_scale, float* l2_loss_out, const float* image, const float* depthmap,
+                         const float* final_weights, const int32_t* ends, const int32_t* selection, float* grad_vertices,
+                         float* grad_colors, float* grad_opacities, int accumulate, void* scratch, size_t scratch_bytes,
+                         tg_stream_t stream) {
     if (int s = blend_args(W, H, tw, th, max_layers)) return s;
     TG_REQUIRE(V >= 0, "V < 0");
-    TG_REQUIRE(offsets && grad_image && grad_depthmap && image && depthmap && final_weights && ends, "null pointer");
+    TG_REQUIRE(offsets && image && depthmap && final_weights && ends, "null pointer");
+    TG_REQUIRE(l2_target || (grad_image && grad_depthmap), "null upstream gradient");
     if (V == 0) return TG_OK;
     TG_REQUIRE(grad_vertices && grad_colors && grad_opacities && scratch, "null gradient / scratch pointer");
-    TG_REQUIRE(((uintptr_t)image & 15) == 0 && ((uintptr_t)grad_image & 15) == 0 && ((uintptr_t)tri_geo & 15) == 0 &&
-                   ((uintptr_t)tri_attr & 15) == 0 && ((uintptr_t)grad_vertices & 15) == 0 && ((uintptr_t)scratch & 15) == 0,
-               "image / grad_image / tri_geo / tri_attr / grad_vertices / scratch must be 16-byte aligned");
+    TG_REQUIRE(((uintptr_t)image & 15) == 0 && ((uintptr_t)grad_image & 15) == 0 && ((uintptr_t)l2_target & 15) == 0 &&
+                   ((uintptr_t)tri_geo & 15) == 0 && ((uintptr_t)tri_attr & 15) == 0 &&
+                   ((uintptr_t)grad_vertices & 15) == 0 && ((uintptr_t)scratch & 15) == 0,
+               "image / grad_image / target / tri_geo / tri_attr / grad_vertices / scratch must be 16-byte aligned");
     if (scratch_bytes < tg_backward_scratch_bytes(V)) {
         tg_host::set_error("backward scratch: need %zu bytes, got %zu", tg_backward_scratch_bytes(V), scratch_bytes);
         return TG_ERR_WORKSPACE;
     }
+    const bool saved = selection != nullptr && tg_selection_planes(per_pixel_sort, max_layers) > 0;
+    TG_REQUIRE(!l2_target || saved, "the fused L2 backward needs the selection saved by the forward pass (default mode)");
     cudaStream_t s = (cudaStream_t)stream;
     float4* gpack = (float4*)scratch;
-    TG_CUDA(cudaMemsetAsync(gpack, 0, (size_t)V * 32, s));
+    float* partials = (float*)((char*)scratch + (size_t)V * 32);
+    TG_CUDA(cudaMemsetAsync(gpack, 0, (size_t)V * 32 + sizeof(float) * tg::kLossPartials, s));
     const tg::BlendParams P = make_params(tri_geo, tri_attr, sorted_ids, offsets, W, H, tw, th, 0.f, max_layers);
     const int tiles = P.tiles_x * ((H + th - 1) / th);
     const int threads = ((tw * th + 31) / 32) * 32;
-    const tg::BackwardIn in = {(const float4*)grad_image, grad_depthmap, (const float4*)image, depthmap, final_weights, ends};
-    const bool saved = selection != nullptr && tg_selection_planes(per_pixel_sort, max_layers) > 0;
+    const tg::BackwardIn in = {(const float4*)grad_image, grad_depthmap, (const float4*)image, depthmap, final_weights,
+                               ends, (const float4*)l2_target, l2_grad_scale, partials};
     if (threads <= 256) {
         if (saved) tg::blend_backward_saved_kernel<256><<<tiles, threads, 0, s>>>(P, in, selection, gpack);
         else if (per_pixel_sort) tg::blend_backward_kernel<true, 256><<<tiles, threads, 0, s>>>(P, in, gpack);
@@ -711,9 +751,33 @@ int tg_blend_backward(const float* tri_geo, const float* tri_attr, const int32_t
     }
     TG_LAUNCH_CHECK("blend_backward_kernel");
     tg::unpack_gradients_kernel<<<(V + 255) / 256, 256, 0, s>>>(gpack, V, (float4*)grad_vertices, grad_colors,
-                                                              grad_opacities, accumulate);
+                                                              grad_opacities, accumulate, partials, l2_loss_scale,
+                                                              l2_target ? l2_loss_out : nullptr);
     TG_LAUNCH_CHECK("unpack_gradients_kernel");
     return TG_OK;
+}
+
+int tg_blend_backward(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids, const int32_t* offsets,
+                      int V, int W, int H, int tw, int th, int per_pixel_sort, int max_layers, const float* grad_image,
+                      const float* grad_depthmap, const float* image, const float* depthmap, const float* final_weights,
+                      const int32_t* ends, const int32_t* selection, float* grad_vertices, float* grad_colors,
+                      float* grad_opacities, int accumulate, void* scratch, size_t scratch_bytes, tg_stream_t stream) {
+    TG_REQUIRE(grad_image && grad_depthmap, "null upstream gradient");
+    return backward_impl(tri_geo, tri_attr, sorted_ids, offsets, V, W, H, tw, th, per_pixel_sort, max_layers, grad_image,
+                         grad_depthmap, nullptr, 0.f, 0.f, nullptr, image, depthmap, final_weights, ends, selection,
+                         grad_vertices, grad_colors, grad_opacities, accumulate, scratch, scratch_bytes, stream);
+}
+
+int tg_blend_backward_l2(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids, const int32_t* offsets,
+                         int V, int W, int H, int tw, int th, int per_pixel_sort, int max_layers, const float* target,
+                         float grad_scale, float loss_scale, float* loss_out, const float* image, const float* depthmap,
+                         const float* final_weights, const int32_t* ends, const int32_t* selection, float* grad_vertices,
+                         float* grad_colors, float* grad_opacities, int accumulate, void* scratch, size_t scratch_bytes,
+                         tg_stream_t stream) {
+    TG_REQUIRE(target && loss_out, "null target / loss pointer");
+    return backward_impl(tri_geo, tri_attr, sorted_ids, offsets, V, W, H, tw, th, per_pixel_sort, max_layers, nullptr,
+                         nullptr, target, grad_scale, loss_scale, loss_out, image, depthmap, final_weights, ends, selection,
+                         grad_vertices, grad_colors, grad_opacities, accumulate, scratch, scratch_bytes, stream);
 }
 
 }  // extern "C"

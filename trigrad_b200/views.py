@@ -4,7 +4,7 @@ The reference renders one view per call and has no multi-device code.  Views are
 batch shards with no data-path exchange: rank r of N renders views [r*B/N, (r+1)*B/N) of the same
 mesh (every GPU holds the whole mesh).  World-space gradients of positions, colours and opacities
 accumulate over the rank's views into ONE contiguous fp32 buffer laid out as
-``[gP (V,3) | gC (V,3) | gO (V)]``; a single ``all_reduce(SUM)`` over NCCL then runs in place on that
+``[gP (V,3) | gC (V,3) | gO (V) | loss]``; a single ``all_reduce(SUM)`` over NCCL then runs in place on that
 buffer.  The projection world -> NDC and its VJP are plain torch ops outside the hot path, as in the
 reference viewer (``viewer.py:274-280``).
 """
@@ -15,6 +15,7 @@ from typing import Callable, Sequence
 
 import torch
 
+from . import wrapper as _w
 from .wrapper import render as _render
 
 
@@ -43,13 +44,15 @@ class GradBuffer:
     points: torch.Tensor     # (V,3) or (V,4) view
     colors: torch.Tensor     # (V,3) view
     opacities: torch.Tensor  # (V,)  view
+    loss: torch.Tensor       # 0-d view of the last element: the summed loss rides along in the same all-reduce
 
     @staticmethod
     def allocate(num_vertices: int, device, position_components: int = 3) -> "GradBuffer":
         """position_components = 3 for world-space positions, 4 for render-space (x, y, z, w) vertices."""
         V, p = num_vertices, position_components
-        flat = torch.zeros((p + 4) * V, dtype=torch.float32, device=device)
-        return GradBuffer(flat, flat[:p * V].view(V, p), flat[p * V:(p + 3) * V].view(V, 3), flat[(p + 3) * V:])
+        flat = torch.zeros((p + 4) * V + 1, dtype=torch.float32, device=device)
+        return GradBuffer(flat, flat[:p * V].view(V, p), flat[p * V:(p + 3) * V].view(V, 3), flat[(p + 3) * V:(p + 4) * V],
+                          flat[(p + 4) * V])
 
     def zero_(self) -> None:
         self.flat.zero_()
@@ -78,6 +81,41 @@ def render_views_l2(points: torch.Tensor, indices: torch.Tensor, colors: torch.T
         grads.opacities += go
         total = total + loss.detach()
     return total
+
+
+def l2_view_step(vertices: torch.Tensor, indices: torch.Tensor, colors: torch.Tensor, opacities: torch.Tensor,
+                 target: torch.Tensor, width: int, height: int, grad_vertices: torch.Tensor, grad_colors: torch.Tensor,
+                 grad_opacities: torch.Tensor, loss: torch.Tensor, tile_width: int = 16, tile_height: int = 16,
+                 early_stopping_threshold: float = 1 / 256, max_layers: int = 32) -> torch.Tensor:
+    """One view of a multi-view optimisation step without autograd: forward, then the backward of
+    ``mean((image - target)**2)`` fused into the gradient kernel.
+
+    Adds the view's gradients to ``grad_vertices [V,4]`` (render-space x, y, z, w), ``grad_colors [V,3]``,
+    ``grad_opacities [V]`` and its loss to the 0-d float32 tensor ``loss`` - no gradient image, no per-view
+    gradient tensors, no elementwise kernels.  Default per-pixel mode only (``max_layers`` in 1..32); use
+    ``render`` with autograd for anything else.  Returns the rendered image.
+    """
+    if not (1 <= max_layers <= 32):
+        raise ValueError("l2_view_step needs 1 <= max_layers <= 32")
+    n, _ = vertices.shape
+    _w.check_tensor(vertices, "vertices", (n, 4))
+    _w.check_tensor(colors, "colors", (n, 3))
+    _w.check_tensor(opacities, "opacities", (n,))
+    m, _ = indices.shape
+    _w.check_tensor(indices, "indices", (m, 3), torch.int32)
+    _w.check_tensor(target, "target", (height, width, 4))
+    if tile_width * tile_height > 1024:
+        raise ValueError("tile_width * tile_height must be <= 1024")
+    if m < 1:
+        loss += torch.mean((torch.tensor([0.0, 0.0, 0.0, 1.0], device=target.device) - target) ** 2)
+        return None
+    (image, depthmap, final_weights, sorted_ids, offsets, tri_geo, tri_attr, ends, selection, _) = _w.forward_native(
+        vertices.contiguous(), indices.contiguous(), colors.contiguous(), opacities.contiguous(), width, height,
+        tile_width, tile_height, early_stopping_threshold, False, True, max_layers)
+    saved = (sorted_ids, offsets, tri_geo, tri_attr, image, depthmap, final_weights, ends, selection)
+    _w.backward_l2_native(target, saved, n, width, height, tile_width, tile_height, True, max_layers,
+                          (grad_vertices, grad_colors, grad_opacities), loss, accumulate=True)
+    return image
 
 
 def allreduce_gradients(grads: GradBuffer, loss: torch.Tensor | None = None, group=None) -> None:

@@ -141,6 +141,34 @@ def backward_native(grad_image, grad_depthmap, saved, V, width, height, tile_wid
     return gV, gC, gO
 
 
+def backward_l2_native(target, saved, V, width, height, tile_width, tile_height, per_pixel_sort, max_layers, out,
+                       loss_out, accumulate=True):
+    """Backward of ``mean((image - target)**2)`` fused into the gradient kernel (no gradient image is formed).
+
+    ``saved`` is the tuple ``forward_native`` returned for backward (it must contain the selection, i.e. the
+    default per-pixel mode with ``max_layers <= 32``); ``out`` = (gV [V,4], gC [V,3], gO [V]) and the 0-d float32
+    ``loss_out`` are overwritten, or added to when ``accumulate`` is true.
+    """
+    lib = N.lib()
+    sorted_ids, offsets, tri_geo, tri_attr, image, depthmap, final_weights, ends, selection = saved
+    if selection is None:
+        raise ValueError("the fused L2 backward needs per_pixel_sort=True and max_layers <= 32")
+    device = image.device
+    n = float(width * height * 4)
+    with torch.cuda.device(device):
+        stream = torch.cuda.current_stream(device).cuda_stream
+        nscratch = lib.tg_backward_scratch_bytes(V)
+        scratch = torch.empty(nscratch, dtype=torch.uint8, device=device)
+        gV, gC, gO = out
+        status = lib.tg_blend_backward_l2(
+            _ptr(tri_geo), _ptr(tri_attr), _ptr(sorted_ids), _ptr(offsets), V, width, height, tile_width, tile_height,
+            int(bool(per_pixel_sort)), int(max_layers), _ptr(target.contiguous()), 2.0 / n, 1.0 / n, _ptr(loss_out),
+            _ptr(image), _ptr(depthmap), _ptr(final_weights), _ptr(ends), _ptr(selection), _ptr(gV), _ptr(gC), _ptr(gO),
+            int(bool(accumulate)), _ptr(scratch), nscratch, C.c_void_p(stream))
+        N.check("blend_backward_l2", status)
+    return gV, gC, gO
+
+
 class Renderer(Function):
     @staticmethod
     def forward(ctx, vertices: torch.Tensor, indices: torch.Tensor, colors: torch.Tensor, opacities: torch.Tensor,
