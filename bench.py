@@ -207,7 +207,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg3")
-    ap.add_argument("--streams", type=int, default=2,
+    ap.add_argument("--streams", type=int, default=4,
                     help="CUDA streams the views of a step are spread over (independent views overlap on the GPU)")
     ap.add_argument("--views-per-gpu", type=int, default=8,
                     help="views of the mesh rendered per GPU per step (a batch of views; gradients are summed)")
