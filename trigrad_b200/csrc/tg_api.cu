@@ -13,14 +13,13 @@ inline int ceil_log2(int x) {
 
 // Carves the caller's workspace; the same function sizes it.
 struct ForwardWorkspace {
-    uint32_t* tri_counts;
     uint32_t* tri_offsets;
-    void* scan_scratch;
-    size_t scan_scratch_bytes;
-    uint32_t* status;
     uint64_t* keys_a;
     uint64_t* keys_b;
     uint32_t* ids_tmp;
+    // status word, scan scratch and sort scratch lie back to back: one memset clears all three
+    uint32_t* status;
+    void* scan_scratch;
     void* sort_scratch;
     size_t sort_scratch_bytes;
     size_t total;
@@ -32,14 +31,12 @@ struct ForwardWorkspace {
             off += align_up(bytes ? bytes : 1);
             return p;
         };
-        tri_counts = (uint32_t*)take(sizeof(uint32_t) * (size_t)T);
         tri_offsets = (uint32_t*)take(sizeof(uint32_t) * ((size_t)T + 1));
-        scan_scratch_bytes = tg_scan_scratch_bytes(T);
-        scan_scratch = take(scan_scratch_bytes);
-        status = (uint32_t*)take(sizeof(uint32_t) * 4);
         keys_a = (uint64_t*)take(sizeof(uint64_t) * (size_t)cap);
         keys_b = (uint64_t*)take(sizeof(uint64_t) * (size_t)cap);
         ids_tmp = (uint32_t*)take(sizeof(uint32_t) * (size_t)cap);
+        status = (uint32_t*)take(sizeof(uint32_t) * 4);
+        scan_scratch = take(tg_host::preprocess_scan_scratch_bytes(T));
         sort_scratch_bytes = tg_sort_scratch_bytes(cap);
         sort_scratch = take(sort_scratch_bytes);
         total = off;
@@ -116,17 +113,16 @@ int tg_render_forward(const float* vertices, const int32_t* indices, const float
     if (int st = scratch_event(&k_ready)) return st;
 
     timer.mark();                                                    // [0] start of "init"
-    TG_CUDA(cudaMemsetAsync(ws.status, 0, sizeof(uint32_t) * 4, s));
-    // look-back words, tickets and digit counters of the sort, sized for the whole list capacity
-    const size_t clear = tg_host::sort_scratch_clear_bytes(list_capacity, passes);
-    if (list_capacity > 0) TG_CUDA(cudaMemsetAsync(ws.sort_scratch, 0, clear, s));
-    timer.mark();                                                    // [1] start of "bary_transforms" (preprocess)
-    int st = tg_preprocess(vertices, indices, colors, opacities, T, W, H, tw, th, ws.tri_counts, nullptr, tri_geo,
-                           tri_attr, stream);
+    // error word, scan tickets and look-back words, and the sort's look-back words, tickets and digit
+    // counters (sized for the whole list capacity): one clear
+    const size_t clear = (size_t)((char*)ws.sort_scratch - (char*)ws.status) +
+                         (list_capacity > 0 ? tg_host::sort_scratch_clear_bytes(list_capacity, passes) : 0);
+    TG_CUDA(cudaMemsetAsync(ws.status, 0, clear, s));
+    timer.mark();                                                    // [1] start of "bary_transforms" (preprocess + scan)
+    int st = tg_host::preprocess_scan(vertices, indices, colors, opacities, T, W, H, tw, th, tri_geo, tri_attr,
+                                      ws.tri_offsets, ws.scan_scratch, ws.status, s);
     if (st) return st;
     timer.mark();                                                    // [2] start of "per_tile_lists"
-    st = tg_scan(ws.tri_counts, ws.tri_offsets, T, ws.scan_scratch, ws.scan_scratch_bytes, ws.status, stream);
-    if (st) return st;
     TG_CUDA(cudaMemcpyAsync(&info_host[0], ws.tri_offsets + T, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
     TG_CUDA(cudaEventRecord(k_ready, s));
     // Keys are emitted while K travels to the host: the kernel drops entries beyond the capacity, and
@@ -163,9 +159,9 @@ int tg_render_forward(const float* vertices, const int32_t* indices, const float
         float ms[5];
         for (int i = 0; i < 5; i++) TG_CUDA(cudaEventElapsedTime(&ms[i], timer.ev[i], timer.ev[i + 1]));
         stage_ms_host[0] = ms[0];   // init
-        stage_ms_host[1] = ms[2];   // per_tile_lists: scan + K read-back + key emission
+        stage_ms_host[1] = ms[2];   // per_tile_lists: K read-back + key emission
         stage_ms_host[2] = ms[3];   // sorting: radix sort + tile ranges
-        stage_ms_host[3] = ms[1];   // bary_transforms: the preprocess kernel
+        stage_ms_host[3] = ms[1];   // bary_transforms: the fused preprocess + scan kernel
         stage_ms_host[4] = ms[4];   // rasterization
         if (info_host[1]) {
             tg_host::set_error("device error word = %u", info_host[1]);

@@ -12,21 +12,18 @@ namespace tg {
 // Stage 1: preprocess.  One thread per triangle: gathers its three vertices and attributes,
 // counts the tiles its bounding box touches and writes the two packed records the compositing
 // kernels stream.  HBM-bound: reads 12 B + 3 gathers of (16+12+4) B, writes 4 + 64 + 96 B.
-__global__ void __launch_bounds__(256) preprocess_kernel(const float4* __restrict__ vertices,
-                                                         const int* __restrict__ indices,
-                                                         const float* __restrict__ colors,
-                                                         const float* __restrict__ opacities, int T, int W, int H,
-                                                         int tw, int th, int tiles_x, int tiles_y,
-                                                         uint32_t* __restrict__ tri_counts, int4* __restrict__ tri_rects,
-                                                         float4* __restrict__ tri_geo, float4* __restrict__ tri_attr) {
-    int t = blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= T) return;
+__device__ __forceinline__ uint32_t preprocess_triangle(int t, const float4* __restrict__ vertices,
+                                                        const int* __restrict__ indices,
+                                                        const float* __restrict__ colors,
+                                                        const float* __restrict__ opacities, int W, int H, int tw,
+                                                        int th, int tiles_x, int tiles_y, int4* __restrict__ tri_rects,
+                                                        float4* __restrict__ tri_geo, float4* __restrict__ tri_attr) {
     int ia = indices[3 * (size_t)t], ib = indices[3 * (size_t)t + 1], ic = indices[3 * (size_t)t + 2];
     float4 a = vertices[ia], b = vertices[ib], c = vertices[ic];
 
     Rect r;
     bool ok = tile_rect(a.x, a.y, b.x, b.y, c.x, c.y, W, H, tw, th, tiles_x, tiles_y, r);
-    tri_counts[t] = ok ? (uint32_t)(r.x1 - r.x0 + 1) * (uint32_t)(r.y1 - r.y0 + 1) : 0u;
+    const uint32_t count = ok ? (uint32_t)(r.x1 - r.x0 + 1) * (uint32_t)(r.y1 - r.y0 + 1) : 0u;
     if (tri_rects) tri_rects[t] = make_int4(r.x0, r.y0, r.x1, r.y1);
 
     // barycentric matrix, reference render.cu:324-336: plain mul/sub/div
@@ -69,6 +66,20 @@ __global__ void __launch_bounds__(256) preprocess_kernel(const float4* __restric
     q[3] = make_float4(div(1.f, a.w), div(1.f, b.w), div(1.f, c.w), __int_as_float(ia));
     q[4] = make_float4(__int_as_float(ib), __int_as_float(ic), a.x, a.y);
     q[5] = make_float4(b.x, b.y, c.x, c.y);
+    return count;
+}
+
+__global__ void __launch_bounds__(256) preprocess_kernel(const float4* __restrict__ vertices,
+                                                         const int* __restrict__ indices,
+                                                         const float* __restrict__ colors,
+                                                         const float* __restrict__ opacities, int T, int W, int H,
+                                                         int tw, int th, int tiles_x, int tiles_y,
+                                                         uint32_t* __restrict__ tri_counts, int4* __restrict__ tri_rects,
+                                                         float4* __restrict__ tri_geo, float4* __restrict__ tri_attr) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    tri_counts[t] = preprocess_triangle(t, vertices, indices, colors, opacities, W, H, tw, th, tiles_x, tiles_y, tri_rects,
+                                        tri_geo, tri_attr);
 }
 
 // ================================================================================================
@@ -91,6 +102,39 @@ __device__ __forceinline__ bool wait_flag(const uint64_t* p, uint64_t& word) {
         if (it > 64) __nanosleep(100);
     }
     return false;
+}
+
+// Decoupled look-back, executed by ONE WARP of partition p: publishes the partition's total, sums the
+// totals of all earlier partitions (32 words per step) until one of them already carries an inclusive
+// prefix, publishes its own inclusive prefix and returns the exclusive one.
+__device__ __forceinline__ uint32_t lookback_exclusive(int p, uint32_t total, uint64_t* part_status, uint32_t* status) {
+    uint32_t excl = 0;
+    if (p == 0) {
+        if (lane_id() == 0) st_volatile(&part_status[0], (2ull << 32) | total);
+        return 0;
+    }
+    if (lane_id() == 0) st_volatile(&part_status[p], (1ull << 32) | total);
+    int q = p - 1 - (int)lane_id();
+    bool failed = false;
+    while (true) {
+        uint64_t word = 2ull << 32;   // virtual partitions before 0: inclusive prefix 0
+        if (q >= 0 && !wait_flag(&part_status[q], word)) { failed = true; word = 2ull << 32; }
+        const uint32_t flag = (uint32_t)(word >> 32), val = (uint32_t)word;
+        const unsigned incl_mask = __ballot_sync(0xffffffffu, flag == 2u);
+        uint32_t contrib = val;
+        if (incl_mask) {
+            const int first = __ffs(incl_mask) - 1;
+            if ((int)lane_id() > first) contrib = 0;
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) contrib += __shfl_xor_sync(0xffffffffu, contrib, d);
+        excl += contrib;
+        if (incl_mask) break;
+        q -= 32;
+    }
+    if (__any_sync(0xffffffffu, failed) && lane_id() == 0) atomicExch(status, 1u);
+    if (lane_id() == 0) st_volatile(&part_status[p], (2ull << 32) | (uint64_t)(excl + total));
+    return excl;
 }
 
 __global__ void __launch_bounds__(kScanThreads) scan_kernel(const uint32_t* __restrict__ in,
@@ -133,32 +177,7 @@ __global__ void __launch_bounds__(kScanThreads) scan_kernel(const uint32_t* __re
     uint32_t thread_excl = warp_off + incl - sum;
 
     if (warp == 0) {
-        uint32_t excl = 0;
-        if (p == 0) {
-            if (lane_id() == 0) st_volatile(&part_status[0], (2ull << 32) | total);
-        } else {
-            if (lane_id() == 0) st_volatile(&part_status[p], (1ull << 32) | total);
-            int q = p - 1 - (int)lane_id();
-            bool failed = false;
-            while (true) {
-                uint64_t word = 2ull << 32;   // virtual partitions before 0: inclusive prefix 0
-                if (q >= 0 && !wait_flag(&part_status[q], word)) { failed = true; word = 2ull << 32; }
-                const uint32_t flag = (uint32_t)(word >> 32), val = (uint32_t)word;
-                const unsigned incl_mask = __ballot_sync(0xffffffffu, flag == 2u);
-                uint32_t contrib = val;
-                if (incl_mask) {
-                    const int first = __ffs(incl_mask) - 1;
-                    if ((int)lane_id() > first) contrib = 0;
-                }
-#pragma unroll
-                for (int d = 16; d > 0; d >>= 1) contrib += __shfl_xor_sync(0xffffffffu, contrib, d);
-                excl += contrib;
-                if (incl_mask) break;
-                q -= 32;
-            }
-            if (__any_sync(0xffffffffu, failed) && lane_id() == 0) atomicExch(status, 1u);
-            if (lane_id() == 0) st_volatile(&part_status[p], (2ull << 32) | (uint64_t)(excl + total));
-        }
+        const uint32_t excl = lookback_exclusive(p, total, part_status, status);
         if (lane_id() == 0) {
             s_excl = excl;
             if (p == num_parts - 1) out[n] = excl + total;
@@ -171,6 +190,54 @@ __global__ void __launch_bounds__(kScanThreads) scan_kernel(const uint32_t* __re
         if (base + i < n) out[base + i] = run;
         run += v[i];
     }
+}
+
+// Stages 1 and 2 in one kernel (the forward path uses this): the CTA that preprocesses 256 triangles
+// scans their tile counts and resolves its prefix by look-back, so the counts never travel through
+// memory and one launch is saved.  Partitions are taken in ticket order.
+__global__ void __launch_bounds__(256) preprocess_scan_kernel(const float4* __restrict__ vertices,
+                                                              const int* __restrict__ indices,
+                                                              const float* __restrict__ colors,
+                                                              const float* __restrict__ opacities, int T, int W, int H,
+                                                              int tw, int th, int tiles_x, int tiles_y,
+                                                              float4* __restrict__ tri_geo, float4* __restrict__ tri_attr,
+                                                              uint32_t* __restrict__ tri_offsets /*[T+1]*/,
+                                                              uint32_t* ticket, uint64_t* part_status, uint32_t* status) {
+    __shared__ uint32_t s_part;
+    __shared__ uint32_t s_warp[8];
+    __shared__ uint32_t s_excl;
+    if (threadIdx.x == 0) s_part = atomicAdd(ticket, 1u);
+    __syncthreads();
+    const int p = (int)s_part, num_parts = gridDim.x;
+    const int t = p * 256 + threadIdx.x;
+    const uint32_t count = (t < T) ? preprocess_triangle(t, vertices, indices, colors, opacities, W, H, tw, th, tiles_x,
+                                                         tiles_y, nullptr, tri_geo, tri_attr)
+                                   : 0u;
+    uint32_t incl = count;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        uint32_t y = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane_id() >= (unsigned)d) incl += y;
+    }
+    const int warp = threadIdx.x >> 5;
+    if (lane_id() == 31) s_warp[warp] = incl;
+    __syncthreads();
+    uint32_t warp_off = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < 8; w++) {
+        uint32_t x = s_warp[w];
+        if (w < warp) warp_off += x;
+        total += x;
+    }
+    if (warp == 0) {
+        const uint32_t excl = lookback_exclusive(p, total, part_status, status);
+        if (lane_id() == 0) {
+            s_excl = excl;
+            if (p == num_parts - 1) tri_offsets[T] = excl + total;
+        }
+    }
+    __syncthreads();
+    if (t < T) tri_offsets[t] = s_excl + warp_off + incl - count;
 }
 
 // ================================================================================================
@@ -363,6 +430,29 @@ static int check_dims_internal(int T, int W, int H, int tw, int th) {
     TG_REQUIRE(W > 0 && H > 0, "image size must be positive");
     TG_REQUIRE(tw > 0 && th > 0, "tile size must be positive");
     TG_REQUIRE(tw * th <= 1024, "tile_width * tile_height must be <= 1024");
+    return TG_OK;
+}
+
+size_t preprocess_scan_scratch_bytes(int T) { return 8 + 8 * ((size_t)(T > 0 ? (T + 255) / 256 : 0) + 1); }
+
+// `scratch` (ticket + partition words) must have been zeroed by the caller.
+int preprocess_scan(const float* vertices, const int32_t* indices, const float* colors, const float* opacities, int T,
+                    int W, int H, int tw, int th, float* tri_geo, float* tri_attr, uint32_t* tri_offsets, void* scratch,
+                    uint32_t* status, cudaStream_t stream) {
+    if (int s = check_dims_internal(T, W, H, tw, th)) return s;
+    TG_REQUIRE(tri_offsets && scratch && status, "null pointer");
+    if (T == 0) {
+        TG_CUDA(cudaMemsetAsync(tri_offsets, 0, sizeof(uint32_t), stream));
+        return TG_OK;
+    }
+    TG_REQUIRE(vertices && indices && colors && opacities && tri_geo && tri_attr, "null pointer");
+    TG_REQUIRE(((uintptr_t)vertices & 15) == 0 && ((uintptr_t)tri_geo & 15) == 0 && ((uintptr_t)tri_attr & 15) == 0,
+               "vertices / tri_geo / tri_attr must be 16-byte aligned");
+    const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
+    tg::preprocess_scan_kernel<<<(T + 255) / 256, 256, 0, stream>>>(
+        (const float4*)vertices, indices, colors, opacities, T, W, H, tw, th, tiles_x, tiles_y, (float4*)tri_geo,
+        (float4*)tri_attr, tri_offsets, (uint32_t*)scratch, (uint64_t*)((char*)scratch + 8), status);
+    TG_LAUNCH_CHECK("preprocess_scan_kernel");
     return TG_OK;
 }
 

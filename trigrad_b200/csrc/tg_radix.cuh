@@ -87,4 +87,8 @@ int sort_pairs(uint64_t* keys_a, uint64_t* keys_b, uint32_t* vals_a, uint32_t* v
                int end_bit, void* scratch, size_t scratch_bytes, uint32_t* status, int* result_in_b_host,
                bool scratch_prepared, cudaStream_t stream);
 size_t sort_scratch_clear_bytes(uint32_t n, int passes);
+size_t preprocess_scan_scratch_bytes(int T);
+int preprocess_scan(const float* vertices, const int32_t* indices, const float* colors, const float* opacities, int T,
+                    int W, int H, int tw, int th, float* tri_geo, float* tri_attr, uint32_t* tri_offsets, void* scratch,
+                    uint32_t* status, cudaStream_t stream);
 }  // namespace tg_host
