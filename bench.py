@@ -74,13 +74,6 @@ def view_vertices(vertices: np.ndarray, k: int) -> np.ndarray:
     return out
 
 
-def tile_bits(tiles: int) -> int:
-    b = 0
-    while (1 << b) < tiles:
-        b += 1
-    return b
-
-
 # ----------------------------------------------------------------------------------------------------
 class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU through NVML (read-only) while a region runs."""
@@ -471,8 +464,6 @@ def measure_stages(torch, St, scene, verts_np, flush, reps: int) -> dict:
     tens = St.scene_tensors(sc)
     T, V, W, H = sc.num_triangles, sc.num_vertices, sc.width, sc.height
     tiles = St.num_tiles(sc)
-    end_bit = 32 + tile_bits(tiles)
-    P = (end_bit + 7) // 8
 
     def timed(fn, setup=None):
         ms = []
@@ -489,22 +480,30 @@ def measure_stages(torch, St, scene, verts_np, flush, reps: int) -> dict:
             ms.append(a.elapsed_time(b))
         return statistics.median(ms), out
 
+    from trigrad_b200 import wrapper as Wr
+
+    # forward: the stage times come from events recorded inside the one forward call (L2 flushed before it)
+    acc = {k: [] for k in Wr.TIMING_KEYS}
+    out = None
+    for _ in range(reps):
+        flush.zero_()
+        out = Wr.forward_native(*tens, W, H,
+                                sc.tile_width, sc.tile_height, 1 / 256, True, True, 32)
+        for k in acc:
+            acc[k].append(out[9][k] * 1e3)
+    med = {k: statistics.median(v) for k, v in acc.items()}
+    image, depth, fw, sids, offsets, geo, attr, ends, sel, _ = out
+    K = int(sids.numel())
+    fwd = (image, depth, fw, ends, sel)
     res = {}
-    ms, (counts, rects, geo, attr) = timed(lambda: St.preprocess(sc, tens))
-    res["preprocess"] = {"kernel": "preprocess_kernel", "ms": ms, "bytes": 16 * T + 16 * V}
-    ms, tri_off = timed(lambda: St.scan(counts))
-    res["scan"] = {"kernel": "scan_kernel", "ms": ms, "bytes": 8 * T}
-    K = int(tri_off[-1])
-    ms, (keys, ids) = timed(lambda: St.emit_keys(sc, tri_off, K, tens))
-    res["emit_keys"] = {"kernel": "emit_keys_kernel", "ms": ms, "bytes": 16 * T + 16 * V + 12 * K}
-    sb = St.SortBuffers(K)
-    ms, (skeys, sids) = timed(lambda: sb.sort(0, end_bit), setup=lambda: sb.load(keys, ids))
-    res["sort"] = {"kernel": "sort_histogram_kernel + onesweep_pass_kernel x P", "ms": ms, "bytes": (8 + 24 * P) * K,
-                   "passes": P}
-    ms, offsets = timed(lambda: St.tile_ranges(skeys, tiles))
-    res["tile_ranges"] = {"kernel": "tile_ranges_kernel", "ms": ms, "bytes": 8 * K + 8 * tiles}
-    ms, fwd = timed(lambda: St.blend_forward(sc, geo, attr, sids, offsets))
-    res["blend_forward"] = {"kernel": "blend_forward_kernel", "ms": ms, "bytes": 100 * K + 28 * W * H}
+    res["init"] = {"kernel": "memset", "ms": med["init"], "bytes": 4 * tiles + 8 * ((T + 255) // 256)}
+    res["binning"] = {"kernel": "preprocess_scan_kernel", "ms": med["bary_transforms"],
+                      "bytes": 12 * T + 32 * V + 164 * T + 8 * tiles}
+    res["emit_entries"] = {"kernel": "emit_keys_kernel<direct> (with the read-back of K)", "ms": med["per_tile_lists"],
+                           "bytes": 16 * T + 16 * V + 8 * K + 8 * tiles}
+    res["tile_sort"] = {"kernel": "tile_sort_kernel + tile_sort_long_kernel", "ms": med["sorting"],
+                        "bytes": 12 * K + 8 * tiles}
+    res["blend_forward"] = {"kernel": "blend_forward_kernel", "ms": med["rasterization"], "bytes": 100 * K + 28 * W * H}
     gi = torch.randn((H, W, 4), device="cuda")
     gd = torch.zeros((H, W), device="cuda")
     ms, _ = timed(lambda: St.blend_backward(sc, geo, attr, sids, offsets, fwd, gi, gd))

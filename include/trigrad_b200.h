@@ -110,6 +110,19 @@ int tg_sort_pairs(uint64_t* keys_a, uint64_t* keys_b, uint32_t* vals_a, uint32_t
  */
 int tg_tile_ranges(const uint64_t* sorted_keys, uint32_t n, int tiles, int32_t* offsets, tg_stream_t stream);
 
+/* ---- stages 3-5 as the forward entry point runs them: segmented sort --------------------------------
+ * entries: uint64 words (ordered depth << 32 | triangle), grouped by tile: tile t owns
+ * entries[offsets[t] .. offsets[t+1]).  Every segment is sorted ascending in place and its low words
+ * are written to sorted_ids at the same positions.  A triangle occurs at most once per tile, so the
+ * result equals the stable sort of (tile << 32 | depth) keys that
+ * cub::DeviceSegmentedSort::StableSortPairs produces for entries emitted in triangle order
+ * (src/trigrad/render.cu:272-284).  scratch: tg_tile_sort_scratch_bytes(tiles) bytes, 4-byte aligned;
+ * need not be cleared.  No device-side waiting: segments of any length are handled by one CTA each.
+ */
+size_t tg_tile_sort_scratch_bytes(int tiles);
+int tg_sort_tile_lists(uint64_t* entries, const int32_t* offsets, int tiles, int32_t* sorted_ids, void* scratch,
+                       size_t scratch_bytes, tg_stream_t stream);
+
 /* ---- stage 6: forward compositing ---------------------------------------------------------------
  * One CTA per tile, one thread per pixel.  Replaces render_forward_kernel
  * (src/trigrad/render.cu:540-619 with :338-453).  max_layers must be >= 1.

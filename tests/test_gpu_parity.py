@@ -129,6 +129,75 @@ def test_tile_ranges_bit_exact(pipeline):
     assert np.array_equal(p["sids"].cpu().numpy(), li.ids)
 
 
+def _forward_entry_lists(sc):
+    """Sorted ids and tile offsets as the whole-forward entry point builds them (fused binning, per-tile sort)."""
+    from trigrad_b200 import wrapper as Wr
+
+    t = Hh.scene_tensors(sc)
+    out = Wr.forward_native(*t, sc.width, sc.height, sc.tile_width,
+                            sc.tile_height, 1 / 256, False, True, 32)
+    torch.cuda.synchronize()
+    return out[3].cpu().numpy(), out[4].cpu().numpy(), out[0].cpu().numpy()
+
+
+def test_forward_entry_lists_bit_exact(pipeline):
+    """tg_render_forward takes another route to the lists (counts per tile, segmented sort): same result."""
+    p = pipeline
+    ids, offsets, _ = _forward_entry_lists(p["sc"])
+    assert np.array_equal(offsets, p["st"].offsets)
+    assert np.array_equal(ids, p["st"].ids_sorted)
+
+
+def test_forward_entry_more_tiles_than_one_cta_scans():
+    """Beyond 65536 tiles the tile offsets come from the device-wide scan instead of the last CTA."""
+    sc = S.random_triangles(6000, 2100, 2100, 0.02, 0.6, name="many_tiles")
+    sc.tile_width = sc.tile_height = 8
+    assert Hh.num_tiles(sc) > 65536
+    ids, offsets, _ = _forward_entry_lists(sc)
+    li = O.build_lists(sc.vertices, sc.indices, sc.width, sc.height, sc.tile_width, sc.tile_height)
+    assert np.array_equal(offsets, li.offsets)
+    assert np.array_equal(ids, li.ids)
+
+
+def test_forward_entry_very_long_tile_lists():
+    """One tile with more than 16384 entries: chunks sorted in shared memory, wide steps in global memory."""
+    sc = S.random_triangles(50_000, 32, 32, 0.5, 0.3, name="one_tile_50k")
+    ids, offsets, image = _forward_entry_lists(sc)
+    li = O.build_lists(sc.vertices, sc.indices, sc.width, sc.height, sc.tile_width, sc.tile_height)
+    assert np.diff(li.offsets).max() > 16384
+    assert np.array_equal(offsets, li.offsets)
+    assert np.array_equal(ids, li.ids)
+    of = O.forward(sc.vertices, sc.indices, sc.colors, sc.opacities, sc.width, sc.height, sc.tile_width, sc.tile_height,
+                   1 / 256, True, 32)
+    assert np.array_equal(image.view(np.uint32), of.image.view(np.uint32))
+
+
+@pytest.mark.parametrize("lengths", [
+    [0, 1, 2, 31, 32, 33, 0, 255, 256, 257, 1023, 1024, 1025, 0, 4096, 5000, 16384],
+    [16385, 3, 40_000, 0, 70_001, 1],
+    [300_000],
+], ids=["short_and_medium", "beyond_one_chunk", "single_300k"])
+def test_sort_tile_lists_segment_lengths(lengths):
+    """Segmented sort alone: every length class of the kernels, duplicates of the high word included."""
+    rng = np.random.default_rng(len(lengths))
+    offsets = np.zeros(len(lengths) + 1, np.int32)
+    np.cumsum(lengths, out=offsets[1:])
+    n = int(offsets[-1])
+    hi = rng.integers(0, 1 << 32, n, dtype=np.uint64)
+    hi[::3] = hi[0] if n else 0                                   # equal depths: the low word decides
+    entries = np.empty(n, np.uint64)
+    expect = np.empty(n, np.uint64)
+    for a, b in zip(offsets[:-1], offsets[1:]):
+        lo = rng.permutation(int(b - a)).astype(np.uint64)        # unique within a segment, like triangle ids
+        entries[a:b] = (hi[a:b] << np.uint64(32)) | lo
+        expect[a:b] = np.sort(entries[a:b])
+    dev = Hh.cuda(entries.view(np.int64))
+    ids = Hh.sort_tile_lists(dev, Hh.cuda(offsets))
+    torch.cuda.synchronize()
+    assert np.array_equal(dev.cpu().numpy().view(np.uint64), expect)
+    assert np.array_equal(ids.cpu().numpy().view(np.uint32), (expect & np.uint64(0xFFFFFFFF)).astype(np.uint32))
+
+
 MODES = [
     dict(per_pixel_sort=True, max_layers=32, thr=1 / 256),    # the reference default
     dict(per_pixel_sort=False, max_layers=32, thr=1 / 256),

@@ -30,6 +30,8 @@ SIGNATURES = {
     "tg_sort_scratch_bytes": (_sz, [_u32]),
     "tg_sort_pairs": (_i, [_vp, _vp, _vp, _vp, _u32, _i, _i, _vp, _sz, _vp, C.POINTER(_i), _vp]),
     "tg_tile_ranges": (_i, [_vp, _u32, _i, _vp, _vp]),
+    "tg_tile_sort_scratch_bytes": (_sz, [_i]),
+    "tg_sort_tile_lists": (_i, [_vp, _vp, _i, _vp, _vp, _sz, _vp]),
     "tg_selection_planes": (_i, [_i, _i]),
     "tg_blend_forward": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tg_backward_scratch_bytes": (_sz, [_i]),

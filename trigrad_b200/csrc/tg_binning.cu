@@ -17,11 +17,11 @@ __device__ __forceinline__ uint32_t preprocess_triangle(int t, const float4* __r
                                                         const float* __restrict__ colors,
                                                         const float* __restrict__ opacities, int W, int H, int tw,
                                                         int th, int tiles_x, int tiles_y, int4* __restrict__ tri_rects,
-                                                        float4* __restrict__ tri_geo, float4* __restrict__ tri_attr) {
+                                                        float4* __restrict__ tri_geo, float4* __restrict__ tri_attr,
+                                                        Rect& r) {
     int ia = indices[3 * (size_t)t], ib = indices[3 * (size_t)t + 1], ic = indices[3 * (size_t)t + 2];
     float4 a = vertices[ia], b = vertices[ib], c = vertices[ic];
 
-    Rect r;
     bool ok = tile_rect(a.x, a.y, b.x, b.y, c.x, c.y, W, H, tw, th, tiles_x, tiles_y, r);
     const uint32_t count = ok ? (uint32_t)(r.x1 - r.x0 + 1) * (uint32_t)(r.y1 - r.y0 + 1) : 0u;
     if (tri_rects) tri_rects[t] = make_int4(r.x0, r.y0, r.x1, r.y1);
@@ -78,8 +78,9 @@ __global__ void __launch_bounds__(256) preprocess_kernel(const float4* __restric
                                                          float4* __restrict__ tri_geo, float4* __restrict__ tri_attr) {
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= T) return;
+    Rect r;
     tri_counts[t] = preprocess_triangle(t, vertices, indices, colors, opacities, W, H, tw, th, tiles_x, tiles_y, tri_rects,
-                                        tri_geo, tri_attr);
+                                        tri_geo, tri_attr, r);
 }
 
 // ================================================================================================
@@ -195,6 +196,61 @@ __global__ void __launch_bounds__(kScanThreads) scan_kernel(const uint32_t* __re
 // Stages 1 and 2 in one kernel (the forward path uses this): the CTA that preprocesses 256 triangles
 // scans their tile counts and resolves its prefix by look-back, so the counts never travel through
 // memory and one launch is saved.  Partitions are taken in ticket order.
+//
+// With `bin.tile_cursor` set the CTA also counts its (triangle, tile) entries per tile, one thread per
+// entry, and the CTA that finishes last turns the counts into the exclusive tile offsets, in place
+// (`tile_cursor[t]` = first slot of tile t, advanced later by the entry writer) and in `bin.offsets`.
+struct TileBinArgs {
+    uint32_t* tile_cursor;   // [tiles], zero on entry; nullptr: no per-tile counting
+    int32_t* offsets;        // [tiles + 1], written when scan_here
+    uint32_t* done;          // zero on entry: counts finished CTAs
+    int tiles;
+    int scan_here;           // 1: the last CTA scans the tile counts; 0: the host launches a scan
+};
+
+// Exclusive scan of cursor[0..tiles) by one CTA of 256 threads, in place, copy in offsets[0..tiles].
+// Every thread takes 32 consecutive counts per round (up to 8192 tiles need a single round) and reads
+// them twice, once for its sum and once to write the running offsets, which keeps its registers few.
+__device__ void tile_offsets_by_one_cta(uint32_t* cursor, int32_t* offsets, int tiles, uint32_t* s_warp /*[8]*/) {
+    constexpr int kPer = 32;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    uint32_t carry = 0;
+    for (int base = 0; base < tiles; base += 256 * kPer) {
+        const int i0 = base + tid * kPer;
+        uint32_t mine = 0;
+#pragma unroll 8
+        for (int k = 0; k < kPer; k++) mine += (i0 + k < tiles) ? __ldcg(cursor + i0 + k) : 0u;
+        uint32_t incl = mine;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            uint32_t y = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane_id() >= (unsigned)d) incl += y;
+        }
+        __syncthreads();                      // s_warp free again
+        if (lane_id() == 31) s_warp[warp] = incl;
+        __syncthreads();
+        uint32_t warp_off = 0, total = 0;
+#pragma unroll
+        for (int w = 0; w < 8; w++) {
+            uint32_t x = s_warp[w];
+            if (w < warp) warp_off += x;
+            total += x;
+        }
+        uint32_t run = carry + warp_off + incl - mine;
+#pragma unroll 8
+        for (int k = 0; k < kPer; k++) {
+            if (i0 + k < tiles) {
+                const uint32_t c = __ldcg(cursor + i0 + k);
+                cursor[i0 + k] = run;
+                offsets[i0 + k] = (int32_t)run;
+                run += c;
+            }
+        }
+        carry += total;
+    }
+    if (tid == 0) offsets[tiles] = (int32_t)carry;
+}
+
 __global__ void __launch_bounds__(256) preprocess_scan_kernel(const float4* __restrict__ vertices,
                                                               const int* __restrict__ indices,
                                                               const float* __restrict__ colors,
@@ -202,16 +258,22 @@ __global__ void __launch_bounds__(256) preprocess_scan_kernel(const float4* __re
                                                               int tw, int th, int tiles_x, int tiles_y,
                                                               float4* __restrict__ tri_geo, float4* __restrict__ tri_attr,
                                                               uint32_t* __restrict__ tri_offsets /*[T+1]*/,
-                                                              uint32_t* ticket, uint64_t* part_status, uint32_t* status) {
+                                                              uint32_t* ticket, uint64_t* part_status, uint32_t* status,
+                                                              TileBinArgs bin) {
     __shared__ uint32_t s_part;
     __shared__ uint32_t s_warp[8];
     __shared__ uint32_t s_excl;
-    if (threadIdx.x == 0) s_part = atomicAdd(ticket, 1u);
+    __shared__ uint32_t s_loc[257];          // exclusive offsets of the CTA's triangles within the CTA
+    __shared__ int s_rect[256 * 3];          // x0, y0, rows of each triangle's tile rectangle
+    __shared__ bool s_last;
+    const int tid = threadIdx.x;
+    if (tid == 0) s_part = atomicAdd(ticket, 1u);
     __syncthreads();
     const int p = (int)s_part, num_parts = gridDim.x;
-    const int t = p * 256 + threadIdx.x;
+    const int t = p * 256 + tid;
+    Rect r = {0, 0, 0, 0};
     const uint32_t count = (t < T) ? preprocess_triangle(t, vertices, indices, colors, opacities, W, H, tw, th, tiles_x,
-                                                         tiles_y, nullptr, tri_geo, tri_attr)
+                                                         tiles_y, nullptr, tri_geo, tri_attr, r)
                                    : 0u;
     uint32_t incl = count;
 #pragma unroll
@@ -219,7 +281,7 @@ __global__ void __launch_bounds__(256) preprocess_scan_kernel(const float4* __re
         uint32_t y = __shfl_up_sync(0xffffffffu, incl, d);
         if (lane_id() >= (unsigned)d) incl += y;
     }
-    const int warp = threadIdx.x >> 5;
+    const int warp = tid >> 5;
     if (lane_id() == 31) s_warp[warp] = incl;
     __syncthreads();
     uint32_t warp_off = 0, total = 0;
@@ -229,6 +291,14 @@ __global__ void __launch_bounds__(256) preprocess_scan_kernel(const float4* __re
         if (w < warp) warp_off += x;
         total += x;
     }
+    const uint32_t local_excl = warp_off + incl - count;
+    if (bin.tile_cursor) {
+        s_loc[tid] = local_excl;
+        if (tid == 0) s_loc[256] = total;
+        s_rect[3 * tid] = r.x0;
+        s_rect[3 * tid + 1] = r.y0;
+        s_rect[3 * tid + 2] = r.y1 - r.y0 + 1;
+    }
     if (warp == 0) {
         const uint32_t excl = lookback_exclusive(p, total, part_status, status);
         if (lane_id() == 0) {
@@ -237,7 +307,28 @@ __global__ void __launch_bounds__(256) preprocess_scan_kernel(const float4* __re
         }
     }
     __syncthreads();
-    if (t < T) tri_offsets[t] = s_excl + warp_off + incl - count;
+    if (t < T) tri_offsets[t] = s_excl + local_excl;
+    if (!bin.tile_cursor) return;
+
+    for (uint32_t e = tid; e < total; e += 256) {
+        int lo = 0, hi = 256;                 // largest i with s_loc[i] <= e
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (s_loc[mid] <= e) lo = mid; else hi = mid;
+        }
+        const uint32_t local = e - s_loc[lo];
+        const uint32_t ny = (uint32_t)s_rect[3 * lo + 2];
+        const int tx = s_rect[3 * lo] + (int)(local / ny), ty = s_rect[3 * lo + 1] + (int)(local % ny);
+        atomicAdd(&bin.tile_cursor[ty * tiles_x + tx], 1u);
+    }
+    if (!bin.scan_here) return;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = (atomicAdd(bin.done, 1u) == (uint32_t)num_parts - 1u);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    tile_offsets_by_one_cta(bin.tile_cursor, bin.offsets, bin.tiles, s_warp);
 }
 
 // ================================================================================================
@@ -332,12 +423,18 @@ struct __align__(16) EmitTri {
 };
 constexpr int kEmitThreads = 256;
 
+//
+// DIRECT: the tile offsets are known already; every entry takes the next free slot of its tile
+// (`tile_cursor`, arrival order) and is stored there as (ordered depth << 32 | triangle), ready for the
+// per-tile sort.  `keys` is that array, `ids` is unused.
+template <bool DIRECT>
 __global__ void __launch_bounds__(kEmitThreads) emit_keys_kernel(const float4* __restrict__ vertices,
                                                                  const int* __restrict__ indices, int T, int W, int H,
                                                                  int tw, int th, int tiles_x, int tiles_y,
                                                                  const uint32_t* __restrict__ tri_offsets,
                                                                  uint64_t* __restrict__ keys, uint32_t* __restrict__ ids,
-                                                                 uint32_t capacity, HistArgs hist) {
+                                                                 uint32_t capacity, HistArgs hist,
+                                                                 uint32_t* __restrict__ tile_cursor) {
     __shared__ EmitTri s_tri[kEmitThreads];
     __shared__ uint32_t s_off[kEmitThreads + 1];
     __shared__ uint32_t s_hist[kMaxPasses * kRadix];
@@ -346,7 +443,7 @@ __global__ void __launch_bounds__(kEmitThreads) emit_keys_kernel(const float4* _
     const int tid = threadIdx.x;
     const int t0 = blockIdx.x * kEmitThreads;
     const int ntri = min(kEmitThreads, T - t0);
-    if (hist.hist)
+    if (!DIRECT && hist.hist)
         for (int i = tid; i < hist.passes * kRadix; i += kEmitThreads) s_hist[i] = 0;
     if (tid < ntri) {
         const int t = t0 + tid;
@@ -382,6 +479,11 @@ __global__ void __launch_bounds__(kEmitThreads) emit_keys_kernel(const float4* _
         const TriXYZ v = {tr.ax, tr.ay, tr.az, tr.bx, tr.by, tr.bz, tr.cx, tr.cy, tr.cz};
         const Plane pl = {tr.A, tr.B, tr.C};
         const float depth = tile_key(v, pl, tx, ty, W, H, tw, th);
+        if (DIRECT) {
+            const uint32_t pos = atomicAdd(&tile_cursor[ty * tiles_x + tx], 1u);
+            if (pos < capacity) keys[pos] = ((uint64_t)float_to_ordered(depth) << 32) | (uint32_t)(t0 + lo);
+            continue;
+        }
         const uint64_t key = ((uint64_t)(uint32_t)(ty * tiles_x + tx) << 32) | float_to_ordered(depth);
         if (ge < capacity) {                       // the host guarantees K <= capacity before the result is used
             keys[ge] = key;
@@ -389,7 +491,7 @@ __global__ void __launch_bounds__(kEmitThreads) emit_keys_kernel(const float4* _
             if (hist.hist) hist_count(s_hist, key, hist);
         }
     }
-    if (hist.hist) {
+    if (!DIRECT && hist.hist) {
         __syncthreads();
         hist_flush_and_finish(s_hist, s_warp_tot, &s_last, hist);
     }
@@ -433,26 +535,46 @@ static int check_dims_internal(int T, int W, int H, int tw, int th) {
     return TG_OK;
 }
 
+// ticket (4) + finished-CTA counter (4) + one look-back word per partition
 size_t preprocess_scan_scratch_bytes(int T) { return 8 + 8 * ((size_t)(T > 0 ? (T + 255) / 256 : 0) + 1); }
 
-// `scratch` (ticket + partition words) must have been zeroed by the caller.
+// `scratch` (ticket, counter and partition words) and, when given, `tile_cursor[tiles]` must have been
+// zeroed by the caller.  With `tile_cursor` the tile offsets are produced as well (in `tile_cursor` itself
+// and in `offsets[tiles + 1]`); beyond kTileScanByLastCta tiles a device-wide scan does that, for which
+// `tile_scan_scratch` (zeroed, tg_scan_scratch_bytes(tiles) bytes) is needed.
 int preprocess_scan(const float* vertices, const int32_t* indices, const float* colors, const float* opacities, int T,
                     int W, int H, int tw, int th, float* tri_geo, float* tri_attr, uint32_t* tri_offsets, void* scratch,
-                    uint32_t* status, cudaStream_t stream) {
+                    uint32_t* status, uint32_t* tile_cursor, int32_t* offsets, void* tile_scan_scratch,
+                    cudaStream_t stream) {
     if (int s = check_dims_internal(T, W, H, tw, th)) return s;
     TG_REQUIRE(tri_offsets && scratch && status, "null pointer");
+    const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
+    const int tiles = tiles_x * tiles_y;
     if (T == 0) {
         TG_CUDA(cudaMemsetAsync(tri_offsets, 0, sizeof(uint32_t), stream));
+        if (tile_cursor) TG_CUDA(cudaMemsetAsync(offsets, 0, sizeof(int32_t) * ((size_t)tiles + 1), stream));
         return TG_OK;
     }
     TG_REQUIRE(vertices && indices && colors && opacities && tri_geo && tri_attr, "null pointer");
     TG_REQUIRE(((uintptr_t)vertices & 15) == 0 && ((uintptr_t)tri_geo & 15) == 0 && ((uintptr_t)tri_attr & 15) == 0,
                "vertices / tri_geo / tri_attr must be 16-byte aligned");
-    const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
+    TG_REQUIRE(!tile_cursor || offsets, "null offsets");
+    const bool by_last_cta = tiles <= tg::kTileScanByLastCta;
+    TG_REQUIRE(!tile_cursor || by_last_cta || tile_scan_scratch, "null tile scan scratch");
+    const tg::TileBinArgs bin = {tile_cursor, offsets, (uint32_t*)scratch + 1, tiles, by_last_cta ? 1 : 0};
     tg::preprocess_scan_kernel<<<(T + 255) / 256, 256, 0, stream>>>(
         (const float4*)vertices, indices, colors, opacities, T, W, H, tw, th, tiles_x, tiles_y, (float4*)tri_geo,
-        (float4*)tri_attr, tri_offsets, (uint32_t*)scratch, (uint64_t*)((char*)scratch + 8), status);
+        (float4*)tri_attr, tri_offsets, (uint32_t*)scratch, (uint64_t*)((char*)scratch + 8), status, bin);
     TG_LAUNCH_CHECK("preprocess_scan_kernel");
+    if (tile_cursor && !by_last_cta) {
+        // counts -> offsets by the device-wide scan, then the cursors start at the offsets
+        const int parts = (tiles + tg::kScanTile - 1) / tg::kScanTile;
+        tg::scan_kernel<<<parts, tg::kScanThreads, 0, stream>>>(tile_cursor, (uint32_t*)offsets, tiles, parts,
+                                                                 (uint32_t*)tile_scan_scratch,
+                                                                 (uint64_t*)((char*)tile_scan_scratch + 8), status);
+        TG_LAUNCH_CHECK("scan_kernel");
+        TG_CUDA(cudaMemcpyAsync(tile_cursor, offsets, sizeof(uint32_t) * (size_t)tiles, cudaMemcpyDeviceToDevice, stream));
+    }
     return TG_OK;
 }
 
@@ -463,9 +585,26 @@ int emit_keys(const float* vertices, const int32_t* indices, int T, int W, int H
     if (T == 0) return TG_OK;
     TG_REQUIRE(vertices && indices && tri_offsets && keys && ids, "null pointer");
     const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
-    tg::emit_keys_kernel<<<(T + tg::kEmitThreads - 1) / tg::kEmitThreads, tg::kEmitThreads, 0, stream>>>(
-        (const float4*)vertices, indices, T, W, H, tw, th, tiles_x, tiles_y, tri_offsets, keys, ids, capacity, hist);
+    tg::emit_keys_kernel<false><<<(T + tg::kEmitThreads - 1) / tg::kEmitThreads, tg::kEmitThreads, 0, stream>>>(
+        (const float4*)vertices, indices, T, W, H, tw, th, tiles_x, tiles_y, tri_offsets, keys, ids, capacity, hist,
+        nullptr);
     TG_LAUNCH_CHECK("emit_keys_kernel");
+    return TG_OK;
+}
+
+// Entries written straight into their tile's segment of `entries` (capacity slots), unsorted within it.
+int emit_entries(const float* vertices, const int32_t* indices, int T, int W, int H, int tw, int th,
+                 const uint32_t* tri_offsets, uint32_t* tile_cursor, uint64_t* entries, uint32_t capacity,
+                 cudaStream_t stream) {
+    if (int s = check_dims_internal(T, W, H, tw, th)) return s;
+    if (T == 0 || capacity == 0) return TG_OK;
+    TG_REQUIRE(vertices && indices && tri_offsets && tile_cursor && entries, "null pointer");
+    const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
+    const tg::HistArgs none = {nullptr, nullptr, 0, 0, 0};
+    tg::emit_keys_kernel<true><<<(T + tg::kEmitThreads - 1) / tg::kEmitThreads, tg::kEmitThreads, 0, stream>>>(
+        (const float4*)vertices, indices, T, W, H, tw, th, tiles_x, tiles_y, tri_offsets, entries, nullptr, capacity, none,
+        tile_cursor);
+    TG_LAUNCH_CHECK("emit_entries_kernel");
     return TG_OK;
 }
 static std::atomic<unsigned long long> g_launches{0};

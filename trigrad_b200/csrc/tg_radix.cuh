@@ -17,6 +17,8 @@ constexpr int kSortWarps = kSortThreads / 32;
 constexpr size_t kHistBytes = (size_t)kMaxPasses * kRadix * sizeof(uint32_t);
 constexpr size_t kCtrBytes = 64;
 constexpr int kHistDoneWord = 8;
+// Up to this many tiles the CTA that finishes the fused preprocess kernel last scans the tile counts itself.
+constexpr int kTileScanByLastCta = 65536;
 
 // Exclusive scan of one value per thread over the first 256 threads of a CTA (all threads of the CTA
 // must call it; threads beyond 256 pass 0 and ignore the result).
@@ -90,5 +92,12 @@ size_t sort_scratch_clear_bytes(uint32_t n, int passes);
 size_t preprocess_scan_scratch_bytes(int T);
 int preprocess_scan(const float* vertices, const int32_t* indices, const float* colors, const float* opacities, int T,
                     int W, int H, int tw, int th, float* tri_geo, float* tri_attr, uint32_t* tri_offsets, void* scratch,
-                    uint32_t* status, cudaStream_t stream);
+                    uint32_t* status, uint32_t* tile_cursor, int32_t* offsets, void* tile_scan_scratch,
+                    cudaStream_t stream);
+int emit_entries(const float* vertices, const int32_t* indices, int T, int W, int H, int tw, int th,
+                 const uint32_t* tri_offsets, uint32_t* tile_cursor, uint64_t* entries, uint32_t capacity,
+                 cudaStream_t stream);
+size_t tile_sort_scratch_bytes(int tiles);
+int sort_tile_lists(uint64_t* entries, const int32_t* offsets, int tiles, int32_t* sorted_ids, uint32_t* long_list,
+                    bool scratch_prepared, bool write_back, cudaStream_t stream);
 }  // namespace tg_host

@@ -1,0 +1,255 @@
+// Per-tile sort of the (depth, triangle) entries: the segmented counterpart of the device-wide radix
+// sort.  The reference sorts (tile << 32 | depth) keys with a stable device-wide sort
+// (render.cu:505-527); because every triangle occurs at most once per tile and entries are emitted in
+// triangle order, sorting each tile's segment by (depth, triangle) gives the same permutation.
+//
+// Entries are uint64 words (ordered depth << 32 | triangle), already grouped by tile:
+// tile t owns entries[offsets[t] .. offsets[t+1]).
+//   n <= 128     one warp per tile, rank sort: every element counts the smaller ones (no exchange steps)
+//   n <= 1024    one warp per tile, bitonic network in the warp's 8 KB slice of shared memory
+//   n <= 16384   bitonic network in 128 KB of shared memory, 1024 threads, tiles taken from a work list
+//   beyond       the same CTA sorts 16384-entry chunks in shared memory and runs the network's wide
+//                steps on the segment in global memory
+// No kernel here waits on another CTA.
+#include "tg_radix.cuh"
+
+namespace tg {
+
+constexpr int kTileSortWarps = 4;                      // tiles per CTA of the short kernel
+constexpr int kTileSortThreads = 32 * kTileSortWarps;
+constexpr int kTileSortRank = 128;
+constexpr int kTileSortShort = 1024;
+constexpr int kTileSortLongThreads = 1024;
+constexpr int kTileSortChunk = 16384;
+
+// Pair q of a step with stride j: the lower index, i.e. q with a zero bit inserted at position log2(j).
+__device__ __forceinline__ uint32_t pair_low(uint32_t q, uint32_t j) { return ((q & ~(j - 1)) << 1) | (q & (j - 1)); }
+
+// NT threads work on one array: a whole CTA (barrier) or one warp (NT == 32, warp barrier).
+template <int NT>
+__device__ __forceinline__ void group_sync() {
+    if (NT == 32) __syncwarp(); else __syncthreads();
+}
+
+// Steps j = j_first, j_first/2, .. 1 of a merge on s[0..P): partner i | j, ascending.
+template <int NT>
+__device__ __forceinline__ void merge_tail_smem(uint64_t* s, int P, int j_first, int tid) {
+    for (int j = j_first; j > 0; j >>= 1) {
+        group_sync<NT>();
+        for (int q = tid; q < (P >> 1); q += NT) {
+            const uint32_t i = pair_low(q, j), l = i | j;
+            uint64_t a = s[i], b = s[l];
+            if (a > b) {
+                s[i] = b;
+                s[l] = a;
+            }
+        }
+    }
+}
+
+// Whole ascending sort of s[0..P), P a power of two.  Every step compares towards the same side (the
+// first step of a merge pairs mirrored positions), so padding with the largest word stays at the end.
+template <int NT>
+__device__ __forceinline__ void bitonic_sort_smem(uint64_t* s, int P, int tid) {
+    for (int k = 2; k <= P; k <<= 1) {
+        const int j = k >> 1;
+        group_sync<NT>();
+        for (int q = tid; q < (P >> 1); q += NT) {
+            const uint32_t i = pair_low(q, j), l = i ^ (uint32_t)(k - 1);
+            uint64_t a = s[i], b = s[l];
+            if (a > b) {
+                s[i] = b;
+                s[l] = a;
+            }
+        }
+        merge_tail_smem<NT>(s, P, j >> 1, tid);
+    }
+    group_sync<NT>();
+}
+
+__device__ __forceinline__ int pow2_at_least(int n) {
+    int p = 1;
+    while (p < n) p <<= 1;
+    return p;
+}
+
+// One warp per tile.  Tiles longer than kTileSortShort are appended to `long_list` ([0] = count, then
+// tile numbers) for tile_sort_long_kernel.
+__global__ void __launch_bounds__(kTileSortThreads) tile_sort_kernel(uint64_t* __restrict__ entries,
+                                                                     const int32_t* __restrict__ offsets, int tiles,
+                                                                     int32_t* __restrict__ sorted_ids,
+                                                                     uint32_t* __restrict__ long_list,
+                                                                     int write_back) {
+    __shared__ uint64_t s_all[kTileSortWarps][kTileSortShort];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tile = blockIdx.x * kTileSortWarps + warp;
+    if (tile >= tiles) return;
+    uint64_t* s = s_all[warp];
+    const int edge = (lane < 2) ? offsets[tile + lane] : 0;
+    const int beg = __shfl_sync(0xffffffffu, edge, 0);
+    const int n = __shfl_sync(0xffffffffu, edge, 1) - beg;
+    if (n <= 0) return;
+    if (n > kTileSortShort) {
+        if (lane == 0) long_list[1 + atomicAdd(&long_list[0], 1u)] = (uint32_t)tile;
+        return;
+    }
+    if (n <= kTileSortRank) {
+        constexpr int kPer = kTileSortRank / 32;
+        uint64_t mine[kPer];
+#pragma unroll
+        for (int r = 0; r < kPer; r++) {
+            const int i = lane + r * 32;
+            mine[r] = (i < n) ? entries[beg + i] : ~0ull;
+            if (i < n) s[i] = mine[r];
+        }
+        __syncwarp();
+        int below[kPer] = {};
+        if (n <= 32) {
+            for (int j = 0; j < n; j++) below[0] += (s[j] < mine[0]) ? 1 : 0;
+        } else {
+            for (int j = 0; j < n; j++) {
+                const uint64_t other = s[j];
+#pragma unroll
+                for (int r = 0; r < kPer; r++) below[r] += (other < mine[r]) ? 1 : 0;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < kPer; r++) {
+            if (lane + r * 32 < n) {
+                sorted_ids[beg + below[r]] = (int32_t)(uint32_t)mine[r];
+                if (write_back) entries[beg + below[r]] = mine[r];
+            }
+        }
+        return;
+    }
+    const int P = pow2_at_least(n);
+    for (int i = lane; i < P; i += 32) s[i] = (i < n) ? entries[beg + i] : ~0ull;
+    bitonic_sort_smem<32>(s, P, lane);
+    for (int i = lane; i < n; i += 32) {
+        sorted_ids[beg + i] = (int32_t)(uint32_t)s[i];
+        if (write_back) entries[beg + i] = s[i];
+    }
+}
+
+// One wide step of the network on a segment in global memory: pairs (i, l) with l >= n do nothing.
+template <bool MIRROR>
+__device__ __forceinline__ void global_step(uint64_t* seg, uint32_t n, uint32_t P, uint32_t j, uint32_t k, int tid) {
+    for (uint32_t q = tid; q < (P >> 1); q += kTileSortLongThreads) {
+        const uint32_t i = pair_low(q, j), l = MIRROR ? (i ^ (k - 1)) : (i | j);
+        if (l < n) {
+            uint64_t a = seg[i], b = seg[l];
+            if (a > b) {
+                seg[i] = b;
+                seg[l] = a;
+            }
+        }
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(kTileSortLongThreads) tile_sort_long_kernel(uint64_t* entries,
+                                                                              const int32_t* __restrict__ offsets,
+                                                                              int32_t* __restrict__ sorted_ids,
+                                                                              const uint32_t* __restrict__ long_list,
+                                                                              int write_back) {
+    extern __shared__ __align__(16) uint64_t s_long[];
+    const int tid = threadIdx.x;
+    const uint32_t count = long_list[0];
+    for (uint32_t w = blockIdx.x; w < count; w += gridDim.x) {
+        const int tile = (int)long_list[1 + w];
+        const int beg = offsets[tile];
+        const uint32_t n = (uint32_t)(offsets[tile + 1] - beg);
+        uint64_t* seg = entries + beg;
+        if (n <= (uint32_t)kTileSortChunk) {
+            const int P = pow2_at_least((int)n);
+            for (int i = tid; i < P; i += kTileSortLongThreads) s_long[i] = ((uint32_t)i < n) ? seg[i] : ~0ull;
+            bitonic_sort_smem<kTileSortLongThreads>(s_long, P, tid);
+            for (uint32_t i = tid; i < n; i += kTileSortLongThreads) {
+                sorted_ids[beg + i] = (int32_t)(uint32_t)s_long[i];
+                if (write_back) seg[i] = s_long[i];
+            }
+            __syncthreads();
+            continue;
+        }
+        // chunks sorted in shared memory, wide steps in global memory
+        uint32_t P = (uint32_t)kTileSortChunk;
+        while (P < n) P <<= 1;
+        for (uint32_t base = 0; base < n; base += kTileSortChunk) {
+            for (int i = tid; i < kTileSortChunk; i += kTileSortLongThreads)
+                s_long[i] = (base + i < n) ? seg[base + i] : ~0ull;
+            bitonic_sort_smem<kTileSortLongThreads>(s_long, kTileSortChunk, tid);
+            for (int i = tid; i < kTileSortChunk; i += kTileSortLongThreads)
+                if (base + i < n) seg[base + i] = s_long[i];
+            __syncthreads();
+        }
+        for (uint32_t k = 2u * kTileSortChunk; k <= P && k != 0; k <<= 1) {
+            global_step<true>(seg, n, P, k >> 1, k, tid);
+            for (uint32_t j = k >> 2; j >= (uint32_t)kTileSortChunk; j >>= 1) global_step<false>(seg, n, P, j, k, tid);
+            for (uint32_t base = 0; base < n; base += kTileSortChunk) {
+                for (int i = tid; i < kTileSortChunk; i += kTileSortLongThreads)
+                    s_long[i] = (base + i < n) ? seg[base + i] : ~0ull;
+                merge_tail_smem<kTileSortLongThreads>(s_long, kTileSortChunk, kTileSortChunk >> 1, tid);
+                __syncthreads();
+                for (int i = tid; i < kTileSortChunk; i += kTileSortLongThreads)
+                    if (base + i < n) seg[base + i] = s_long[i];
+                __syncthreads();
+            }
+        }
+        for (uint32_t i = tid; i < n; i += kTileSortLongThreads) sorted_ids[beg + i] = (int32_t)(uint32_t)seg[i];
+        __syncthreads();
+    }
+}
+
+}  // namespace tg
+
+namespace tg_host {
+
+size_t tile_sort_scratch_bytes(int tiles) { return sizeof(uint32_t) * ((size_t)(tiles > 0 ? tiles : 0) + 1); }
+
+// `scratch_prepared`: the caller has zeroed the first word of `long_list`.
+int sort_tile_lists(uint64_t* entries, const int32_t* offsets, int tiles, int32_t* sorted_ids, uint32_t* long_list,
+                    bool scratch_prepared, bool write_back, cudaStream_t s) {
+    TG_REQUIRE(tiles >= 0, "tiles < 0");
+    if (tiles == 0) return TG_OK;
+    TG_REQUIRE(entries && offsets && sorted_ids && long_list, "null pointer");
+    constexpr int kMaxDevices = 64;
+    static bool attr_set[kMaxDevices] = {};
+    const size_t long_smem = sizeof(uint64_t) * tg::kTileSortChunk;
+    int dev = 0;
+    TG_CUDA(cudaGetDevice(&dev));
+    TG_REQUIRE(dev >= 0 && dev < kMaxDevices, "device index outside the supported range");
+    if (!attr_set[dev]) {
+        TG_CUDA(cudaFuncSetAttribute(tg::tile_sort_long_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)long_smem));
+        attr_set[dev] = true;
+    }
+    if (!scratch_prepared) TG_CUDA(cudaMemsetAsync(long_list, 0, sizeof(uint32_t), s));
+    tg::tile_sort_kernel<<<(tiles + tg::kTileSortWarps - 1) / tg::kTileSortWarps, tg::kTileSortThreads, 0, s>>>(
+        entries, offsets, tiles, sorted_ids, long_list, write_back ? 1 : 0);
+    TG_LAUNCH_CHECK("tile_sort_kernel");
+    const int grid = tiles < 148 ? tiles : 148;
+    tg::tile_sort_long_kernel<<<grid, tg::kTileSortLongThreads, long_smem, s>>>(entries, offsets, sorted_ids, long_list,
+                                                                                 write_back ? 1 : 0);
+    TG_LAUNCH_CHECK("tile_sort_long_kernel");
+    return TG_OK;
+}
+
+}  // namespace tg_host
+
+extern "C" {
+
+size_t tg_tile_sort_scratch_bytes(int tiles) { return tg_host::tile_sort_scratch_bytes(tiles); }
+
+int tg_sort_tile_lists(uint64_t* entries, const int32_t* offsets, int tiles, int32_t* sorted_ids, void* scratch,
+                       size_t scratch_bytes, tg_stream_t stream) {
+    if (scratch_bytes < tg_host::tile_sort_scratch_bytes(tiles)) {
+        tg_host::set_error("tile sort scratch: need %zu bytes, got %zu", tg_host::tile_sort_scratch_bytes(tiles),
+                           scratch_bytes);
+        return TG_ERR_WORKSPACE;
+    }
+    TG_REQUIRE(((uintptr_t)scratch & 3) == 0 && ((uintptr_t)entries & 7) == 0, "alignment");
+    return tg_host::sort_tile_lists(entries, offsets, tiles, sorted_ids, (uint32_t*)scratch, false, true,
+                                    (cudaStream_t)stream);
+}
+
+}  // extern "C"

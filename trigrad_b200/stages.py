@@ -118,6 +118,17 @@ def tile_ranges(sorted_keys: torch.Tensor, tiles: int):
     return off
 
 
+def sort_tile_lists(entries: torch.Tensor, offsets: torch.Tensor):
+    """Sorts every tile's segment of `entries` (uint64 as int64 storage) in place; returns the low words."""
+    tiles = offsets.numel() - 1
+    ids = torch.empty(entries.numel(), dtype=torch.int32, device="cuda")
+    nscratch = N.lib().tg_tile_sort_scratch_bytes(tiles)
+    scratch = torch.empty(nscratch, dtype=torch.uint8, device="cuda")
+    N.check("sort_tile_lists", N.lib().tg_sort_tile_lists(ptr(entries), ptr(offsets), tiles, ptr(ids), ptr(scratch),
+                                                          nscratch, stream()))
+    return ids
+
+
 def blend_forward(sc, geo, attr, ids, offsets, thr=1 / 256, per_pixel_sort=True, max_layers=32, save_selection=True):
     """Returns (image, depthmap, final_weights, ends, selection); selection is None when not applicable."""
     H, W = sc.height, sc.width
