@@ -209,24 +209,34 @@ struct TileBinArgs {
 };
 
 // Exclusive scan of cursor[0..tiles) by one CTA of 256 threads, in place, copy in offsets[0..tiles].
-// Every thread takes 32 consecutive counts per round (up to 8192 tiles need a single round) and reads
-// them twice, once for its sum and once to write the running offsets, which keeps its registers few.
-__device__ void tile_offsets_by_one_cta(uint32_t* cursor, int32_t* offsets, int tiles, uint32_t* s_warp /*[8]*/) {
-    constexpr int kPer = 32;
+// Rounds of 2048 counts: coalesced loads into shared memory, eight consecutive counts per thread,
+// coalesced stores (a single SM issues too few memory requests per clock for anything strided).
+constexpr int kTileScanRound = 2048;
+__device__ void tile_offsets_by_one_cta(uint32_t* cursor, int32_t* offsets, int tiles, uint32_t* s_buf /*[2048]*/,
+                                        uint32_t* s_warp /*[8]*/) {
+    constexpr int kPer = kTileScanRound / 256;
     const int tid = threadIdx.x, warp = tid >> 5;
     uint32_t carry = 0;
-    for (int base = 0; base < tiles; base += 256 * kPer) {
-        const int i0 = base + tid * kPer;
-        uint32_t mine = 0;
-#pragma unroll 8
-        for (int k = 0; k < kPer; k++) mine += (i0 + k < tiles) ? __ldcg(cursor + i0 + k) : 0u;
+    for (int base = 0; base < tiles; base += kTileScanRound) {
+        __syncthreads();                      // s_buf and s_warp free again
+#pragma unroll
+        for (int k = 0; k < kPer; k++) {
+            const int i = base + k * 256 + tid;
+            s_buf[k * 256 + tid] = (i < tiles) ? __ldcg(cursor + i) : 0u;
+        }
+        __syncthreads();
+        uint32_t v[kPer], mine = 0;
+#pragma unroll
+        for (int k = 0; k < kPer; k++) {
+            v[k] = s_buf[tid * kPer + k];
+            mine += v[k];
+        }
         uint32_t incl = mine;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
             uint32_t y = __shfl_up_sync(0xffffffffu, incl, d);
             if (lane_id() >= (unsigned)d) incl += y;
         }
-        __syncthreads();                      // s_warp free again
         if (lane_id() == 31) s_warp[warp] = incl;
         __syncthreads();
         uint32_t warp_off = 0, total = 0;
@@ -237,13 +247,19 @@ __device__ void tile_offsets_by_one_cta(uint32_t* cursor, int32_t* offsets, int 
             total += x;
         }
         uint32_t run = carry + warp_off + incl - mine;
-#pragma unroll 8
+#pragma unroll
         for (int k = 0; k < kPer; k++) {
-            if (i0 + k < tiles) {
-                const uint32_t c = __ldcg(cursor + i0 + k);
-                cursor[i0 + k] = run;
-                offsets[i0 + k] = (int32_t)run;
-                run += c;
+            s_buf[tid * kPer + k] = run;
+            run += v[k];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < kPer; k++) {
+            const int i = base + k * 256 + tid;
+            if (i < tiles) {
+                const uint32_t x = s_buf[k * 256 + tid];
+                cursor[i] = x;
+                offsets[i] = (int32_t)x;
             }
         }
         carry += total;
@@ -251,7 +267,7 @@ __device__ void tile_offsets_by_one_cta(uint32_t* cursor, int32_t* offsets, int 
     if (tid == 0) offsets[tiles] = (int32_t)carry;
 }
 
-__global__ void __launch_bounds__(256) preprocess_scan_kernel(const float4* __restrict__ vertices,
+__global__ void __launch_bounds__(256, 6) preprocess_scan_kernel(const float4* __restrict__ vertices,
                                                               const int* __restrict__ indices,
                                                               const float* __restrict__ colors,
                                                               const float* __restrict__ opacities, int T, int W, int H,
@@ -263,8 +279,9 @@ __global__ void __launch_bounds__(256) preprocess_scan_kernel(const float4* __re
     __shared__ uint32_t s_part;
     __shared__ uint32_t s_warp[8];
     __shared__ uint32_t s_excl;
-    __shared__ uint32_t s_loc[257];          // exclusive offsets of the CTA's triangles within the CTA
-    __shared__ int s_rect[256 * 3];          // x0, y0, rows of each triangle's tile rectangle
+    __shared__ uint32_t s_buf[kTileScanRound];
+    uint32_t* s_loc = s_buf;                 // [257] exclusive offsets of the CTA's triangles within the CTA
+    int* s_rect = (int*)s_buf + 257;         // [768] x0, y0, rows of each triangle's tile rectangle
     __shared__ bool s_last;
     const int tid = threadIdx.x;
     if (tid == 0) s_part = atomicAdd(ticket, 1u);
@@ -322,13 +339,15 @@ __global__ void __launch_bounds__(256) preprocess_scan_kernel(const float4* __re
         atomicAdd(&bin.tile_cursor[ty * tiles_x + tx], 1u);
     }
     if (!bin.scan_here) return;
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) s_last = (atomicAdd(bin.done, 1u) == (uint32_t)num_parts - 1u);
+    __syncthreads();                          // the CTA's counts are issued; one cumulative fence publishes them
+    if (tid == 0) {
+        __threadfence();
+        s_last = (atomicAdd(bin.done, 1u) == (uint32_t)num_parts - 1u);
+    }
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    tile_offsets_by_one_cta(bin.tile_cursor, bin.offsets, bin.tiles, s_warp);
+    tile_offsets_by_one_cta(bin.tile_cursor, bin.offsets, bin.tiles, s_buf, s_warp);
 }
 
 // ================================================================================================
