@@ -7,7 +7,8 @@
 // tile t owns entries[offsets[t] .. offsets[t+1]).
 //   n <= 128     one warp per tile, rank sort: every element counts the smaller ones (no exchange steps)
 //   n <= 1024    one warp per tile, bitonic network in the warp's 8 KB slice of shared memory
-//   n <= 16384   bitonic network in 128 KB of shared memory, 1024 threads, tiles taken from a work list
+//   n <= 16384   bitonic network in 136 KB of shared memory, 1024 threads that keep up to 16 words each in
+//                registers between trips to shared memory; tiles taken from a work list
 //   beyond       the same CTA sorts 16384-entry chunks in shared memory and runs the network's wide
 //                steps on the segment in global memory
 // No kernel here waits on another CTA.
@@ -73,8 +74,8 @@ __device__ __forceinline__ int pow2_at_least(int n) {
     return p;
 }
 
-// One warp per tile.  Tiles longer than kTileSortShort are appended to `long_list` ([0] = count, then
-// tile numbers) for tile_sort_long_kernel.
+// One warp per tile.  Tiles longer than kTileSortShort are appended to `long_list` ([0] = count, [1] is
+// the long kernel's, then tile numbers) for tile_sort_long_kernel.
 __global__ void __launch_bounds__(kTileSortThreads) tile_sort_kernel(uint64_t* __restrict__ entries,
                                                                      const int32_t* __restrict__ offsets, int tiles,
                                                                      int32_t* __restrict__ sorted_ids,
@@ -90,7 +91,7 @@ __global__ void __launch_bounds__(kTileSortThreads) tile_sort_kernel(uint64_t* _
     const int n = __shfl_sync(0xffffffffu, edge, 1) - beg;
     if (n <= 0) return;
     if (n > kTileSortShort) {
-        if (lane == 0) long_list[1 + atomicAdd(&long_list[0], 1u)] = (uint32_t)tile;
+        if (lane == 0) long_list[2 + atomicAdd(&long_list[0], 1u)] = (uint32_t)tile;
         return;
     }
     if (n <= kTileSortRank) {
@@ -147,56 +148,150 @@ __device__ __forceinline__ void global_step(uint64_t* seg, uint32_t n, uint32_t 
     __syncthreads();
 }
 
+// ---- register-blocked network for the long kernel --------------------------------------------------
+// The array of P = 1024 << LOGE words lives in shared memory with one spare word after every 16 (so that
+// a thread's 16 consecutive words do not fall on the banks of its neighbours').  A thread keeps
+// E = 1 << LOGE words in registers per round: the words whose indices differ only in LOGE chosen bits,
+// which lets it run up to LOGE steps of the network between two trips to shared memory.
+__device__ __forceinline__ int padded(int i) { return i + (i >> 4); }
+constexpr int kLongSmemWords = kTileSortChunk + (kTileSortChunk >> 4);
+
+// Steps for index bits b_top .. 0 of the phase that merges runs of 1 << kb words.  Direction of a pair:
+// ascending where bit kb of the index is clear (classic bitonic sort), always ascending with all_asc
+// (the merge tail of the all-ascending network used on segments that span several chunks).
+template <int LOGE>
+__device__ __forceinline__ void blocked_steps(uint64_t* s, int tid, int kb, int b_top, bool all_asc) {
+    constexpr int E = 1 << LOGE;
+    int b = b_top;
+    while (b >= 0) {
+        const int lo = (b - LOGE + 1 > 0) ? b - LOGE + 1 : 0;
+        const int base = ((tid >> lo) << (lo + LOGE)) | (tid & ((1 << lo) - 1));
+        uint64_t v[E];
+#pragma unroll
+        for (int r = 0; r < E; r++) v[r] = s[padded(base + (r << lo))];
+#pragma unroll
+        for (int bit = LOGE - 1; bit >= 0; bit--) {
+            if (bit > b - lo) continue;
+#pragma unroll
+            for (int r = 0; r < E; r++) {
+                if (r & (1 << bit)) continue;
+                const bool desc = !all_asc && (((base + (r << lo)) >> kb) & 1);
+                const uint64_t x = v[r], y = v[r | (1 << bit)];
+                const bool sw = (x > y) != desc;
+                v[r] = sw ? y : x;
+                v[r | (1 << bit)] = sw ? x : y;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < E; r++) s[padded(base + (r << lo))] = v[r];
+        __syncthreads();
+        b = lo - 1;
+    }
+}
+
+// Whole ascending sort of the padded array of 1024 << LOGE words (data in place, barrier passed).
+template <int LOGE>
+__device__ __forceinline__ void blocked_sort(uint64_t* s, int tid) {
+    constexpr int E = 1 << LOGE;
+    {   // phases 1 .. LOGE touch only the thread's own E consecutive words: one trip
+        const int base = tid << LOGE;
+        uint64_t v[E];
+#pragma unroll
+        for (int r = 0; r < E; r++) v[r] = s[padded(base + r)];
+#pragma unroll
+        for (int kb = 1; kb <= LOGE; kb++) {
+#pragma unroll
+            for (int bit = kb - 1; bit >= 0; bit--) {
+#pragma unroll
+                for (int r = 0; r < E; r++) {
+                    if (r & (1 << bit)) continue;
+                    const bool desc = ((base + r) >> kb) & 1;
+                    const uint64_t x = v[r], y = v[r | (1 << bit)];
+                    const bool sw = (x > y) != desc;
+                    v[r] = sw ? y : x;
+                    v[r | (1 << bit)] = sw ? x : y;
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < E; r++) s[padded(base + r)] = v[r];
+        __syncthreads();
+    }
+    for (int kb = LOGE + 1; kb <= 10 + LOGE; kb++) blocked_steps<LOGE>(s, tid, kb, kb - 1, false);
+}
+
+// Loads seg[0..n) (padding with the largest word up to 1024 << LOGE), sorts, hands the result out.
+template <int LOGE>
+__device__ __forceinline__ void sort_segment_in_smem(uint64_t* s, uint64_t* seg, uint32_t n, int32_t* ids_out,
+                                                     bool write_back, int tid) {
+    constexpr int P = kTileSortLongThreads << LOGE;
+    for (int i = tid; i < P; i += kTileSortLongThreads) s[padded(i)] = ((uint32_t)i < n) ? seg[i] : ~0ull;
+    __syncthreads();
+    blocked_sort<LOGE>(s, tid);
+    for (uint32_t i = tid; i < n; i += kTileSortLongThreads) {
+        const uint64_t x = s[padded((int)i)];
+        if (ids_out) ids_out[i] = (int32_t)(uint32_t)x;
+        if (write_back) seg[i] = x;
+    }
+    __syncthreads();
+}
+
+// Persistent CTAs (one per SM) take the long tiles from the work list, next free item first.
+// long_list: [0] number of items, [1] next item to hand out (both zero before tile_sort_kernel), items.
 __global__ void __launch_bounds__(kTileSortLongThreads) tile_sort_long_kernel(uint64_t* entries,
                                                                               const int32_t* __restrict__ offsets,
                                                                               int32_t* __restrict__ sorted_ids,
-                                                                              const uint32_t* __restrict__ long_list,
-                                                                              int write_back) {
+                                                                              uint32_t* long_list, int write_back) {
     extern __shared__ __align__(16) uint64_t s_long[];
+    __shared__ uint32_t s_item;
+    constexpr int kLogChunk = 14;
+    static_assert((1 << kLogChunk) == kTileSortChunk && kTileSortLongThreads == 1024, "chunk = 1024 threads x 16 words");
     const int tid = threadIdx.x;
     const uint32_t count = long_list[0];
-    for (uint32_t w = blockIdx.x; w < count; w += gridDim.x) {
-        const int tile = (int)long_list[1 + w];
+    while (true) {
+        if (tid == 0) s_item = atomicAdd(&long_list[1], 1u);
+        __syncthreads();
+        const uint32_t w = s_item;
+        __syncthreads();
+        if (w >= count) break;
+        const int tile = (int)long_list[2 + w];
         const int beg = offsets[tile];
         const uint32_t n = (uint32_t)(offsets[tile + 1] - beg);
         uint64_t* seg = entries + beg;
-        if (n <= (uint32_t)kTileSortChunk) {
-            const int P = pow2_at_least((int)n);
-            for (int i = tid; i < P; i += kTileSortLongThreads) s_long[i] = ((uint32_t)i < n) ? seg[i] : ~0ull;
-            bitonic_sort_smem<kTileSortLongThreads>(s_long, P, tid);
-            for (uint32_t i = tid; i < n; i += kTileSortLongThreads) {
-                sorted_ids[beg + i] = (int32_t)(uint32_t)s_long[i];
-                if (write_back) seg[i] = s_long[i];
-            }
-            __syncthreads();
-            continue;
-        }
-        // chunks sorted in shared memory, wide steps in global memory
-        uint32_t P = (uint32_t)kTileSortChunk;
-        while (P < n) P <<= 1;
-        for (uint32_t base = 0; base < n; base += kTileSortChunk) {
-            for (int i = tid; i < kTileSortChunk; i += kTileSortLongThreads)
-                s_long[i] = (base + i < n) ? seg[base + i] : ~0ull;
-            bitonic_sort_smem<kTileSortLongThreads>(s_long, kTileSortChunk, tid);
-            for (int i = tid; i < kTileSortChunk; i += kTileSortLongThreads)
-                if (base + i < n) seg[base + i] = s_long[i];
-            __syncthreads();
-        }
-        for (uint32_t k = 2u * kTileSortChunk; k <= P && k != 0; k <<= 1) {
-            global_step<true>(seg, n, P, k >> 1, k, tid);
-            for (uint32_t j = k >> 2; j >= (uint32_t)kTileSortChunk; j >>= 1) global_step<false>(seg, n, P, j, k, tid);
+        if (n <= 2048u) {
+            sort_segment_in_smem<1>(s_long, seg, n, sorted_ids + beg, write_back, tid);
+        } else if (n <= 4096u) {
+            sort_segment_in_smem<2>(s_long, seg, n, sorted_ids + beg, write_back, tid);
+        } else if (n <= 8192u) {
+            sort_segment_in_smem<3>(s_long, seg, n, sorted_ids + beg, write_back, tid);
+        } else if (n <= (uint32_t)kTileSortChunk) {
+            sort_segment_in_smem<4>(s_long, seg, n, sorted_ids + beg, write_back, tid);
+        } else {
+            // Chunks sorted in shared memory; the steps wider than a chunk run on the segment in global
+            // memory.  This network compares towards the same side everywhere (the first step of a merge
+            // pairs mirrored positions), so the words missing beyond n act as padding without being stored.
+            uint32_t P = (uint32_t)kTileSortChunk;
+            while (P < n) P <<= 1;
             for (uint32_t base = 0; base < n; base += kTileSortChunk) {
-                for (int i = tid; i < kTileSortChunk; i += kTileSortLongThreads)
-                    s_long[i] = (base + i < n) ? seg[base + i] : ~0ull;
-                merge_tail_smem<kTileSortLongThreads>(s_long, kTileSortChunk, kTileSortChunk >> 1, tid);
-                __syncthreads();
-                for (int i = tid; i < kTileSortChunk; i += kTileSortLongThreads)
-                    if (base + i < n) seg[base + i] = s_long[i];
-                __syncthreads();
+                const uint32_t m = (n - base < (uint32_t)kTileSortChunk) ? n - base : (uint32_t)kTileSortChunk;
+                sort_segment_in_smem<4>(s_long, seg + base, m, nullptr, true, tid);
             }
+            for (uint32_t k = 2u * kTileSortChunk; k <= P && k != 0; k <<= 1) {
+                global_step<true>(seg, n, P, k >> 1, k, tid);
+                for (uint32_t j = k >> 2; j >= (uint32_t)kTileSortChunk; j >>= 1) global_step<false>(seg, n, P, j, k, tid);
+                for (uint32_t base = 0; base < n; base += kTileSortChunk) {
+                    for (int i = tid; i < kTileSortChunk; i += kTileSortLongThreads)
+                        s_long[padded(i)] = (base + i < n) ? seg[base + i] : ~0ull;
+                    __syncthreads();
+                    blocked_steps<4>(s_long, tid, kLogChunk, kLogChunk - 1, true);
+                    for (int i = tid; i < kTileSortChunk; i += kTileSortLongThreads)
+                        if (base + i < n) seg[base + i] = s_long[padded(i)];
+                    __syncthreads();
+                }
+            }
+            for (uint32_t i = tid; i < n; i += kTileSortLongThreads) sorted_ids[beg + i] = (int32_t)(uint32_t)seg[i];
+            __syncthreads();
         }
-        for (uint32_t i = tid; i < n; i += kTileSortLongThreads) sorted_ids[beg + i] = (int32_t)(uint32_t)seg[i];
-        __syncthreads();
     }
 }
 
@@ -204,9 +299,9 @@ __global__ void __launch_bounds__(kTileSortLongThreads) tile_sort_long_kernel(ui
 
 namespace tg_host {
 
-size_t tile_sort_scratch_bytes(int tiles) { return sizeof(uint32_t) * ((size_t)(tiles > 0 ? tiles : 0) + 1); }
+size_t tile_sort_scratch_bytes(int tiles) { return sizeof(uint32_t) * ((size_t)(tiles > 0 ? tiles : 0) + 2); }
 
-// `scratch_prepared`: the caller has zeroed the first word of `long_list`.
+// `scratch_prepared`: the caller has zeroed the first two words of `long_list`.
 int sort_tile_lists(uint64_t* entries, const int32_t* offsets, int tiles, int32_t* sorted_ids, uint32_t* long_list,
                     bool scratch_prepared, bool write_back, cudaStream_t s) {
     TG_REQUIRE(tiles >= 0, "tiles < 0");
@@ -214,7 +309,7 @@ int sort_tile_lists(uint64_t* entries, const int32_t* offsets, int tiles, int32_
     TG_REQUIRE(entries && offsets && sorted_ids && long_list, "null pointer");
     constexpr int kMaxDevices = 64;
     static bool attr_set[kMaxDevices] = {};
-    const size_t long_smem = sizeof(uint64_t) * tg::kTileSortChunk;
+    const size_t long_smem = sizeof(uint64_t) * tg::kLongSmemWords;
     int dev = 0;
     TG_CUDA(cudaGetDevice(&dev));
     TG_REQUIRE(dev >= 0 && dev < kMaxDevices, "device index outside the supported range");
@@ -223,7 +318,7 @@ int sort_tile_lists(uint64_t* entries, const int32_t* offsets, int tiles, int32_
                                      (int)long_smem));
         attr_set[dev] = true;
     }
-    if (!scratch_prepared) TG_CUDA(cudaMemsetAsync(long_list, 0, sizeof(uint32_t), s));
+    if (!scratch_prepared) TG_CUDA(cudaMemsetAsync(long_list, 0, 2 * sizeof(uint32_t), s));
     tg::tile_sort_kernel<<<(tiles + tg::kTileSortWarps - 1) / tg::kTileSortWarps, tg::kTileSortThreads, 0, s>>>(
         entries, offsets, tiles, sorted_ids, long_list, write_back ? 1 : 0);
     TG_LAUNCH_CHECK("tile_sort_kernel");
