@@ -6,9 +6,10 @@
 // Entries are uint64 words (ordered depth << 32 | triangle), already grouped by tile:
 // tile t owns entries[offsets[t] .. offsets[t+1]).
 //   n <= 128     one warp per tile, rank sort: every element counts the smaller ones (no exchange steps)
-//   n <= 1024    one warp per tile, bitonic network in the warp's 8 KB slice of shared memory
-//   n <= 16384   bitonic network in 136 KB of shared memory, 1024 threads that keep up to 16 words each in
-//                registers between trips to shared memory; tiles taken from a work list
+//   n <= 1024    the four warps of the CTA together: bitonic network in shared memory, 8 words per thread
+//                kept in registers between trips to shared memory
+//   n <= 16384   the same network in 136 KB of shared memory, 1024 threads with 8 or 16 words each;
+//                tiles taken from a work list
 //   beyond       the same CTA sorts 16384-entry chunks in shared memory and runs the network's wide
 //                steps on the segment in global memory
 // No kernel here waits on another CTA.
@@ -26,75 +27,130 @@ constexpr int kTileSortChunk = 16384;
 // Pair q of a step with stride j: the lower index, i.e. q with a zero bit inserted at position log2(j).
 __device__ __forceinline__ uint32_t pair_low(uint32_t q, uint32_t j) { return ((q & ~(j - 1)) << 1) | (q & (j - 1)); }
 
-// NT threads work on one array: a whole CTA (barrier) or one warp (NT == 32, warp barrier).
-template <int NT>
-__device__ __forceinline__ void group_sync() {
-    if (NT == 32) __syncwarp(); else __syncthreads();
+// ---- register-blocked bitonic network -----------------------------------------------------------------
+// The array of P = 1 << logP words lives in shared memory with one spare word after every 16 (so that
+// the consecutive words of one thread do not fall on the banks of its neighbours').  P >> LOGE threads
+// take part; each keeps E = 1 << LOGE words in registers per round - the words whose indices differ
+// only in LOGE chosen bits - and so runs up to LOGE steps of the network between two trips to shared
+// memory.  Every thread of the CTA must call (barriers inside).
+__device__ __forceinline__ int padded(int i) { return i + (i >> 4); }
+constexpr int kMidSmemWords = kTileSortShort + (kTileSortShort >> 4);
+constexpr int kLongSmemWords = kTileSortChunk + (kTileSortChunk >> 4);
+
+template <int E>
+__device__ __forceinline__ void exchange_in_registers(uint64_t (&v)[E], int bit, int r, bool desc) {
+    const uint64_t x = v[r], y = v[r | (1 << bit)];
+    const bool sw = (x > y) != desc;
+    v[r] = sw ? y : x;
+    v[r | (1 << bit)] = sw ? x : y;
 }
 
-// Steps j = j_first, j_first/2, .. 1 of a merge on s[0..P): partner i | j, ascending.
-template <int NT>
-__device__ __forceinline__ void merge_tail_smem(uint64_t* s, int P, int j_first, int tid) {
-    for (int j = j_first; j > 0; j >>= 1) {
-        group_sync<NT>();
-        for (int q = tid; q < (P >> 1); q += NT) {
-            const uint32_t i = pair_low(q, j), l = i | j;
-            uint64_t a = s[i], b = s[l];
-            if (a > b) {
-                s[i] = b;
-                s[l] = a;
+// Steps for index bits b_top .. 0 of the phase that merges runs of 1 << kb words.  Direction of a pair:
+// ascending where bit kb of the index is clear (classic bitonic sort), always ascending with all_asc
+// (the merge tail of the all-ascending network used on segments that span several chunks).
+template <int LOGE>
+__device__ __forceinline__ void blocked_steps(uint64_t* s, int tid, int logP, int kb, int b_top, bool all_asc) {
+    constexpr int E = 1 << LOGE;
+    const bool active = tid < (1 << (logP - LOGE));
+    int b = b_top;
+    while (b >= 0) {
+        const int lo = (b - LOGE + 1 > 0) ? b - LOGE + 1 : 0;
+        if (active) {
+            const int base = ((tid >> lo) << (lo + LOGE)) | (tid & ((1 << lo) - 1));
+            uint64_t v[E];
+#pragma unroll
+            for (int r = 0; r < E; r++) v[r] = s[padded(base + (r << lo))];
+#pragma unroll
+            for (int bit = LOGE - 1; bit >= 0; bit--) {
+                if (bit > b - lo) continue;
+#pragma unroll
+                for (int r = 0; r < E; r++) {
+                    if (r & (1 << bit)) continue;
+                    exchange_in_registers<E>(v, bit, r, !all_asc && (((base + (r << lo)) >> kb) & 1));
+                }
             }
+#pragma unroll
+            for (int r = 0; r < E; r++) s[padded(base + (r << lo))] = v[r];
         }
+        __syncthreads();
+        b = lo - 1;
     }
 }
 
-// Whole ascending sort of s[0..P), P a power of two.  Every step compares towards the same side (the
-// first step of a merge pairs mirrored positions), so padding with the largest word stays at the end.
-template <int NT>
-__device__ __forceinline__ void bitonic_sort_smem(uint64_t* s, int P, int tid) {
-    for (int k = 2; k <= P; k <<= 1) {
-        const int j = k >> 1;
-        group_sync<NT>();
-        for (int q = tid; q < (P >> 1); q += NT) {
-            const uint32_t i = pair_low(q, j), l = i ^ (uint32_t)(k - 1);
-            uint64_t a = s[i], b = s[l];
-            if (a > b) {
-                s[i] = b;
-                s[l] = a;
+// Whole ascending sort of the padded array of 1 << logP words (data in place, barrier passed), logP >= LOGE.
+template <int LOGE>
+__device__ __forceinline__ void blocked_sort(uint64_t* s, int tid, int logP) {
+    constexpr int E = 1 << LOGE;
+    if (tid < (1 << (logP - LOGE))) {   // phases 1 .. LOGE touch only the thread's own E consecutive words: one trip
+        const int base = tid << LOGE;
+        uint64_t v[E];
+#pragma unroll
+        for (int r = 0; r < E; r++) v[r] = s[padded(base + r)];
+#pragma unroll
+        for (int kb = 1; kb <= LOGE; kb++) {
+#pragma unroll
+            for (int bit = kb - 1; bit >= 0; bit--) {
+#pragma unroll
+                for (int r = 0; r < E; r++) {
+                    if (r & (1 << bit)) continue;
+                    exchange_in_registers<E>(v, bit, r, ((base + r) >> kb) & 1);
+                }
             }
         }
-        merge_tail_smem<NT>(s, P, j >> 1, tid);
+#pragma unroll
+        for (int r = 0; r < E; r++) s[padded(base + r)] = v[r];
     }
-    group_sync<NT>();
+    __syncthreads();
+    for (int kb = LOGE + 1; kb <= logP; kb++) blocked_steps<LOGE>(s, tid, logP, kb, kb - 1, false);
 }
 
-__device__ __forceinline__ int pow2_at_least(int n) {
-    int p = 1;
-    while (p < n) p <<= 1;
-    return p;
+// Loads seg[0..n) (padding with the largest word up to 1 << logP), sorts, hands the result out.
+template <int LOGE, int NT>
+__device__ __forceinline__ void sort_segment_in_smem(uint64_t* s, uint64_t* seg, uint32_t n, int logP, int32_t* ids_out,
+                                                     bool write_back, int tid) {
+    for (int i = tid; i < (1 << logP); i += NT) s[padded(i)] = ((uint32_t)i < n) ? seg[i] : ~0ull;
+    __syncthreads();
+    blocked_sort<LOGE>(s, tid, logP);
+    for (uint32_t i = tid; i < n; i += NT) {
+        const uint64_t x = s[padded((int)i)];
+        if (ids_out) ids_out[i] = (int32_t)(uint32_t)x;
+        if (write_back) seg[i] = x;
+    }
+    __syncthreads();
 }
 
-// One warp per tile.  Tiles longer than kTileSortShort are appended to `long_list` ([0] = count, [1] is
-// the long kernel's, then tile numbers) for tile_sort_long_kernel.
+__device__ __forceinline__ int log2_at_least(uint32_t n) {
+    int b = 0;
+    while ((1u << b) < n) b++;
+    return b;
+}
+
+// One CTA per four consecutive tiles.  First every warp rank-sorts its own tile if that has at most
+// kTileSortRank entries; then the whole CTA sorts, one after the other, those of its tiles that have up
+// to kTileSortShort.  Longer tiles are appended to `long_list` ([0] = count, [1] is the long kernel's,
+// then tile numbers) for tile_sort_long_kernel.
 __global__ void __launch_bounds__(kTileSortThreads) tile_sort_kernel(uint64_t* __restrict__ entries,
                                                                      const int32_t* __restrict__ offsets, int tiles,
                                                                      int32_t* __restrict__ sorted_ids,
                                                                      uint32_t* __restrict__ long_list,
                                                                      int write_back) {
-    __shared__ uint64_t s_all[kTileSortWarps][kTileSortShort];
+    __shared__ uint64_t s_all[kMidSmemWords];
+    __shared__ int s_beg[kTileSortWarps], s_n[kTileSortWarps];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int tile = blockIdx.x * kTileSortWarps + warp;
-    if (tile >= tiles) return;
-    uint64_t* s = s_all[warp];
-    const int edge = (lane < 2) ? offsets[tile + lane] : 0;
-    const int beg = __shfl_sync(0xffffffffu, edge, 0);
-    const int n = __shfl_sync(0xffffffffu, edge, 1) - beg;
-    if (n <= 0) return;
-    if (n > kTileSortShort) {
-        if (lane == 0) long_list[2 + atomicAdd(&long_list[0], 1u)] = (uint32_t)tile;
-        return;
+    int beg = 0, n = 0;
+    if (tile < tiles) {
+        const int edge = (lane < 2) ? offsets[tile + lane] : 0;
+        beg = __shfl_sync(0xffffffffu, edge, 0);
+        n = __shfl_sync(0xffffffffu, edge, 1) - beg;
     }
-    if (n <= kTileSortRank) {
+    if (lane == 0) {
+        s_beg[warp] = beg;
+        s_n[warp] = n;
+        if (n > kTileSortShort) long_list[2 + atomicAdd(&long_list[0], 1u)] = (uint32_t)tile;
+    }
+    if (n > 0 && n <= kTileSortRank) {
+        uint64_t* s = s_all + warp * kTileSortRank;
         constexpr int kPer = kTileSortRank / 32;
         uint64_t mine[kPer];
 #pragma unroll
@@ -121,14 +177,14 @@ __global__ void __launch_bounds__(kTileSortThreads) tile_sort_kernel(uint64_t* _
                 if (write_back) entries[beg + below[r]] = mine[r];
             }
         }
-        return;
     }
-    const int P = pow2_at_least(n);
-    for (int i = lane; i < P; i += 32) s[i] = (i < n) ? entries[beg + i] : ~0ull;
-    bitonic_sort_smem<32>(s, P, lane);
-    for (int i = lane; i < n; i += 32) {
-        sorted_ids[beg + i] = (int32_t)(uint32_t)s[i];
-        if (write_back) entries[beg + i] = s[i];
+    __syncthreads();
+#pragma unroll 1
+    for (int t = 0; t < kTileSortWarps; t++) {
+        const int nt = s_n[t];
+        if (nt <= kTileSortRank || nt > kTileSortShort) continue;   // uniform over the CTA
+        sort_segment_in_smem<3, kTileSortThreads>(s_all, entries + s_beg[t], (uint32_t)nt, log2_at_least((uint32_t)nt),
+                                                  sorted_ids + s_beg[t], write_back != 0, threadIdx.x);
     }
 }
 
@@ -144,94 +200,6 @@ __device__ __forceinline__ void global_step(uint64_t* seg, uint32_t n, uint32_t 
                 seg[l] = a;
             }
         }
-    }
-    __syncthreads();
-}
-
-// ---- register-blocked network for the long kernel --------------------------------------------------
-// The array of P = 1024 << LOGE words lives in shared memory with one spare word after every 16 (so that
-// a thread's 16 consecutive words do not fall on the banks of its neighbours').  A thread keeps
-// E = 1 << LOGE words in registers per round: the words whose indices differ only in LOGE chosen bits,
-// which lets it run up to LOGE steps of the network between two trips to shared memory.
-__device__ __forceinline__ int padded(int i) { return i + (i >> 4); }
-constexpr int kLongSmemWords = kTileSortChunk + (kTileSortChunk >> 4);
-
-// Steps for index bits b_top .. 0 of the phase that merges runs of 1 << kb words.  Direction of a pair:
-// ascending where bit kb of the index is clear (classic bitonic sort), always ascending with all_asc
-// (the merge tail of the all-ascending network used on segments that span several chunks).
-template <int LOGE>
-__device__ __forceinline__ void blocked_steps(uint64_t* s, int tid, int kb, int b_top, bool all_asc) {
-    constexpr int E = 1 << LOGE;
-    int b = b_top;
-    while (b >= 0) {
-        const int lo = (b - LOGE + 1 > 0) ? b - LOGE + 1 : 0;
-        const int base = ((tid >> lo) << (lo + LOGE)) | (tid & ((1 << lo) - 1));
-        uint64_t v[E];
-#pragma unroll
-        for (int r = 0; r < E; r++) v[r] = s[padded(base + (r << lo))];
-#pragma unroll
-        for (int bit = LOGE - 1; bit >= 0; bit--) {
-            if (bit > b - lo) continue;
-#pragma unroll
-            for (int r = 0; r < E; r++) {
-                if (r & (1 << bit)) continue;
-                const bool desc = !all_asc && (((base + (r << lo)) >> kb) & 1);
-                const uint64_t x = v[r], y = v[r | (1 << bit)];
-                const bool sw = (x > y) != desc;
-                v[r] = sw ? y : x;
-                v[r | (1 << bit)] = sw ? x : y;
-            }
-        }
-#pragma unroll
-        for (int r = 0; r < E; r++) s[padded(base + (r << lo))] = v[r];
-        __syncthreads();
-        b = lo - 1;
-    }
-}
-
-// Whole ascending sort of the padded array of 1024 << LOGE words (data in place, barrier passed).
-template <int LOGE>
-__device__ __forceinline__ void blocked_sort(uint64_t* s, int tid) {
-    constexpr int E = 1 << LOGE;
-    {   // phases 1 .. LOGE touch only the thread's own E consecutive words: one trip
-        const int base = tid << LOGE;
-        uint64_t v[E];
-#pragma unroll
-        for (int r = 0; r < E; r++) v[r] = s[padded(base + r)];
-#pragma unroll
-        for (int kb = 1; kb <= LOGE; kb++) {
-#pragma unroll
-            for (int bit = kb - 1; bit >= 0; bit--) {
-#pragma unroll
-                for (int r = 0; r < E; r++) {
-                    if (r & (1 << bit)) continue;
-                    const bool desc = ((base + r) >> kb) & 1;
-                    const uint64_t x = v[r], y = v[r | (1 << bit)];
-                    const bool sw = (x > y) != desc;
-                    v[r] = sw ? y : x;
-                    v[r | (1 << bit)] = sw ? x : y;
-                }
-            }
-        }
-#pragma unroll
-        for (int r = 0; r < E; r++) s[padded(base + r)] = v[r];
-        __syncthreads();
-    }
-    for (int kb = LOGE + 1; kb <= 10 + LOGE; kb++) blocked_steps<LOGE>(s, tid, kb, kb - 1, false);
-}
-
-// Loads seg[0..n) (padding with the largest word up to 1024 << LOGE), sorts, hands the result out.
-template <int LOGE>
-__device__ __forceinline__ void sort_segment_in_smem(uint64_t* s, uint64_t* seg, uint32_t n, int32_t* ids_out,
-                                                     bool write_back, int tid) {
-    constexpr int P = kTileSortLongThreads << LOGE;
-    for (int i = tid; i < P; i += kTileSortLongThreads) s[padded(i)] = ((uint32_t)i < n) ? seg[i] : ~0ull;
-    __syncthreads();
-    blocked_sort<LOGE>(s, tid);
-    for (uint32_t i = tid; i < n; i += kTileSortLongThreads) {
-        const uint64_t x = s[padded((int)i)];
-        if (ids_out) ids_out[i] = (int32_t)(uint32_t)x;
-        if (write_back) seg[i] = x;
     }
     __syncthreads();
 }
@@ -258,14 +226,12 @@ __global__ void __launch_bounds__(kTileSortLongThreads) tile_sort_long_kernel(ui
         const int beg = offsets[tile];
         const uint32_t n = (uint32_t)(offsets[tile + 1] - beg);
         uint64_t* seg = entries + beg;
-        if (n <= 2048u) {
-            sort_segment_in_smem<1>(s_long, seg, n, sorted_ids + beg, write_back, tid);
-        } else if (n <= 4096u) {
-            sort_segment_in_smem<2>(s_long, seg, n, sorted_ids + beg, write_back, tid);
-        } else if (n <= 8192u) {
-            sort_segment_in_smem<3>(s_long, seg, n, sorted_ids + beg, write_back, tid);
+        if (n <= 8192u) {            // 8 words per thread: 256, 512 or 1024 threads take part
+            sort_segment_in_smem<3, kTileSortLongThreads>(s_long, seg, n, log2_at_least(n), sorted_ids + beg,
+                                                          write_back != 0, tid);
         } else if (n <= (uint32_t)kTileSortChunk) {
-            sort_segment_in_smem<4>(s_long, seg, n, sorted_ids + beg, write_back, tid);
+            sort_segment_in_smem<4, kTileSortLongThreads>(s_long, seg, n, kLogChunk, sorted_ids + beg, write_back != 0,
+                                                          tid);
         } else {
             // Chunks sorted in shared memory; the steps wider than a chunk run on the segment in global
             // memory.  This network compares towards the same side everywhere (the first step of a merge
@@ -274,7 +240,7 @@ __global__ void __launch_bounds__(kTileSortLongThreads) tile_sort_long_kernel(ui
             while (P < n) P <<= 1;
             for (uint32_t base = 0; base < n; base += kTileSortChunk) {
                 const uint32_t m = (n - base < (uint32_t)kTileSortChunk) ? n - base : (uint32_t)kTileSortChunk;
-                sort_segment_in_smem<4>(s_long, seg + base, m, nullptr, true, tid);
+                sort_segment_in_smem<4, kTileSortLongThreads>(s_long, seg + base, m, kLogChunk, nullptr, true, tid);
             }
             for (uint32_t k = 2u * kTileSortChunk; k <= P && k != 0; k <<= 1) {
                 global_step<true>(seg, n, P, k >> 1, k, tid);
@@ -283,7 +249,7 @@ __global__ void __launch_bounds__(kTileSortLongThreads) tile_sort_long_kernel(ui
                     for (int i = tid; i < kTileSortChunk; i += kTileSortLongThreads)
                         s_long[padded(i)] = (base + i < n) ? seg[base + i] : ~0ull;
                     __syncthreads();
-                    blocked_steps<4>(s_long, tid, kLogChunk, kLogChunk - 1, true);
+                    blocked_steps<4>(s_long, tid, kLogChunk, kLogChunk, kLogChunk - 1, true);
                     for (int i = tid; i < kTileSortChunk; i += kTileSortLongThreads)
                         if (base + i < n) seg[base + i] = s_long[padded(i)];
                     __syncthreads();
