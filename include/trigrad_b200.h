@@ -116,8 +116,9 @@ int tg_tile_ranges(const uint64_t* sorted_keys, uint32_t n, int tiles, int32_t* 
  * are written to sorted_ids at the same positions.  A triangle occurs at most once per tile, so the
  * result equals the stable sort of (tile << 32 | depth) keys that
  * cub::DeviceSegmentedSort::StableSortPairs produces for entries emitted in triangle order
- * (src/trigrad/render.cu:272-284).  scratch: tg_tile_sort_scratch_bytes(tiles) bytes, 4-byte aligned;
- * need not be cleared.  No device-side waiting: segments of any length are handled by one CTA each.
+ * (src/trigrad/render.cu:272-284).  scratch: tg_tile_sort_scratch_bytes(tiles) bytes (work lists of the
+ * longer segments), 4-byte aligned; need not be cleared.  No device-side waiting: a segment of any length
+ * is handled by one warp or one CTA.
  */
 size_t tg_tile_sort_scratch_bytes(int tiles);
 int tg_sort_tile_lists(uint64_t* entries, const int32_t* offsets, int tiles, int32_t* sorted_ids, void* scratch,
@@ -172,10 +173,11 @@ int tg_blend_backward_l2(const float* tri_geo, const float* tri_attr, const int3
  *   selection    as for tg_blend_forward (may be NULL)
  *   sorted_ids   [list_capacity] int32   out, first K entries valid
  *   offsets      [tiles+1] int32         out
- *   info_host    uint32[2] in (preferably pinned) host memory.  [0] receives K; the call
- *                synchronises the stream once to read it (the reference does the same,
- *                src/trigrad/render.cu:290).  [1] receives the device error word (0 = fine) by an
- *                asynchronous copy: it is valid after the caller next synchronises the stream.
+ *   info_host    uint32[4] in (preferably pinned) host memory.  [0] receives K and [1] the length
+ *                of the longest tile list; the call synchronises the stream once to read them (the
+ *                reference does the same, src/trigrad/render.cu:290).  [2] receives the device error
+ *                word (0 = fine) by an asynchronous copy: it is valid after the caller next
+ *                synchronises the stream.  [3] is not used.
  *   stage_ms_host  NULL or float[5]: milliseconds of {init, per_tile_lists, sorting,
  *                bary_transforms, rasterization} measured with CUDA events (synchronises)
  * If K > list_capacity nothing past the scan is run and TG_ERR_CAPACITY is returned with info_host[0]

@@ -13,7 +13,7 @@ struct ForwardWorkspace {
     uint32_t* status;
     void* scan_scratch;        // fused preprocess + scan: ticket, finished-CTA counter, look-back words
     void* tile_scan_scratch;   // device-wide scan of the tile counts (only beyond kTileScanByLastCta tiles)
-    uint32_t* long_list;       // work list of the per-tile sort; only its first two words need clearing
+    uint32_t* long_list;       // work lists of the per-tile sort; only their four head words need clearing
     uint32_t* tile_cursor;     // [tiles]
     char* clear_end;
     size_t total;
@@ -25,14 +25,14 @@ struct ForwardWorkspace {
             off += align_up(bytes ? bytes : 1);
             return p;
         };
-        tri_offsets = (uint32_t*)take(sizeof(uint32_t) * ((size_t)T + 1));
+        tri_offsets = (uint32_t*)take(sizeof(uint32_t) * ((size_t)T + 2));   // [T] = K, [T+1] = longest tile list
         entries = (uint64_t*)take(sizeof(uint64_t) * (size_t)cap);
         status = (uint32_t*)take(sizeof(uint32_t) * 4);
         scan_scratch = take(tg_host::preprocess_scan_scratch_bytes(T));
         tile_scan_scratch = take(tiles > tg::kTileScanByLastCta ? tg_scan_scratch_bytes(tiles) : 0);
         tile_cursor = (uint32_t*)take(sizeof(uint32_t) * (size_t)tiles);
         long_list = (uint32_t*)take(tg_host::tile_sort_scratch_bytes(tiles));
-        clear_end = (char*)long_list + 2 * sizeof(uint32_t);
+        clear_end = (char*)long_list + 4 * sizeof(uint32_t);
         total = off;
     }
 };
@@ -96,6 +96,7 @@ int tg_render_forward(const float* vertices, const int32_t* indices, const float
     StageTimer timer(stage_ms_host != nullptr, s);
     info_host[0] = 0;
     info_host[1] = 0;
+    info_host[2] = 0;
 
     TG_REQUIRE(list_capacity == 0 || sorted_ids != nullptr, "null sorted_ids");
     cudaEvent_t k_ready;
@@ -111,7 +112,7 @@ int tg_render_forward(const float* vertices, const int32_t* indices, const float
                                       ws.tile_scan_scratch, s);
     if (st) return st;
     timer.mark();                                                    // [2] start of "per_tile_lists"
-    TG_CUDA(cudaMemcpyAsync(&info_host[0], ws.tri_offsets + T, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+    TG_CUDA(cudaMemcpyAsync(&info_host[0], ws.tri_offsets + T, 2 * sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
     TG_CUDA(cudaEventRecord(k_ready, s));
     // Entries are written while K travels to the host: the kernel drops those beyond the capacity, and
     // nothing that reads them is launched before K has been checked.
@@ -126,7 +127,7 @@ int tg_render_forward(const float* vertices, const int32_t* indices, const float
     }
     timer.mark();                                                    // [3] start of "sorting"
     if (K > 0) {
-        st = tg_host::sort_tile_lists(ws.entries, offsets, tiles, sorted_ids, ws.long_list, true, false, s);
+        st = tg_host::sort_tile_lists(ws.entries, offsets, tiles, sorted_ids, ws.long_list, true, false, info_host[1], s);
         if (st) return st;
     }
     timer.mark();                                                    // [4] start of "rasterization"
@@ -135,7 +136,7 @@ int tg_render_forward(const float* vertices, const int32_t* indices, const float
     if (st) return st;
     timer.mark();                                                    // [5] end
     // device error word: valid on the host once the stream has been synchronised
-    TG_CUDA(cudaMemcpyAsync(&info_host[1], ws.status, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+    TG_CUDA(cudaMemcpyAsync(&info_host[2], ws.status, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
     if (stage_ms_host) {
         TG_CUDA(cudaStreamSynchronize(s));
         float ms[5];
@@ -145,8 +146,8 @@ int tg_render_forward(const float* vertices, const int32_t* indices, const float
         stage_ms_host[2] = ms[3];   // sorting: per-tile sort
         stage_ms_host[3] = ms[1];   // bary_transforms: preprocess + scan + tile counts and offsets
         stage_ms_host[4] = ms[4];   // rasterization
-        if (info_host[1]) {
-            tg_host::set_error("device error word = %u", info_host[1]);
+        if (info_host[2]) {
+            tg_host::set_error("device error word = %u", info_host[2]);
             return TG_ERR_DEVICE_FLAG;
         }
     }

@@ -206,17 +206,18 @@ struct TileBinArgs {
     uint32_t* done;          // zero on entry: counts finished CTAs
     int tiles;
     int scan_here;           // 1: the last CTA scans the tile counts; 0: the host launches a scan
+    uint32_t* longest;       // written when scan_here: the largest tile count
 };
 
 // Exclusive scan of cursor[0..tiles) by one CTA of 256 threads, in place, copy in offsets[0..tiles].
 // Rounds of 2048 counts: coalesced loads into shared memory, eight consecutive counts per thread,
 // coalesced stores (a single SM issues too few memory requests per clock for anything strided).
 constexpr int kTileScanRound = 2048;
-__device__ void tile_offsets_by_one_cta(uint32_t* cursor, int32_t* offsets, int tiles, uint32_t* s_buf /*[2048]*/,
-                                        uint32_t* s_warp /*[8]*/) {
+__device__ void tile_offsets_by_one_cta(uint32_t* cursor, int32_t* offsets, int tiles, uint32_t* longest,
+                                        uint32_t* s_buf /*[2048]*/, uint32_t* s_warp /*[8]*/) {
     constexpr int kPer = kTileScanRound / 256;
     const int tid = threadIdx.x, warp = tid >> 5;
-    uint32_t carry = 0;
+    uint32_t carry = 0, biggest = 0;
     for (int base = 0; base < tiles; base += kTileScanRound) {
         __syncthreads();                      // s_buf and s_warp free again
 #pragma unroll
@@ -230,6 +231,7 @@ __device__ void tile_offsets_by_one_cta(uint32_t* cursor, int32_t* offsets, int 
         for (int k = 0; k < kPer; k++) {
             v[k] = s_buf[tid * kPer + k];
             mine += v[k];
+            biggest = max(biggest, v[k]);
         }
         uint32_t incl = mine;
 #pragma unroll
@@ -265,6 +267,15 @@ __device__ void tile_offsets_by_one_cta(uint32_t* cursor, int32_t* offsets, int 
         carry += total;
     }
     if (tid == 0) offsets[tiles] = (int32_t)carry;
+    biggest = __reduce_max_sync(0xffffffffu, biggest);
+    __syncthreads();
+    if (lane_id() == 0) s_warp[warp] = biggest;
+    __syncthreads();
+    if (tid == 0) {
+#pragma unroll
+        for (int w = 1; w < 8; w++) biggest = max(biggest, s_warp[w]);
+        *longest = biggest;
+    }
 }
 
 __global__ void __launch_bounds__(256, 6) preprocess_scan_kernel(const float4* __restrict__ vertices,
@@ -347,7 +358,7 @@ __global__ void __launch_bounds__(256, 6) preprocess_scan_kernel(const float4* _
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    tile_offsets_by_one_cta(bin.tile_cursor, bin.offsets, bin.tiles, s_buf, s_warp);
+    tile_offsets_by_one_cta(bin.tile_cursor, bin.offsets, bin.tiles, bin.longest, s_buf, s_warp);
 }
 
 // ================================================================================================
@@ -559,8 +570,9 @@ size_t preprocess_scan_scratch_bytes(int T) { return 8 + 8 * ((size_t)(T > 0 ? (
 
 // `scratch` (ticket, counter and partition words) and, when given, `tile_cursor[tiles]` must have been
 // zeroed by the caller.  With `tile_cursor` the tile offsets are produced as well (in `tile_cursor` itself
-// and in `offsets[tiles + 1]`); beyond kTileScanByLastCta tiles a device-wide scan does that, for which
-// `tile_scan_scratch` (zeroed, tg_scan_scratch_bytes(tiles) bytes) is needed.
+// and in `offsets[tiles + 1]`) and `tri_offsets` has T + 2 words: [T + 1] receives the longest tile list.
+// Beyond kTileScanByLastCta tiles a device-wide scan makes the offsets, for which `tile_scan_scratch`
+// (zeroed, tg_scan_scratch_bytes(tiles) bytes) is needed, and [T + 1] is set to UINT32_MAX (not known).
 int preprocess_scan(const float* vertices, const int32_t* indices, const float* colors, const float* opacities, int T,
                     int W, int H, int tw, int th, float* tri_geo, float* tri_attr, uint32_t* tri_offsets, void* scratch,
                     uint32_t* status, uint32_t* tile_cursor, int32_t* offsets, void* tile_scan_scratch,
@@ -570,7 +582,7 @@ int preprocess_scan(const float* vertices, const int32_t* indices, const float* 
     const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
     const int tiles = tiles_x * tiles_y;
     if (T == 0) {
-        TG_CUDA(cudaMemsetAsync(tri_offsets, 0, sizeof(uint32_t), stream));
+        TG_CUDA(cudaMemsetAsync(tri_offsets, 0, sizeof(uint32_t) * (tile_cursor ? 2 : 1), stream));
         if (tile_cursor) TG_CUDA(cudaMemsetAsync(offsets, 0, sizeof(int32_t) * ((size_t)tiles + 1), stream));
         return TG_OK;
     }
@@ -580,7 +592,8 @@ int preprocess_scan(const float* vertices, const int32_t* indices, const float* 
     TG_REQUIRE(!tile_cursor || offsets, "null offsets");
     const bool by_last_cta = tiles <= tg::kTileScanByLastCta;
     TG_REQUIRE(!tile_cursor || by_last_cta || tile_scan_scratch, "null tile scan scratch");
-    const tg::TileBinArgs bin = {tile_cursor, offsets, (uint32_t*)scratch + 1, tiles, by_last_cta ? 1 : 0};
+    const tg::TileBinArgs bin = {tile_cursor, offsets, (uint32_t*)scratch + 1, tiles, by_last_cta ? 1 : 0,
+                                 tri_offsets + T + 1};
     tg::preprocess_scan_kernel<<<(T + 255) / 256, 256, 0, stream>>>(
         (const float4*)vertices, indices, colors, opacities, T, W, H, tw, th, tiles_x, tiles_y, (float4*)tri_geo,
         (float4*)tri_attr, tri_offsets, (uint32_t*)scratch, (uint64_t*)((char*)scratch + 8), status, bin);
@@ -593,6 +606,7 @@ int preprocess_scan(const float* vertices, const int32_t* indices, const float* 
                                                                  (uint64_t*)((char*)tile_scan_scratch + 8), status);
         TG_LAUNCH_CHECK("scan_kernel");
         TG_CUDA(cudaMemcpyAsync(tile_cursor, offsets, sizeof(uint32_t) * (size_t)tiles, cudaMemcpyDeviceToDevice, stream));
+        TG_CUDA(cudaMemsetAsync(tri_offsets + T + 1, 0xff, sizeof(uint32_t), stream));
     }
     return TG_OK;
 }

@@ -98,6 +98,6 @@ int emit_entries(const float* vertices, const int32_t* indices, int T, int W, in
                  const uint32_t* tri_offsets, uint32_t* tile_cursor, uint64_t* entries, uint32_t capacity,
                  cudaStream_t stream);
 size_t tile_sort_scratch_bytes(int tiles);
-int sort_tile_lists(uint64_t* entries, const int32_t* offsets, int tiles, int32_t* sorted_ids, uint32_t* long_list,
-                    bool scratch_prepared, bool write_back, cudaStream_t stream);
+int sort_tile_lists(uint64_t* entries, const int32_t* offsets, int tiles, int32_t* sorted_ids, uint32_t* lists,
+                    bool scratch_prepared, bool write_back, uint32_t longest, cudaStream_t stream);
 }  // namespace tg_host

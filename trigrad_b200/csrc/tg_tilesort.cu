@@ -6,8 +6,8 @@
 // Entries are uint64 words (ordered depth << 32 | triangle), already grouped by tile:
 // tile t owns entries[offsets[t] .. offsets[t+1]).
 //   n <= 128     one warp per tile, rank sort: every element counts the smaller ones (no exchange steps)
-//   n <= 1024    the four warps of the CTA together: bitonic network in shared memory, 8 words per thread
-//                kept in registers between trips to shared memory
+//   n <= 1024    a CTA of 128 threads per tile (work list): bitonic network in shared memory, 8 words per
+//                thread kept in registers between trips to shared memory
 //   n <= 16384   the same network in 136 KB of shared memory, 1024 threads with 8 or 16 words each;
 //                tiles taken from a work list
 //   beyond       the same CTA sorts 16384-entry chunks in shared memory and runs the network's wide
@@ -125,66 +125,82 @@ __device__ __forceinline__ int log2_at_least(uint32_t n) {
     return b;
 }
 
-// One CTA per four consecutive tiles.  First every warp rank-sorts its own tile if that has at most
-// kTileSortRank entries; then the whole CTA sorts, one after the other, those of its tiles that have up
-// to kTileSortShort.  Longer tiles are appended to `long_list` ([0] = count, [1] is the long kernel's,
-// then tile numbers) for tile_sort_long_kernel.
+// Work lists in the sort's scratch: [0] long tiles, [1] next long item to hand out, [2] mid tiles,
+// [3] next mid item (all zero before tile_sort_kernel), then `tiles` slots of long items and `tiles`
+// slots of mid items.
+__device__ __forceinline__ uint32_t* long_items(uint32_t* lists) { return lists + 4; }
+__device__ __forceinline__ uint32_t* mid_items(uint32_t* lists, int tiles) { return lists + 4 + tiles; }
+
+// One warp per tile: rank sort of the tiles with at most kTileSortRank entries, the others go to the
+// work list of their length class.
 __global__ void __launch_bounds__(kTileSortThreads) tile_sort_kernel(uint64_t* __restrict__ entries,
                                                                      const int32_t* __restrict__ offsets, int tiles,
                                                                      int32_t* __restrict__ sorted_ids,
-                                                                     uint32_t* __restrict__ long_list,
-                                                                     int write_back) {
-    __shared__ uint64_t s_all[kMidSmemWords];
-    __shared__ int s_beg[kTileSortWarps], s_n[kTileSortWarps];
+                                                                     uint32_t* __restrict__ lists, int write_back) {
+    __shared__ uint64_t s_all[kTileSortWarps][kTileSortRank];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int tile = blockIdx.x * kTileSortWarps + warp;
-    int beg = 0, n = 0;
-    if (tile < tiles) {
-        const int edge = (lane < 2) ? offsets[tile + lane] : 0;
-        beg = __shfl_sync(0xffffffffu, edge, 0);
-        n = __shfl_sync(0xffffffffu, edge, 1) - beg;
-    }
-    if (lane == 0) {
-        s_beg[warp] = beg;
-        s_n[warp] = n;
-        if (n > kTileSortShort) long_list[2 + atomicAdd(&long_list[0], 1u)] = (uint32_t)tile;
-    }
-    if (n > 0 && n <= kTileSortRank) {
-        uint64_t* s = s_all + warp * kTileSortRank;
-        constexpr int kPer = kTileSortRank / 32;
-        uint64_t mine[kPer];
-#pragma unroll
-        for (int r = 0; r < kPer; r++) {
-            const int i = lane + r * 32;
-            mine[r] = (i < n) ? entries[beg + i] : ~0ull;
-            if (i < n) s[i] = mine[r];
+    if (tile >= tiles) return;
+    const int edge = (lane < 2) ? offsets[tile + lane] : 0;
+    const int beg = __shfl_sync(0xffffffffu, edge, 0);
+    const int n = __shfl_sync(0xffffffffu, edge, 1) - beg;
+    if (n <= 0) return;
+    if (n > kTileSortRank) {
+        if (lane == 0) {
+            if (n > kTileSortShort) long_items(lists)[atomicAdd(&lists[0], 1u)] = (uint32_t)tile;
+            else mid_items(lists, tiles)[atomicAdd(&lists[2], 1u)] = (uint32_t)tile;
         }
-        __syncwarp();
-        int below[kPer] = {};
-        if (n <= 32) {
-            for (int j = 0; j < n; j++) below[0] += (s[j] < mine[0]) ? 1 : 0;
-        } else {
-            for (int j = 0; j < n; j++) {
-                const uint64_t other = s[j];
+        return;
+    }
+    uint64_t* s = s_all[warp];
+    constexpr int kPer = kTileSortRank / 32;
+    uint64_t mine[kPer];
 #pragma unroll
-                for (int r = 0; r < kPer; r++) below[r] += (other < mine[r]) ? 1 : 0;
-            }
-        }
+    for (int r = 0; r < kPer; r++) {
+        const int i = lane + r * 32;
+        mine[r] = (i < n) ? entries[beg + i] : ~0ull;
+        if (i < n) s[i] = mine[r];
+    }
+    __syncwarp();
+    int below[kPer] = {};
+    if (n <= 32) {
+        for (int j = 0; j < n; j++) below[0] += (s[j] < mine[0]) ? 1 : 0;
+    } else {
+        for (int j = 0; j < n; j++) {
+            const uint64_t other = s[j];
 #pragma unroll
-        for (int r = 0; r < kPer; r++) {
-            if (lane + r * 32 < n) {
-                sorted_ids[beg + below[r]] = (int32_t)(uint32_t)mine[r];
-                if (write_back) entries[beg + below[r]] = mine[r];
-            }
+            for (int r = 0; r < kPer; r++) below[r] += (other < mine[r]) ? 1 : 0;
         }
     }
-    __syncthreads();
-#pragma unroll 1
-    for (int t = 0; t < kTileSortWarps; t++) {
-        const int nt = s_n[t];
-        if (nt <= kTileSortRank || nt > kTileSortShort) continue;   // uniform over the CTA
-        sort_segment_in_smem<3, kTileSortThreads>(s_all, entries + s_beg[t], (uint32_t)nt, log2_at_least((uint32_t)nt),
-                                                  sorted_ids + s_beg[t], write_back != 0, threadIdx.x);
+#pragma unroll
+    for (int r = 0; r < kPer; r++) {
+        if (lane + r * 32 < n) {
+            sorted_ids[beg + below[r]] = (int32_t)(uint32_t)mine[r];
+            if (write_back) entries[beg + below[r]] = mine[r];
+        }
+    }
+}
+
+// Tiles of kTileSortRank < n <= kTileSortShort entries: persistent CTAs of 128 threads, next free item first.
+__global__ void __launch_bounds__(kTileSortThreads) tile_sort_mid_kernel(uint64_t* entries,
+                                                                         const int32_t* __restrict__ offsets, int tiles,
+                                                                         int32_t* __restrict__ sorted_ids, uint32_t* lists,
+                                                                         int write_back) {
+    __shared__ uint64_t s_mid[kMidSmemWords];
+    __shared__ uint32_t s_item;
+    const int tid = threadIdx.x;
+    const uint32_t count = lists[2];
+    while (true) {
+        if (tid == 0) s_item = atomicAdd(&lists[3], 1u);
+        __syncthreads();
+        const uint32_t w = s_item;
+        __syncthreads();
+        if (w >= count) break;
+        const int tile = (int)mid_items(lists, tiles)[w];
+        const int beg = offsets[tile];
+        const uint32_t n = (uint32_t)(offsets[tile + 1] - beg);
+        sort_segment_in_smem<3, kTileSortThreads>(s_mid, entries + beg, n, log2_at_least(n), sorted_ids + beg,
+                                                  write_back != 0, tid);
     }
 }
 
@@ -205,24 +221,23 @@ __device__ __forceinline__ void global_step(uint64_t* seg, uint32_t n, uint32_t 
 }
 
 // Persistent CTAs (one per SM) take the long tiles from the work list, next free item first.
-// long_list: [0] number of items, [1] next item to hand out (both zero before tile_sort_kernel), items.
 __global__ void __launch_bounds__(kTileSortLongThreads) tile_sort_long_kernel(uint64_t* entries,
                                                                               const int32_t* __restrict__ offsets,
                                                                               int32_t* __restrict__ sorted_ids,
-                                                                              uint32_t* long_list, int write_back) {
+                                                                              uint32_t* lists, int write_back) {
     extern __shared__ __align__(16) uint64_t s_long[];
     __shared__ uint32_t s_item;
     constexpr int kLogChunk = 14;
     static_assert((1 << kLogChunk) == kTileSortChunk && kTileSortLongThreads == 1024, "chunk = 1024 threads x 16 words");
     const int tid = threadIdx.x;
-    const uint32_t count = long_list[0];
+    const uint32_t count = lists[0];
     while (true) {
-        if (tid == 0) s_item = atomicAdd(&long_list[1], 1u);
+        if (tid == 0) s_item = atomicAdd(&lists[1], 1u);
         __syncthreads();
         const uint32_t w = s_item;
         __syncthreads();
         if (w >= count) break;
-        const int tile = (int)long_list[2 + w];
+        const int tile = (int)long_items(lists)[w];
         const int beg = offsets[tile];
         const uint32_t n = (uint32_t)(offsets[tile + 1] - beg);
         uint64_t* seg = entries + beg;
@@ -265,33 +280,43 @@ __global__ void __launch_bounds__(kTileSortLongThreads) tile_sort_long_kernel(ui
 
 namespace tg_host {
 
-size_t tile_sort_scratch_bytes(int tiles) { return sizeof(uint32_t) * ((size_t)(tiles > 0 ? tiles : 0) + 2); }
+size_t tile_sort_scratch_bytes(int tiles) { return sizeof(uint32_t) * (2 * (size_t)(tiles > 0 ? tiles : 0) + 4); }
 
-// `scratch_prepared`: the caller has zeroed the first two words of `long_list`.
-int sort_tile_lists(uint64_t* entries, const int32_t* offsets, int tiles, int32_t* sorted_ids, uint32_t* long_list,
-                    bool scratch_prepared, bool write_back, cudaStream_t s) {
+// `scratch_prepared`: the caller has zeroed the first four words of `lists`.  `longest`: an upper bound
+// of the longest tile list when the caller knows one (the kernels of the length classes above it are
+// not launched), UINT32_MAX otherwise.
+int sort_tile_lists(uint64_t* entries, const int32_t* offsets, int tiles, int32_t* sorted_ids, uint32_t* lists,
+                    bool scratch_prepared, bool write_back, uint32_t longest, cudaStream_t s) {
     TG_REQUIRE(tiles >= 0, "tiles < 0");
     if (tiles == 0) return TG_OK;
-    TG_REQUIRE(entries && offsets && sorted_ids && long_list, "null pointer");
-    constexpr int kMaxDevices = 64;
-    static bool attr_set[kMaxDevices] = {};
-    const size_t long_smem = sizeof(uint64_t) * tg::kLongSmemWords;
-    int dev = 0;
-    TG_CUDA(cudaGetDevice(&dev));
-    TG_REQUIRE(dev >= 0 && dev < kMaxDevices, "device index outside the supported range");
-    if (!attr_set[dev]) {
-        TG_CUDA(cudaFuncSetAttribute(tg::tile_sort_long_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)long_smem));
-        attr_set[dev] = true;
-    }
-    if (!scratch_prepared) TG_CUDA(cudaMemsetAsync(long_list, 0, 2 * sizeof(uint32_t), s));
+    TG_REQUIRE(entries && offsets && sorted_ids && lists, "null pointer");
+    if (!scratch_prepared) TG_CUDA(cudaMemsetAsync(lists, 0, 4 * sizeof(uint32_t), s));
     tg::tile_sort_kernel<<<(tiles + tg::kTileSortWarps - 1) / tg::kTileSortWarps, tg::kTileSortThreads, 0, s>>>(
-        entries, offsets, tiles, sorted_ids, long_list, write_back ? 1 : 0);
+        entries, offsets, tiles, sorted_ids, lists, write_back ? 1 : 0);
     TG_LAUNCH_CHECK("tile_sort_kernel");
-    const int grid = tiles < 148 ? tiles : 148;
-    tg::tile_sort_long_kernel<<<grid, tg::kTileSortLongThreads, long_smem, s>>>(entries, offsets, sorted_ids, long_list,
-                                                                                 write_back ? 1 : 0);
-    TG_LAUNCH_CHECK("tile_sort_long_kernel");
+    if (longest > (uint32_t)tg::kTileSortRank) {
+        const int grid = tiles < 148 * 12 ? tiles : 148 * 12;
+        tg::tile_sort_mid_kernel<<<grid, tg::kTileSortThreads, 0, s>>>(entries, offsets, tiles, sorted_ids, lists,
+                                                                        write_back ? 1 : 0);
+        TG_LAUNCH_CHECK("tile_sort_mid_kernel");
+    }
+    if (longest > (uint32_t)tg::kTileSortShort) {
+        constexpr int kMaxDevices = 64;
+        static bool attr_set[kMaxDevices] = {};
+        const size_t long_smem = sizeof(uint64_t) * tg::kLongSmemWords;
+        int dev = 0;
+        TG_CUDA(cudaGetDevice(&dev));
+        TG_REQUIRE(dev >= 0 && dev < kMaxDevices, "device index outside the supported range");
+        if (!attr_set[dev]) {
+            TG_CUDA(cudaFuncSetAttribute(tg::tile_sort_long_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)long_smem));
+            attr_set[dev] = true;
+        }
+        const int grid = tiles < 148 ? tiles : 148;
+        tg::tile_sort_long_kernel<<<grid, tg::kTileSortLongThreads, long_smem, s>>>(entries, offsets, sorted_ids, lists,
+                                                                                     write_back ? 1 : 0);
+        TG_LAUNCH_CHECK("tile_sort_long_kernel");
+    }
     return TG_OK;
 }
 
@@ -309,7 +334,7 @@ int tg_sort_tile_lists(uint64_t* entries, const int32_t* offsets, int tiles, int
         return TG_ERR_WORKSPACE;
     }
     TG_REQUIRE(((uintptr_t)scratch & 3) == 0 && ((uintptr_t)entries & 7) == 0, "alignment");
-    return tg_host::sort_tile_lists(entries, offsets, tiles, sorted_ids, (uint32_t*)scratch, false, true,
+    return tg_host::sort_tile_lists(entries, offsets, tiles, sorted_ids, (uint32_t*)scratch, false, true, UINT32_MAX,
                                     (cudaStream_t)stream);
 }
 

@@ -32,16 +32,16 @@ class _DeviceState:
     def __init__(self, device: torch.device):
         self.device = device
         self.workspace = torch.empty(0, dtype=torch.uint8, device=device)
-        self.info = torch.zeros((self.SLOTS, 2), dtype=torch.int32).pin_memory()
+        self.info = torch.zeros((self.SLOTS, 4), dtype=torch.int32).pin_memory()   # K, longest list, error word, -
         self.slot = 0
         self.k_estimate = 0
 
     def next_slot(self) -> int:
         s = self.slot
         self.slot = (self.slot + 1) % self.SLOTS
-        stale = int(self.info[s, 1])
+        stale = int(self.info[s, 2])
         if stale:
-            self.info[s, 1] = 0
+            self.info[s, 2] = 0
             raise RuntimeError(f"trigrad_b200: an earlier render reported device error word {stale} "
                                "(a bounded wait ran out inside a kernel)")
         return s
