@@ -28,14 +28,16 @@ constexpr int kTileSortChunk = 16384;
 __device__ __forceinline__ uint32_t pair_low(uint32_t q, uint32_t j) { return ((q & ~(j - 1)) << 1) | (q & (j - 1)); }
 
 // ---- register-blocked bitonic network -----------------------------------------------------------------
-// The array of P = 1 << logP words lives in shared memory with one spare word after every 16 (so that
-// the consecutive words of one thread do not fall on the banks of its neighbours').  P >> LOGE threads
-// take part; each keeps E = 1 << LOGE words in registers per round - the words whose indices differ
-// only in LOGE chosen bits - and so runs up to LOGE steps of the network between two trips to shared
-// memory.  Every thread of the CTA must call (barriers inside).
-__device__ __forceinline__ int padded(int i) { return i + (i >> 4); }
-constexpr int kMidSmemWords = kTileSortShort + (kTileSortShort >> 4);
-constexpr int kLongSmemWords = kTileSortChunk + (kTileSortChunk >> 4);
+// The array of P = 1 << logP words lives in shared memory.  P >> LOGE threads take part; each keeps
+// E = 1 << LOGE words in registers per round - the words whose indices differ only in LOGE chosen
+// bits [LO, LO + LOGE) - and so runs up to LOGE steps of the network between two trips to shared memory.
+// One spare word after every E keeps the rounds free of bank conflicts: for a fixed register slot the
+// sixteen lanes of a half-warp then fall on sixteen different 8-byte banks whatever LO is.
+// Every thread of the CTA must call (barriers inside).
+template <int LOGE>
+__device__ __forceinline__ int padded(int i) { return i + (i >> LOGE); }
+constexpr int kMidSmemWords = kTileSortShort + (kTileSortShort >> 3);
+constexpr int kLongSmemWords = kTileSortChunk + (kTileSortChunk >> 3);   // covers 8192 + 8192/8 and 16384 + 16384/16
 
 template <int E>
 __device__ __forceinline__ void exchange_in_registers(uint64_t (&v)[E], int bit, int r, bool desc) {
@@ -45,47 +47,82 @@ __device__ __forceinline__ void exchange_in_registers(uint64_t (&v)[E], int bit,
     v[r | (1 << bit)] = sw ? x : y;
 }
 
-// Steps for index bits b_top .. 0 of the phase that merges runs of 1 << kb words.  Direction of a pair:
-// ascending where bit kb of the index is clear (classic bitonic sort), always ascending with all_asc
-// (the merge tail of the all-ascending network used on segments that span several chunks).
+// One round: index bits [LO, LO + LOGE) in registers, steps for the NB highest... lowest of them
+// (NB == LOGE except in the last round of a phase, where LO == 0 and only bits NB-1 .. 0 remain).
+// LO and NB are compile-time so that all shared-memory offsets are immediates.
+template <int LOGE, int LO, int NB>
+__device__ __forceinline__ void blocked_round(uint64_t* s, int tid, bool desc) {
+    constexpr int E = 1 << LOGE;
+    const int base = ((tid >> LO) << (LO + LOGE)) | (tid & ((1 << LO) - 1));
+    // base has zero bits in [LO, LO + LOGE): padded(base + (r << LO)) = padded(base) + (r << LO) + ((r << LO) >> LOGE)
+    uint64_t* p = s + padded<LOGE>(base);
+    uint64_t v[E];
+#pragma unroll
+    for (int r = 0; r < E; r++) v[r] = p[(r << LO) + ((r << LO) >> LOGE)];
+#pragma unroll
+    for (int bit = NB - 1; bit >= 0; bit--) {
+#pragma unroll
+        for (int r = 0; r < E; r++) {
+            if (r & (1 << bit)) continue;
+            exchange_in_registers<E>(v, bit, r, desc);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < E; r++) p[(r << LO) + ((r << LO) >> LOGE)] = v[r];
+}
+
+template <int LOGE, int LO>
+__device__ __forceinline__ void blocked_round_lo(uint64_t* s, int tid, int lo, bool desc) {
+    if constexpr (LO > 14 - LOGE) {
+        return;                               // logP <= 14: no round starts higher
+    } else {
+        if (lo == LO) blocked_round<LOGE, LO, LOGE>(s, tid, desc);
+        else blocked_round_lo<LOGE, LO + 1>(s, tid, lo, desc);
+    }
+}
+
+template <int LOGE, int NB>
+__device__ __forceinline__ void blocked_round_last(uint64_t* s, int tid, int nb, bool desc) {
+    if constexpr (NB > LOGE) {
+        return;
+    } else {
+        if (nb == NB) blocked_round<LOGE, 0, NB>(s, tid, desc);
+        else blocked_round_last<LOGE, NB + 1>(s, tid, nb, desc);
+    }
+}
+
+// Steps for index bits b_top .. 0 of the phase that merges runs of 1 << kb words (kb > LOGE).  Direction
+// of a pair: ascending where bit kb of the index is clear (classic bitonic sort), always ascending with
+// all_asc (the merge tail of the all-ascending network used on segments that span several chunks).
 template <int LOGE>
 __device__ __forceinline__ void blocked_steps(uint64_t* s, int tid, int logP, int kb, int b_top, bool all_asc) {
-    constexpr int E = 1 << LOGE;
     const bool active = tid < (1 << (logP - LOGE));
     int b = b_top;
     while (b >= 0) {
         const int lo = (b - LOGE + 1 > 0) ? b - LOGE + 1 : 0;
         if (active) {
+            // bit kb lies above the bits held in registers: one direction per thread and round
             const int base = ((tid >> lo) << (lo + LOGE)) | (tid & ((1 << lo) - 1));
-            uint64_t v[E];
-#pragma unroll
-            for (int r = 0; r < E; r++) v[r] = s[padded(base + (r << lo))];
-#pragma unroll
-            for (int bit = LOGE - 1; bit >= 0; bit--) {
-                if (bit > b - lo) continue;
-#pragma unroll
-                for (int r = 0; r < E; r++) {
-                    if (r & (1 << bit)) continue;
-                    exchange_in_registers<E>(v, bit, r, !all_asc && (((base + (r << lo)) >> kb) & 1));
-                }
-            }
-#pragma unroll
-            for (int r = 0; r < E; r++) s[padded(base + (r << lo))] = v[r];
+            const bool desc = !all_asc && ((base >> kb) & 1);
+            if (lo > 0) blocked_round_lo<LOGE, 1>(s, tid, lo, desc);
+            else blocked_round_last<LOGE, 1>(s, tid, b + 1, desc);
         }
         __syncthreads();
         b = lo - 1;
     }
 }
 
-// Whole ascending sort of the padded array of 1 << logP words (data in place, barrier passed), logP >= LOGE.
+// Whole ascending sort of the padded array of 1 << logP words (data in place, barrier passed),
+// LOGE <= logP <= 14.
 template <int LOGE>
 __device__ __forceinline__ void blocked_sort(uint64_t* s, int tid, int logP) {
     constexpr int E = 1 << LOGE;
     if (tid < (1 << (logP - LOGE))) {   // phases 1 .. LOGE touch only the thread's own E consecutive words: one trip
         const int base = tid << LOGE;
+        uint64_t* p = s + padded<LOGE>(base);
         uint64_t v[E];
 #pragma unroll
-        for (int r = 0; r < E; r++) v[r] = s[padded(base + r)];
+        for (int r = 0; r < E; r++) v[r] = p[r];
 #pragma unroll
         for (int kb = 1; kb <= LOGE; kb++) {
 #pragma unroll
@@ -98,7 +135,7 @@ __device__ __forceinline__ void blocked_sort(uint64_t* s, int tid, int logP) {
             }
         }
 #pragma unroll
-        for (int r = 0; r < E; r++) s[padded(base + r)] = v[r];
+        for (int r = 0; r < E; r++) p[r] = v[r];
     }
     __syncthreads();
     for (int kb = LOGE + 1; kb <= logP; kb++) blocked_steps<LOGE>(s, tid, logP, kb, kb - 1, false);
@@ -108,11 +145,11 @@ __device__ __forceinline__ void blocked_sort(uint64_t* s, int tid, int logP) {
 template <int LOGE, int NT>
 __device__ __forceinline__ void sort_segment_in_smem(uint64_t* s, uint64_t* seg, uint32_t n, int logP, int32_t* ids_out,
                                                      bool write_back, int tid) {
-    for (int i = tid; i < (1 << logP); i += NT) s[padded(i)] = ((uint32_t)i < n) ? seg[i] : ~0ull;
+    for (int i = tid; i < (1 << logP); i += NT) s[padded<LOGE>(i)] = ((uint32_t)i < n) ? seg[i] : ~0ull;
     __syncthreads();
     blocked_sort<LOGE>(s, tid, logP);
     for (uint32_t i = tid; i < n; i += NT) {
-        const uint64_t x = s[padded((int)i)];
+        const uint64_t x = s[padded<LOGE>((int)i)];
         if (ids_out) ids_out[i] = (int32_t)(uint32_t)x;
         if (write_back) seg[i] = x;
     }
@@ -262,11 +299,11 @@ __global__ void __launch_bounds__(kTileSortLongThreads) tile_sort_long_kernel(ui
                 for (uint32_t j = k >> 2; j >= (uint32_t)kTileSortChunk; j >>= 1) global_step<false>(seg, n, P, j, k, tid);
                 for (uint32_t base = 0; base < n; base += kTileSortChunk) {
                     for (int i = tid; i < kTileSortChunk; i += kTileSortLongThreads)
-                        s_long[padded(i)] = (base + i < n) ? seg[base + i] : ~0ull;
+                        s_long[padded<4>(i)] = (base + i < n) ? seg[base + i] : ~0ull;
                     __syncthreads();
                     blocked_steps<4>(s_long, tid, kLogChunk, kLogChunk, kLogChunk - 1, true);
                     for (int i = tid; i < kTileSortChunk; i += kTileSortLongThreads)
-                        if (base + i < n) seg[base + i] = s_long[padded(i)];
+                        if (base + i < n) seg[base + i] = s_long[padded<4>(i)];
                     __syncthreads();
                 }
             }
