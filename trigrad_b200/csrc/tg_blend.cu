@@ -251,7 +251,7 @@ __device__ __forceinline__ void store_pixel(const TileCtx& c, const BlendParams&
 // sel: optional [planes][H*W] int32; plane k of a pixel receives the triangle id of its k-th blended
 // fragment (k < ends).  Only written when it is not null (per-pixel mode, max_layers <= 32).
 template <bool SORT, int MAXT>
-__global__ void __launch_bounds__(MAXT) blend_forward_kernel(BlendParams P, float4* __restrict__ image,
+__global__ void __launch_bounds__(MAXT, MAXT <= 256 ? 5 : 1) blend_forward_kernel(BlendParams P, float4* __restrict__ image,
                                                              float* __restrict__ depthmap, float* __restrict__ final_w,
                                                              int* __restrict__ ends, int* __restrict__ sel) {
     __shared__ float4 s_geo[kChunk * 4];
