@@ -556,6 +556,213 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 256 ? 4 : 1) blend_backward_save
     }
 }
 
+// ---- default mode, two-part gradient with a per-warp queue ------------------------------------------
+// The pixels of a warp blend different numbers of fragments (on average fewer than half the lanes have
+// one in a given round), and only the transmittance recurrence ties a pixel's fragments together.  So
+// the work is split: part A (per pixel, back to front) runs the recurrence and produces the upstream
+// gradients of the fragment's interpolations; these go into a queue in shared memory; part B (the
+// expensive barycentric partials and the 21 per-vertex outputs) pops 32 queued fragments at a time and
+// so runs with full warps.  The arithmetic per fragment is that of backward_one.
+struct QueuedFragment {
+    float px, py;
+    int id;
+    float bx, by, bz;
+    float o_raw, cr, cg, cb, z;
+    float uo, ur, ug, ub, uz;
+};
+constexpr int kQueueFields = 16, kQueueSlots = 64;
+
+// Part A: render.cu:455-538 up to the upstream gradients; updates the pixel's running state.
+__device__ __forceinline__ void backward_state(const float* w, const AttrRec& a, const Bary& b, const PixelGrad& pg,
+                                               BackState& st, QueuedFragment& f) {
+    const float bw0 = b.x * w[0], bw1 = b.y * w[1], bw2 = b.z * w[2];
+    const float den = bw0 + bw1 + bw2;
+    const bool ok = !(den * den < kEffZero);
+    const float inv = rcp_fast(den);
+    const float o_raw = (bw0 * a.o[0] + bw1 * a.o[1] + bw2 * a.o[2]) * inv;
+    const float o = fminf(fmaxf(o_raw, 0.f), kMaxOpacity);
+    const float cr = (bw0 * a.c[0] + bw1 * a.c[3] + bw2 * a.c[6]) * inv;
+    const float cg = (bw0 * a.c[1] + bw1 * a.c[4] + bw2 * a.c[7]) * inv;
+    const float cb = (bw0 * a.c[2] + bw1 * a.c[5] + bw2 * a.c[8]) * inv;
+    const float denz = b.x + b.y + b.z;
+    const bool okz = !(denz * denz < kEffZero);
+    const float invz = rcp_fast(denz);
+    const float z = (b.x * a.iw[0] + b.y * a.iw[1] + b.z * a.iw[2]) * invz;
+    const float iom = rcp_fast(1.f - o);
+
+    const float drgb_do = ((cr * st.alpha - st.sr) * pg.gr + (cg * st.alpha - st.sg) * pg.gg + (cb * st.alpha - st.sb) * pg.gb -
+                           pg.ga * pg.final_alpha) * iom;
+    st.alpha = st.alpha * iom;
+    const float ao = st.alpha * o;
+    st.sr += cr * ao;
+    st.sg += cg * ao;
+    st.sb += cb * ao;
+    const float ddw_do = st.alpha - st.oa * iom;
+    const float dud_do = st.alpha * z - st.zoa * iom;
+    st.oa += ao;
+    st.zoa += z * ao;
+    const bool has_w = !(pg.final_weight < kEffZero);
+    const float inv_fw = has_w ? rcp_fast(pg.final_weight) : 0.f;
+    const float dd_do = (dud_do - pg.final_depth * ddw_do) * inv_fw * pg.gd;
+    const float d_do = drgb_do + (has_w ? dd_do : 0.f);
+
+    f.bx = b.x; f.by = b.y; f.bz = b.z;
+    f.o_raw = o_raw; f.cr = cr; f.cg = cg; f.cb = cb; f.z = z;
+    f.uo = ok ? d_do * inv : 0.f;
+    f.ur = ok ? ao * pg.gr * inv : 0.f;
+    f.ug = ok ? ao * pg.gg * inv : 0.f;
+    f.ub = ok ? ao * pg.gb * inv : 0.f;
+    f.uz = (okz && has_w) ? ao * pg.gd * inv_fw * invz : 0.f;
+}
+
+// Part B: from the upstream gradients to the contribution for the triangle's three vertices.
+__device__ __forceinline__ void backward_outputs(const float* w, const AttrRec& a, const QueuedFragment& f, Contrib& out) {
+    const float uo = f.uo, ur = f.ur, ug = f.ug, ub = f.ub, uz = f.uz;
+    const float e0 = uo * (a.o[0] - f.o_raw) + ur * (a.c[0] - f.cr) + ug * (a.c[1] - f.cg) + ub * (a.c[2] - f.cb);
+    const float e1 = uo * (a.o[1] - f.o_raw) + ur * (a.c[3] - f.cr) + ug * (a.c[4] - f.cg) + ub * (a.c[5] - f.cb);
+    const float e2 = uo * (a.o[2] - f.o_raw) + ur * (a.c[6] - f.cr) + ug * (a.c[7] - f.cg) + ub * (a.c[8] - f.cb);
+    const float iw0 = a.iw[0], iw1 = a.iw[1], iw2 = a.iw[2];
+    const float z0 = uz * (iw0 - f.z), z1 = uz * (iw1 - f.z), z2 = uz * (iw2 - f.z);
+    const float g0 = w[0] * e0 + z0, g1 = w[1] * e1 + z1, g2 = w[2] * e2 + z2;
+    const float gw0 = f.bx * e0 + f.bx * z0 - uz * f.bx * iw0 * iw0;
+    const float gw1 = f.by * e1 + f.by * z1 - uz * f.by * iw1 * iw1;
+    const float gw2 = f.bz * e2 + f.bz * z2 - uz * f.bz * iw2 * iw2;
+    const float px = f.px, py = f.py;
+    const float ax = a.xy[0], ay = a.xy[1], bx = a.xy[2], by = a.xy[3], cx = a.xy[4], cy = a.xy[5];
+    float gxy[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const float d = ax * (by - cy) + bx * (-ay + cy) + cx * (ay - by);
+    if (!(fabsf(d) < kEffZero)) {
+        const float iT = rcp_fast((bx - ax) * (cy - ay) - (by - ay) * (cx - ax));
+        const float lx = ((bx - px) * (cy - py) - (by - py) * (cx - px)) * iT;
+        const float ly = ((cx - px) * (ay - py) - (cy - py) * (ax - px)) * iT;
+        const float lz = ((ax - px) * (by - py) - (ay - py) * (bx - px)) * iT;
+        const float id = rcp_fast(d);
+        gxy[0] = (g0 * (lx * (-by + cy)) + g1 * (-cy - ly * (by - cy) + py) + g2 * (by - lz * (by - cy) - py)) * id;
+        gxy[1] = (g0 * (lx * (bx - cx)) + g1 * (cx + ly * (bx - cx) - px) + g2 * (-bx + lz * (bx - cx) + px)) * id;
+        gxy[2] = (g0 * (cy + lx * (ay - cy) - py) + g1 * (ly * (ay - cy)) + g2 * (-ay + lz * (ay - cy) + py)) * id;
+        gxy[3] = (g0 * (-cx - lx * (ax - cx) + px) + g1 * (ly * (-ax + cx)) + g2 * (ax - lz * (ax - cx) - px)) * id;
+        gxy[4] = (g0 * (-by - lx * (ay - by) + py) + g1 * (ay - ly * (ay - by) - py) + g2 * (lz * (-ay + by))) * id;
+        gxy[5] = (g0 * (bx + lx * (ax - bx) - px) + g1 * (-ax + ly * (ax - bx) + px) + g2 * (lz * (ax - bx))) * id;
+    }
+    const float gw[3] = {gw0, gw1, gw2}, bwk[3] = {f.bx * w[0], f.by * w[1], f.bz * w[2]};
+#pragma unroll
+    for (int k = 0; k < 3; k++) {
+        out.vid[k] = a.vid[k];
+        out.v[k][0] = gxy[2 * k];
+        out.v[k][1] = gxy[2 * k + 1];
+        out.v[k][2] = gw[k];
+        out.v[k][3] = uo * bwk[k];
+        out.v[k][4] = ur * bwk[k];
+        out.v[k][5] = ug * bwk[k];
+        out.v[k][6] = ub * bwk[k];
+    }
+}
+
+// Part B for the fragments in queue slots first .. first + count - 1 (count <= 32), one per lane.
+// Consecutive slots that hold the same triangle (neighbouring pixels mostly do) are summed over runs of
+// up to eight with three shuffle rounds before the vector reductions are issued.
+__device__ __forceinline__ void drain_queue(const BlendParams& P, float (*q)[kQueueSlots], int first, int count,
+                                            float4* __restrict__ gpack) {
+    const int lane = lane_id();
+    const bool valid = lane < count;
+    QueuedFragment f;
+    const int slot = first + (valid ? lane : 0);
+    f.px = q[0][slot]; f.py = q[1][slot]; f.id = __float_as_int(q[2][slot]);
+    f.bx = q[3][slot]; f.by = q[4][slot]; f.bz = q[5][slot];
+    f.o_raw = q[6][slot]; f.cr = q[7][slot]; f.cg = q[8][slot]; f.cb = q[9][slot]; f.z = q[10][slot];
+    f.uo = q[11][slot]; f.ur = q[12][slot]; f.ug = q[13][slot]; f.ub = q[14][slot]; f.uz = q[15][slot];
+    const int id = valid ? f.id : -1 - lane;
+    Contrib ct;
+#pragma unroll
+    for (int j = 0; j < 3; j++) {
+        ct.vid[j] = 0;
+#pragma unroll
+        for (int k = 0; k < 7; k++) ct.v[j][k] = 0.f;
+    }
+    if (valid) {
+        const float4 g3 = __ldg(P.geo + 4 * (size_t)id + 3);
+        const float w[3] = {g3.x, g3.y, g3.z};
+        const AttrRec a = load_attr<true>(P.attr, id);
+        backward_outputs(w, a, f, ct);
+    }
+    // runs of equal triangle ids in lane order
+    const int prev = __shfl_up_sync(0xffffffffu, id, 1);
+    const unsigned heads = __ballot_sync(0xffffffffu, lane == 0 || prev != id);
+    const unsigned above = (lane == 31) ? 1u : (heads >> (lane + 1));      // head flags of lanes lane+1 .. (bit 0 = next lane)
+    const bool same1 = (above & 1u) == 0 && lane + 1 < 32;
+    const bool same2 = (above & 3u) == 0 && lane + 2 < 32;
+    const bool same4 = (above & 15u) == 0 && lane + 4 < 32;
+    const int run_start = 31 - __clz(heads & (0xffffffffu >> (31 - lane)));
+#pragma unroll
+    for (int j = 0; j < 3; j++) {
+#pragma unroll
+        for (int k = 0; k < 7; k++) {
+            float t = ct.v[j][k], u;
+            u = __shfl_down_sync(0xffffffffu, t, 1); if (same1) t += u;
+            u = __shfl_down_sync(0xffffffffu, t, 2); if (same2) t += u;
+            u = __shfl_down_sync(0xffffffffu, t, 4); if (same4) t += u;
+            ct.v[j][k] = t;
+        }
+    }
+    if (valid && ((lane - run_start) & 7) == 0) emit_contrib(ct, gpack);
+}
+
+template <int MAXT>
+__global__ void __launch_bounds__(MAXT, 4) blend_backward_queued_kernel(BlendParams P, BackwardIn in,
+                                                                        const int* __restrict__ sel,
+                                                                        float4* __restrict__ gpack) {
+    static_assert(MAXT == 256, "the per-warp queues are sized for 8 warps");
+    __shared__ float s_coord[kMaxTileCoords];
+    __shared__ float s_queue[MAXT / 32][kQueueFields][kQueueSlots];
+    const TileCtx c = tile_context(P, s_coord);
+    PixelGrad pg;
+    BackState st;
+    float sq = 0.f;
+    const int n = load_pixel_state(c, P, in, pg, st, &sq);
+    const size_t plane = (size_t)P.W * P.H, index = (size_t)c.iy * P.W + c.ix;
+    const int lane = lane_id();
+    float (*q)[kQueueSlots] = s_queue[threadIdx.x >> 5];
+    if (in.l2_target) {
+        // loss: warp sum, then one atomic per warp into one of 64 partial sums (spread addresses)
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, d);
+        if (lane == 0 && sq != 0.f) atomicAdd(in.l2_partials + ((blockIdx.x * 8 + (threadIdx.x >> 5)) & (kLossPartials - 1)), sq);
+    }
+    int nmax = n;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) nmax = max(nmax, __shfl_xor_sync(0xffffffffu, nmax, d));
+    int queued = 0;                                    // uniform over the warp
+    int id_next = (n > 0) ? sel[(size_t)(n - 1) * plane + index] : 0;   // ids are fetched one fragment ahead
+    for (int s = 0; s < nmax; s++) {
+        const int k = n - 1 - s;
+        const bool has = k >= 0;
+        const int id = id_next;
+        if (k > 0) id_next = sel[(size_t)(k - 1) * plane + index];
+        const unsigned pushing = __ballot_sync(0xffffffffu, has);
+        if (has) {
+            float m[9], w[3];
+            load_geo(P.geo, id, m, w);
+            const AttrRec a = load_attr<false>(P.attr, id);
+            const Bary b = apply_bary(m, c.px, c.py);
+            QueuedFragment f;
+            backward_state(w, a, b, pg, st, f);
+            const int slot = queued + __popc(pushing & ((1u << lane) - 1u));
+            q[0][slot] = c.px; q[1][slot] = c.py; q[2][slot] = __int_as_float(id);
+            q[3][slot] = f.bx; q[4][slot] = f.by; q[5][slot] = f.bz;
+            q[6][slot] = f.o_raw; q[7][slot] = f.cr; q[8][slot] = f.cg; q[9][slot] = f.cb; q[10][slot] = f.z;
+            q[11][slot] = f.uo; q[12][slot] = f.ur; q[13][slot] = f.ug; q[14][slot] = f.ub; q[15][slot] = f.uz;
+        }
+        queued += __popc(pushing);
+        __syncwarp();
+        if (queued >= 32) {
+            queued -= 32;
+            drain_queue(P, q, queued, 32, gpack);
+            __syncwarp();
+        }
+    }
+    if (queued > 0) drain_queue(P, q, 0, queued, gpack);
+}
+
 // General path (any max_layers, both modes): searches the list again as the reference does.
 template <bool SORT, int MAXT>
 __global__ void __launch_bounds__(MAXT) blend_backward_kernel(BlendParams P, BackwardIn in, float4* __restrict__ gpack) {
@@ -741,7 +948,7 @@ static int backward_impl(const float* tri_geo, const float* tri_attr, const int3
     const tg::BackwardIn in = {(const float4*)grad_image, grad_depthmap, (const float4*)image, depthmap, final_weights,
                                ends, (const float4*)l2_target, l2_grad_scale, partials};
     if (threads <= 256) {
-        if (saved) tg::blend_backward_saved_kernel<256><<<tiles, threads, 0, s>>>(P, in, selection, gpack);
+        if (saved) tg::blend_backward_queued_kernel<256><<<tiles, threads, 0, s>>>(P, in, selection, gpack);
         else if (per_pixel_sort) tg::blend_backward_kernel<true, 256><<<tiles, threads, 0, s>>>(P, in, gpack);
         else tg::blend_backward_kernel<false, 256><<<tiles, threads, 0, s>>>(P, in, gpack);
     } else {
