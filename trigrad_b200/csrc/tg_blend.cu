@@ -562,7 +562,8 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 256 ? 4 : 1) blend_backward_save
 // the work is split: part A (per pixel, back to front) runs the recurrence and produces the upstream
 // gradients of the fragment's interpolations; these go into a queue in shared memory; part B (the
 // expensive barycentric partials and the 21 per-vertex outputs) pops 32 queued fragments at a time and
-// so runs with full warps.  The arithmetic per fragment is that of backward_one.
+// so runs with full warps.  The arithmetic per fragment is that of backward_one.  A warp whose lanes are
+// busy anyway (deep overlap, or one opaque layer everywhere) skips the queue.
 struct QueuedFragment {
     float px, py;
     int id;
@@ -660,7 +661,8 @@ __device__ __forceinline__ void backward_outputs(const float* w, const AttrRec& 
 
 // Part B for the fragments in queue slots first .. first + count - 1 (count <= 32), one per lane.
 // Consecutive slots that hold the same triangle (neighbouring pixels mostly do) are summed over runs of
-// up to eight with three shuffle rounds before the vector reductions are issued.
+// up to four with two shuffle rounds before the vector reductions are issued (a third round, runs of
+// eight, costs more in shuffles than it saves in reductions).
 __device__ __forceinline__ void drain_queue(const BlendParams& P, float (*q)[kQueueSlots], int first, int count,
                                             float4* __restrict__ gpack) {
     const int lane = lane_id();
@@ -691,7 +693,6 @@ __device__ __forceinline__ void drain_queue(const BlendParams& P, float (*q)[kQu
     const unsigned above = (lane == 31) ? 1u : (heads >> (lane + 1));      // head flags of lanes lane+1 .. (bit 0 = next lane)
     const bool same1 = (above & 1u) == 0 && lane + 1 < 32;
     const bool same2 = (above & 3u) == 0 && lane + 2 < 32;
-    const bool same4 = (above & 15u) == 0 && lane + 4 < 32;
     const int run_start = 31 - __clz(heads & (0xffffffffu >> (31 - lane)));
 #pragma unroll
     for (int j = 0; j < 3; j++) {
@@ -700,11 +701,53 @@ __device__ __forceinline__ void drain_queue(const BlendParams& P, float (*q)[kQu
             float t = ct.v[j][k], u;
             u = __shfl_down_sync(0xffffffffu, t, 1); if (same1) t += u;
             u = __shfl_down_sync(0xffffffffu, t, 2); if (same2) t += u;
-            u = __shfl_down_sync(0xffffffffu, t, 4); if (same4) t += u;
             ct.v[j][k] = t;
         }
     }
-    if (valid && ((lane - run_start) & 7) == 0) emit_contrib(ct, gpack);
+    if (valid && ((lane - run_start) & 3) == 0) emit_contrib(ct, gpack);
+}
+
+// Whole fragments per round, for warps whose lanes are busy anyway.  Pixels of one 2x2 quad (lanes L, L^1,
+// L^8, L^9 of the warp's 8x4 block) that hold the same triangle are summed before one lane issues the
+// reductions.  Kept out of line so that it does not weigh on the register allocation of the queued path.
+__device__ __noinline__ void backward_rounds_direct(const BlendParams& P, float px, float py, PixelGrad pg, BackState st,
+                                                    int n, int nmax, int id_next, const int* __restrict__ sel_pixel,
+                                                    size_t plane, float4* __restrict__ gpack) {
+    const int lane = lane_id();
+    const unsigned quad = 0x303u << (lane & ~9);
+    for (int s = 0; s < nmax; s++) {
+        const int k = n - 1 - s;
+        const bool has = k >= 0;
+        const int id = has ? id_next : -1 - lane;          // distinct negatives never match
+        if (k > 0) id_next = sel_pixel[(size_t)(k - 1) * plane];
+        Contrib ct;
+#pragma unroll
+        for (int j = 0; j < 3; j++) {
+            ct.vid[j] = 0;
+#pragma unroll
+            for (int i = 0; i < 7; i++) ct.v[j][i] = 0.f;
+        }
+        if (has) {
+            float m[9], w[3];
+            load_geo(P.geo, id, m, w);
+            const AttrRec a = load_attr<true>(P.attr, id);
+            const Bary b = apply_bary(m, px, py);
+            backward_one(w, a, b, px, py, pg, st, ct);
+        }
+        const unsigned peers = __match_any_sync(0xffffffffu, id);
+        const bool full4 = has && ((peers & quad) == quad);
+#pragma unroll
+        for (int j = 0; j < 3; j++) {
+#pragma unroll
+            for (int i = 0; i < 7; i++) {
+                float t = ct.v[j][i];
+                t += __shfl_xor_sync(0xffffffffu, t, 1);
+                t += __shfl_xor_sync(0xffffffffu, t, 8);
+                if (full4) ct.v[j][i] = t;
+            }
+        }
+        if (has && (!full4 || (lane & 9) == 0)) emit_contrib(ct, gpack);
+    }
 }
 
 template <int MAXT>
@@ -731,8 +774,17 @@ __global__ void __launch_bounds__(MAXT, 4) blend_backward_queued_kernel(BlendPar
     int nmax = n;
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) nmax = max(nmax, __shfl_xor_sync(0xffffffffu, nmax, d));
-    int queued = 0;                                    // uniform over the warp
+    int nsum = n;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) nsum += __shfl_xor_sync(0xffffffffu, nsum, d);
     int id_next = (n > 0) ? sel[(size_t)(n - 1) * plane + index] : 0;   // ids are fetched one fragment ahead
+    if (nsum * 10 >= nmax * 32 * 9) {
+        // Nearly all lanes have a fragment in every round (90 % or more): the queue would cost more than the idle
+        // lanes do.
+        backward_rounds_direct(P, c.px, c.py, pg, st, n, nmax, id_next, sel + index, plane, gpack);
+        return;
+    }
+    int queued = 0;                                    // uniform over the warp
     for (int s = 0; s < nmax; s++) {
         const int k = n - 1 - s;
         const bool has = k >= 0;
