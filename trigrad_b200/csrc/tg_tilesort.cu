@@ -168,6 +168,34 @@ __device__ __forceinline__ int log2_at_least(uint32_t n) {
 __device__ __forceinline__ uint32_t* long_items(uint32_t* lists) { return lists + 4; }
 __device__ __forceinline__ uint32_t* mid_items(uint32_t* lists, int tiles) { return lists + 4 + tiles; }
 
+// Rank sort of n <= 32 * PER words by one warp: every lane counts, for each of its PER words, the words
+// of the segment that are smaller, which is the word's final position (all words differ).
+template <int PER>
+__device__ __forceinline__ void rank_sort_warp(uint64_t* s, uint64_t* __restrict__ entries, int32_t* __restrict__ sorted_ids,
+                                               int beg, int n, int lane, int write_back) {
+    uint64_t mine[PER];
+#pragma unroll
+    for (int r = 0; r < PER; r++) {
+        const int i = lane + r * 32;
+        mine[r] = (i < n) ? entries[beg + i] : ~0ull;
+        if (i < n) s[i] = mine[r];
+    }
+    __syncwarp();
+    int below[PER] = {};
+    for (int j = 0; j < n; j++) {
+        const uint64_t other = s[j];
+#pragma unroll
+        for (int r = 0; r < PER; r++) below[r] += (other < mine[r]) ? 1 : 0;
+    }
+#pragma unroll
+    for (int r = 0; r < PER; r++) {
+        if (lane + r * 32 < n) {
+            sorted_ids[beg + below[r]] = (int32_t)(uint32_t)mine[r];
+            if (write_back) entries[beg + below[r]] = mine[r];
+        }
+    }
+}
+
 // One warp per tile: rank sort of the tiles with at most kTileSortRank entries, the others go to the
 // work list of their length class.
 __global__ void __launch_bounds__(kTileSortThreads) tile_sort_kernel(uint64_t* __restrict__ entries,
@@ -190,32 +218,9 @@ __global__ void __launch_bounds__(kTileSortThreads) tile_sort_kernel(uint64_t* _
         return;
     }
     uint64_t* s = s_all[warp];
-    constexpr int kPer = kTileSortRank / 32;
-    uint64_t mine[kPer];
-#pragma unroll
-    for (int r = 0; r < kPer; r++) {
-        const int i = lane + r * 32;
-        mine[r] = (i < n) ? entries[beg + i] : ~0ull;
-        if (i < n) s[i] = mine[r];
-    }
-    __syncwarp();
-    int below[kPer] = {};
-    if (n <= 32) {
-        for (int j = 0; j < n; j++) below[0] += (s[j] < mine[0]) ? 1 : 0;
-    } else {
-        for (int j = 0; j < n; j++) {
-            const uint64_t other = s[j];
-#pragma unroll
-            for (int r = 0; r < kPer; r++) below[r] += (other < mine[r]) ? 1 : 0;
-        }
-    }
-#pragma unroll
-    for (int r = 0; r < kPer; r++) {
-        if (lane + r * 32 < n) {
-            sorted_ids[beg + below[r]] = (int32_t)(uint32_t)mine[r];
-            if (write_back) entries[beg + below[r]] = mine[r];
-        }
-    }
+    if (n <= 32) rank_sort_warp<1>(s, entries, sorted_ids, beg, n, lane, write_back);
+    else if (n <= 64) rank_sort_warp<2>(s, entries, sorted_ids, beg, n, lane, write_back);
+    else rank_sort_warp<kTileSortRank / 32>(s, entries, sorted_ids, beg, n, lane, write_back);
 }
 
 // Tiles of kTileSortRank < n <= kTileSortShort entries: persistent CTAs of 128 threads, next free item first.
