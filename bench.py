@@ -205,6 +205,8 @@ def main() -> None:
     ap.add_argument("--views-per-gpu", type=int, default=8,
                     help="views of the mesh rendered per GPU per step (a batch of views; gradients are summed)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--one-kernel", action="store_true",
+                    help="forward and backward of a view in one compositing kernel (tg_render_step_l2)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -275,12 +277,12 @@ def main() -> None:
             verts = Vw.project(p, v)
             gverts = torch.zeros_like(verts)
             Vw.l2_view_step(verts.detach(), i, c, o, target, W, H, gverts, grads.colors, grads.opacities, grads.loss,
-                            scene.tile_width, scene.tile_height)
+                            scene.tile_width, scene.tile_height, one_kernel=args.one_kernel)
             (gp,) = torch.autograd.grad(verts, p, grad_outputs=gverts)
             grads.points.add_(gp)
         else:
             Vw.l2_view_step(v, i, c, o, target, W, H, grads.points, grads.colors, grads.opacities, grads.loss,
-                            scene.tile_width, scene.tile_height)
+                            scene.tile_width, scene.tile_height, one_kernel=args.one_kernel)
         return None
 
     def run_views(items):
@@ -420,7 +422,7 @@ def main() -> None:
         "data": "synthetic",
         "config": {"workload": wname, "triangles": T, "vertices": V, "width": W, "height": H,
                    "tile": [scene.tile_width, scene.tile_height], "per_pixel_sort": True, "max_layers": 32,
-                   "views_per_gpu_per_step": B, "streams": n_streams, "K_pairs": stages["_K"], "l2": "256 MB buffer rewritten between timed steps",
+                   "views_per_gpu_per_step": B, "streams": n_streams, "one_kernel_step": bool(args.one_kernel), "K_pairs": stages["_K"], "l2": "256 MB buffer rewritten between timed steps",
                    "exchange": "none" if world == 1 else f"one NCCL all_reduce of {pos_comp + 4}V fp32 gradients per step"},
         "triangles_per_s": T * B * world / (ms_per_step * 1e-3),
         "ms_per_view": ms_per_step / B,

@@ -168,6 +168,19 @@ int tg_blend_backward_l2(const float* tri_geo, const float* tri_attr, const int3
                          float* grad_vertices, float* grad_colors, float* grad_opacities, int accumulate, void* scratch,
                          size_t scratch_bytes, tg_stream_t stream);
 
+/* ---- forward + backward of mean((image - target)^2) in one kernel --------------------------------
+ * No counterpart in the reference: tg_blend_forward followed by tg_blend_backward_l2 for the default
+ * mode (per-pixel sort, 1 <= max_layers <= 32, tiles of at most 256 pixels), fused so that the values
+ * the forward interpolates feed the backward recurrence directly (no selection planes, no second
+ * read of the image).  Outputs and gradient conventions as for those two calls; the image, depth map,
+ * final weights and ends are bit-identical to tg_blend_forward's.
+ */
+int tg_blend_step_l2(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids, const int32_t* offsets,
+                     int V, int W, int H, int tile_w, int tile_h, float early_stopping_threshold, int max_layers,
+                     const float* target, float grad_scale, float loss_scale, float* loss_out, float* image,
+                     float* depthmap, float* final_weights, int32_t* ends, float* grad_vertices, float* grad_colors,
+                     float* grad_opacities, int accumulate, void* scratch, size_t scratch_bytes, tg_stream_t stream);
+
 /* ---- whole forward path -------------------------------------------------------------------------
  * Replaces render_forward (src/trigrad/render.cu:713-763).  Runs stages 1-6 on `stream`.
  *   selection    as for tg_blend_forward (may be NULL)
@@ -190,6 +203,20 @@ int tg_render_forward(const float* vertices, const int32_t* indices, const float
                       int32_t* ends, int32_t* selection, float* tri_geo, float* tri_attr, int32_t* sorted_ids,
                       uint32_t list_capacity, int32_t* offsets, void* workspace, size_t workspace_bytes, uint32_t* info_host,
                       float* stage_ms_host, tg_stream_t stream);
+
+/* ---- whole optimisation step of one view ------------------------------------------------------------
+ * tg_render_forward with tg_blend_step_l2 in place of the compositing kernel: binning, tile lists,
+ * forward, loss and gradients of one view in one call (same restrictions as tg_blend_step_l2).
+ * Arguments as for tg_render_forward (workspace, info_host, stage_ms_host: "rasterization" then covers
+ * forward + backward) and tg_blend_backward_l2 (target, scales, loss_out, gradients, scratch).
+ */
+int tg_render_step_l2(const float* vertices, const int32_t* indices, const float* colors, const float* opacities,
+                      int T, int V, int W, int H, int tile_w, int tile_h, float early_stopping_threshold, int max_layers,
+                      const float* target, float grad_scale, float loss_scale, float* loss_out, float* image,
+                      float* depthmap, float* final_weights, int32_t* ends, float* tri_geo, float* tri_attr,
+                      int32_t* sorted_ids, uint32_t list_capacity, int32_t* offsets, float* grad_vertices,
+                      float* grad_colors, float* grad_opacities, int accumulate, void* workspace, size_t workspace_bytes,
+                      void* scratch, size_t scratch_bytes, uint32_t* info_host, float* stage_ms_host, tg_stream_t stream);
 
 #ifdef __cplusplus
 }

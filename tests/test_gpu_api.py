@@ -142,10 +142,14 @@ def test_non_contiguous_inputs():
     assert torch.equal(a, b)
 
 
-def test_fused_l2_view_step_matches_autograd():
-    """views.l2_view_step (forward + loss-fused backward, accumulating) against render() + torch autograd."""
+@pytest.mark.parametrize("tile,one_kernel", [(16, False), (16, True), (32, True)],
+                         ids=["two_kernels", "one_kernel", "one_kernel_asked_with_big_tiles"])
+def test_fused_l2_view_step_matches_autograd(tile, one_kernel):
+    """views.l2_view_step (accumulating; forward + loss-fused backward, or both directions in one compositing
+    kernel, which tiles of more than 256 pixels cannot use) against render() + torch autograd."""
     from trigrad_b200 import views
     sc = S.config2_random10k()
+    sc.tile_width = sc.tile_height = tile
     V = sc.num_vertices
     gV = torch.zeros((V, 4), device="cuda")
     gC = torch.zeros((V, 3), device="cuda")
@@ -159,9 +163,10 @@ def test_fused_l2_view_step_matches_autograd():
         verts[:, 0] += 0.01 * k
         target = Hh.cuda(rng.random((sc.height, sc.width, 4), dtype=np.float32))
         v, i, c, o = Hh.cuda(verts), Hh.cuda(sc.indices), Hh.cuda(sc.colors), Hh.cuda(sc.opacities)
-        img = views.l2_view_step(v, i, c, o, target, sc.width, sc.height, gV, gC, gO, loss)
+        img = views.l2_view_step(v, i, c, o, target, sc.width, sc.height, gV, gC, gO, loss, tile, tile,
+                                 one_kernel=one_kernel)
         vv, cc, oo = v.clone().requires_grad_(), c.clone().requires_grad_(), o.clone().requires_grad_()
-        image, _ = trigrad_b200.render(vv, i, cc, oo, sc.width, sc.height)
+        image, _ = trigrad_b200.render(vv, i, cc, oo, sc.width, sc.height, tile, tile)
         assert torch.equal(image, img)
         l = torch.mean((image - target) ** 2)
         g = torch.autograd.grad(l, (vv, cc, oo))

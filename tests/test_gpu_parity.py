@@ -248,6 +248,50 @@ def test_forward_and_backward_vs_oracle(pipeline, mode):
         assert err_max <= GRAD_TOL_MAX, f"grad_{name} ({path}): worst element {err_max:.3e}"
 
 
+@pytest.mark.parametrize("max_layers", [32, 5])
+def test_one_kernel_step_vs_oracle(pipeline, max_layers):
+    """tg_blend_step_l2 (forward + backward of the mean squared error in one kernel): image identical to the
+    oracle's forward, loss and gradients equal to the oracle's backward of the same loss."""
+    p, sc = pipeline, pipeline["sc"]
+    if sc.tile_width * sc.tile_height > 256:
+        pytest.skip("the one-kernel step needs tiles of at most 256 pixels")
+    rng = np.random.default_rng(11)
+    target = rng.random((sc.height, sc.width, 4), dtype=np.float32)
+    (image, depth, fw, ends), grads, loss = Hh.blend_step_l2(sc, p["geo"], p["attr"], p["sids"], p["offsets"],
+                                                            Hh.cuda(target), 1 / 256, max_layers)
+    of = O.forward(sc.vertices, sc.indices, sc.colors, sc.opacities, sc.width, sc.height, sc.tile_width,
+                   sc.tile_height, 1 / 256, True, max_layers)
+    assert np.array_equal(ends.cpu().numpy(), of.ends)
+    assert np.array_equal(image.cpu().numpy().view(np.uint32), of.image.view(np.uint32))
+    assert np.array_equal(depth.cpu().numpy().view(np.uint32), of.depthmap.view(np.uint32))
+    assert np.array_equal(fw.cpu().numpy().view(np.uint32), of.final_weights.view(np.uint32))
+    n = np.float32(sc.width * sc.height * 4)
+    diff = of.image - target
+    ref_loss = float(np.sum(diff.astype(np.float64) ** 2) / n)
+    assert abs(float(loss) - ref_loss) <= 1e-5 * ref_loss
+    gi = (diff * (np.float32(2) / n)).astype(np.float32)
+    og = O.backward(sc.vertices, sc.indices, sc.colors, sc.opacities, sc.width, sc.height, of, gi,
+                    np.zeros((sc.height, sc.width), np.float32), sc.tile_width, sc.tile_height, True, max_layers)
+    # A gradient that is analytically zero (triangles with one colour and one opacity: no dependence on the
+    # vertex positions) comes out of fp32 as cancellation noise, 1e-8 against 1e-2 for the colours.  The fp64
+    # oracle tells which gradients are of that kind; those only have to be negligible here as well.
+    f64 = [np.asarray(x, np.float64) for x in (sc.vertices, sc.colors, sc.opacities)]
+    of64 = O.forward(f64[0], sc.indices, f64[1], f64[2], sc.width, sc.height, sc.tile_width, sc.tile_height, 1 / 256, True,
+                     max_layers)
+    gi64 = (of64.image - target) * (2.0 / float(n))
+    og64 = O.backward(f64[0], sc.indices, f64[1], f64[2], sc.width, sc.height, of64, gi64,
+                      np.zeros((sc.height, sc.width)), sc.tile_width, sc.tile_height, True, max_layers)
+    whole = float(np.sqrt(sum(float(np.sum(g ** 2)) for g in og64)))
+    for name, a, b, b64 in zip(("vertices", "colors", "opacities"), grads, og, og64):
+        a = a.cpu().numpy()
+        if float(np.linalg.norm(b64)) < 1e-4 * whole:
+            assert float(np.linalg.norm(a.astype(np.float64))) <= 1e-4 * whole, f"grad_{name} should be negligible"
+            continue
+        err, err_max = Hh.rel_l2(a, b), Hh.rel_err(a, b)
+        assert err <= GRAD_TOL, f"grad_{name}: relative L2 error {err:.3e}"
+        assert err_max <= GRAD_TOL_MAX, f"grad_{name}: worst element {err_max:.3e}"
+
+
 def test_large_sort_random_keys():
     """Sort alone on 3M random 45-bit keys, odd length, against numpy's stable sort."""
     rng = np.random.default_rng(3)

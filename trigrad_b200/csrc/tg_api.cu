@@ -66,38 +66,29 @@ struct StageTimer {
 
 }  // namespace
 
-extern "C" {
-
-size_t tg_forward_workspace_bytes(int T, int tiles, uint32_t list_capacity) {
-    if (T < 0) T = 0;
-    if (tiles < 0) tiles = 0;
-    return ForwardWorkspace(nullptr, T, tiles, list_capacity).total;
-}
-
-int tg_render_forward(const float* vertices, const int32_t* indices, const float* colors, const float* opacities, int T,
-                      int W, int H, int tw, int th, float thr, int per_pixel_sort, int max_layers, float* image,
-                      float* depthmap, float* final_weights, int32_t* ends, int32_t* selection, float* tri_geo,
-                      float* tri_attr, int32_t* sorted_ids, uint32_t list_capacity, int32_t* offsets, void* workspace,
-                      size_t workspace_bytes, uint32_t* info_host, float* stage_ms_host, tg_stream_t stream) {
+// Everything before compositing: per-triangle records, tile offsets, sorted tile lists (timer marks 0-3).
+static int build_tile_lists(const float* vertices, const int32_t* indices, const float* colors, const float* opacities,
+                            int T, int W, int H, int tw, int th, int max_layers, float* tri_geo, float* tri_attr,
+                            int32_t* sorted_ids, uint32_t list_capacity, int32_t* offsets, void* workspace,
+                            size_t workspace_bytes, uint32_t* info_host, StageTimer& timer, uint32_t** device_status,
+                            cudaStream_t s) {
     TG_REQUIRE(T >= 0 && W > 0 && H > 0 && tw > 0 && th > 0, "sizes");
     TG_REQUIRE(tw * th <= 1024, "tile_width * tile_height must be <= 1024");
     TG_REQUIRE(max_layers >= 1, "max_layers must be >= 1");
-    TG_REQUIRE(workspace && info_host && offsets && image && depthmap && final_weights && ends, "null pointer");
+    TG_REQUIRE(workspace && info_host && offsets, "null pointer");
     TG_REQUIRE(((uintptr_t)workspace & 255) == 0, "workspace must be 256-byte aligned");
     TG_REQUIRE(list_capacity < 0x80000000u, "list capacity must stay below 2^31");
     const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
     const int tiles = tiles_x * tiles_y;
-    ForwardWorkspace ws(workspace, T, tiles, list_capacity);
+    const ForwardWorkspace ws(workspace, T, tiles, list_capacity);
+    *device_status = ws.status;
     if (workspace_bytes < ws.total) {
         tg_host::set_error("forward workspace: need %zu bytes, got %zu", ws.total, workspace_bytes);
         return TG_ERR_WORKSPACE;
     }
-    cudaStream_t s = (cudaStream_t)stream;
-    StageTimer timer(stage_ms_host != nullptr, s);
     info_host[0] = 0;
     info_host[1] = 0;
     info_host[2] = 0;
-
     TG_REQUIRE(list_capacity == 0 || sorted_ids != nullptr, "null sorted_ids");
     cudaEvent_t k_ready;
     if (int st = scratch_event(&k_ready)) return st;
@@ -130,28 +121,80 @@ int tg_render_forward(const float* vertices, const int32_t* indices, const float
         st = tg_host::sort_tile_lists(ws.entries, offsets, tiles, sorted_ids, ws.long_list, true, false, info_host[1], s);
         if (st) return st;
     }
+    return TG_OK;
+}
+
+// Stage times from the timer's six marks (synchronises), then the device error word.
+static int finish_timing(StageTimer& timer, float* stage_ms_host, const uint32_t* info_host, cudaStream_t s) {
+    if (!stage_ms_host) return TG_OK;
+    TG_CUDA(cudaStreamSynchronize(s));
+    float ms[5];
+    for (int i = 0; i < 5; i++) TG_CUDA(cudaEventElapsedTime(&ms[i], timer.ev[i], timer.ev[i + 1]));
+    stage_ms_host[0] = ms[0];   // init
+    stage_ms_host[1] = ms[2];   // per_tile_lists: K read-back + entry emission
+    stage_ms_host[2] = ms[3];   // sorting: per-tile sort
+    stage_ms_host[3] = ms[1];   // bary_transforms: preprocess + scan + tile counts and offsets
+    stage_ms_host[4] = ms[4];   // rasterization
+    if (info_host[2]) {
+        tg_host::set_error("device error word = %u", info_host[2]);
+        return TG_ERR_DEVICE_FLAG;
+    }
+    return TG_OK;
+}
+
+extern "C" {
+
+size_t tg_forward_workspace_bytes(int T, int tiles, uint32_t list_capacity) {
+    if (T < 0) T = 0;
+    if (tiles < 0) tiles = 0;
+    return ForwardWorkspace(nullptr, T, tiles, list_capacity).total;
+}
+
+int tg_render_forward(const float* vertices, const int32_t* indices, const float* colors, const float* opacities, int T,
+                      int W, int H, int tw, int th, float thr, int per_pixel_sort, int max_layers, float* image,
+                      float* depthmap, float* final_weights, int32_t* ends, int32_t* selection, float* tri_geo,
+                      float* tri_attr, int32_t* sorted_ids, uint32_t list_capacity, int32_t* offsets, void* workspace,
+                      size_t workspace_bytes, uint32_t* info_host, float* stage_ms_host, tg_stream_t stream) {
+    TG_REQUIRE(image && depthmap && final_weights && ends, "null pointer");
+    cudaStream_t s = (cudaStream_t)stream;
+    StageTimer timer(stage_ms_host != nullptr, s);
+    uint32_t* device_status = nullptr;
+    int st = build_tile_lists(vertices, indices, colors, opacities, T, W, H, tw, th, max_layers, tri_geo, tri_attr,
+                              sorted_ids, list_capacity, offsets, workspace, workspace_bytes, info_host, timer, &device_status, s);
+    if (st) return st;
     timer.mark();                                                    // [4] start of "rasterization"
     st = tg_blend_forward(tri_geo, tri_attr, sorted_ids, offsets, W, H, tw, th, thr, per_pixel_sort, max_layers, image,
                           depthmap, final_weights, ends, selection, stream);
     if (st) return st;
     timer.mark();                                                    // [5] end
     // device error word: valid on the host once the stream has been synchronised
-    TG_CUDA(cudaMemcpyAsync(&info_host[2], ws.status, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
-    if (stage_ms_host) {
-        TG_CUDA(cudaStreamSynchronize(s));
-        float ms[5];
-        for (int i = 0; i < 5; i++) TG_CUDA(cudaEventElapsedTime(&ms[i], timer.ev[i], timer.ev[i + 1]));
-        stage_ms_host[0] = ms[0];   // init
-        stage_ms_host[1] = ms[2];   // per_tile_lists: K read-back + entry emission
-        stage_ms_host[2] = ms[3];   // sorting: per-tile sort
-        stage_ms_host[3] = ms[1];   // bary_transforms: preprocess + scan + tile counts and offsets
-        stage_ms_host[4] = ms[4];   // rasterization
-        if (info_host[2]) {
-            tg_host::set_error("device error word = %u", info_host[2]);
-            return TG_ERR_DEVICE_FLAG;
-        }
-    }
-    return TG_OK;
+    TG_CUDA(cudaMemcpyAsync(&info_host[2], device_status, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+    return finish_timing(timer, stage_ms_host, info_host, s);
+}
+
+int tg_render_step_l2(const float* vertices, const int32_t* indices, const float* colors, const float* opacities, int T,
+                      int V, int W, int H, int tw, int th, float thr, int max_layers, const float* target,
+                      float grad_scale, float loss_scale, float* loss_out, float* image, float* depthmap,
+                      float* final_weights, int32_t* ends, float* tri_geo, float* tri_attr, int32_t* sorted_ids,
+                      uint32_t list_capacity, int32_t* offsets, float* grad_vertices, float* grad_colors,
+                      float* grad_opacities, int accumulate, void* workspace, size_t workspace_bytes, void* scratch,
+                      size_t scratch_bytes, uint32_t* info_host, float* stage_ms_host, tg_stream_t stream) {
+    TG_REQUIRE(image && depthmap && final_weights && ends && target && loss_out, "null pointer");
+    TG_REQUIRE(tw * th <= 256 && max_layers <= 32, "the one-kernel step needs tiles of at most 256 pixels and max_layers <= 32");
+    cudaStream_t s = (cudaStream_t)stream;
+    StageTimer timer(stage_ms_host != nullptr, s);
+    uint32_t* device_status = nullptr;
+    int st = build_tile_lists(vertices, indices, colors, opacities, T, W, H, tw, th, max_layers, tri_geo, tri_attr,
+                              sorted_ids, list_capacity, offsets, workspace, workspace_bytes, info_host, timer, &device_status, s);
+    if (st) return st;
+    timer.mark();                                                    // [4] start of "rasterization" (here: forward + backward)
+    st = tg_blend_step_l2(tri_geo, tri_attr, sorted_ids, offsets, V, W, H, tw, th, thr, max_layers, target, grad_scale,
+                          loss_scale, loss_out, image, depthmap, final_weights, ends, grad_vertices, grad_colors,
+                          grad_opacities, accumulate, scratch, scratch_bytes, stream);
+    if (st) return st;
+    timer.mark();                                                    // [5] end
+    TG_CUDA(cudaMemcpyAsync(&info_host[2], device_status, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+    return finish_timing(timer, stage_ms_host, info_host, s);
 }
 
 }  // extern "C"

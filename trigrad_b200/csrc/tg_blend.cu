@@ -72,28 +72,33 @@ __device__ __forceinline__ AttrRec load_attr(const float4* attr, int id) {
 // process_forward of the reference (render.cu:417-453); every operation rounded separately, in the
 // oracle's order, so that the image agrees bit for bit with it.  The four weighted interpolations
 // share one correctly rounded reciprocal of their common denominator.
-__device__ __forceinline__ void blend_one(const Bary& b, const float* w, const AttrRec& a, PixelAcc& acc) {
-    const float inv = __frcp_rn(fma_(b.z, w[2], fma_(b.y, w[1], mul(b.x, w[0]))));
+struct BlendedValues { float o_raw, cr, cg, cb, z, den; };
+
+__device__ __forceinline__ BlendedValues blend_one(const Bary& b, const float* w, const AttrRec& a, PixelAcc& acc) {
+    BlendedValues v;
+    v.den = fma_(b.z, w[2], fma_(b.y, w[1], mul(b.x, w[0])));
+    const float inv = __frcp_rn(v.den);
     auto weighted = [&](float a0, float a1, float a2) -> float {
         float nom = mul(mul(b.x, a0), w[0]);
         nom = fma_(mul(b.y, a1), w[1], nom);
         nom = fma_(mul(b.z, a2), w[2], nom);
         return mul(nom, inv);
     };
-    float o = weighted(a.o[0], a.o[1], a.o[2]);
-    o = fminf(fmaxf(o, 0.f), kMaxOpacity);
-    const float cr = weighted(a.c[0], a.c[3], a.c[6]);
-    const float cg = weighted(a.c[1], a.c[4], a.c[7]);
-    const float cb = weighted(a.c[2], a.c[5], a.c[8]);
-    const float zv = interp_rn(b, a.iw[0], a.iw[1], a.iw[2], 1.f, 1.f, 1.f);
+    v.o_raw = weighted(a.o[0], a.o[1], a.o[2]);
+    const float o = fminf(fmaxf(v.o_raw, 0.f), kMaxOpacity);
+    v.cr = weighted(a.c[0], a.c[3], a.c[6]);
+    v.cg = weighted(a.c[1], a.c[4], a.c[7]);
+    v.cb = weighted(a.c[2], a.c[5], a.c[8]);
+    v.z = interp_rn(b, a.iw[0], a.iw[1], a.iw[2], 1.f, 1.f, 1.f);
     const float ao = mul(acc.alpha, o);
-    acc.depth = add(acc.depth, mul(ao, zv));
+    acc.depth = add(acc.depth, mul(ao, v.z));
     acc.weight = add(acc.weight, ao);
-    acc.r = add(acc.r, mul(ao, cr));
-    acc.g = add(acc.g, mul(ao, cg));
-    acc.b = add(acc.b, mul(ao, cb));
+    acc.r = add(acc.r, mul(ao, v.cr));
+    acc.g = add(acc.g, mul(ao, v.cg));
+    acc.b = add(acc.b, mul(ao, v.cb));
     acc.alpha = mul(acc.alpha, sub(1.f, o));
     acc.blended++;
+    return v;
 }
 
 // NDC extent (pixel centres) of the active pixels of one warp.
@@ -573,24 +578,14 @@ struct QueuedFragment {
 };
 constexpr int kQueueFields = 16, kQueueSlots = 64;
 
-// Part A: render.cu:455-538 up to the upstream gradients; updates the pixel's running state.
-__device__ __forceinline__ void backward_state(const float* w, const AttrRec& a, const Bary& b, const PixelGrad& pg,
-                                               BackState& st, QueuedFragment& f) {
-    const float bw0 = b.x * w[0], bw1 = b.y * w[1], bw2 = b.z * w[2];
-    const float den = bw0 + bw1 + bw2;
-    const bool ok = !(den * den < kEffZero);
-    const float inv = rcp_fast(den);
-    const float o_raw = (bw0 * a.o[0] + bw1 * a.o[1] + bw2 * a.o[2]) * inv;
+// Part A, second half: the transmittance recurrence of render.cu:455-538 for one fragment (back to
+// front) and the upstream gradients of its interpolations.  inv_den / inv_denz are the reciprocals of
+// the interpolation denominators, or 0 where the reference's guard returns zero gradients.
+__device__ __forceinline__ void backward_recurrence(float o_raw, float cr, float cg, float cb, float z, float inv_den,
+                                                    float inv_denz, const PixelGrad& pg, BackState& st,
+                                                    QueuedFragment& f) {
     const float o = fminf(fmaxf(o_raw, 0.f), kMaxOpacity);
-    const float cr = (bw0 * a.c[0] + bw1 * a.c[3] + bw2 * a.c[6]) * inv;
-    const float cg = (bw0 * a.c[1] + bw1 * a.c[4] + bw2 * a.c[7]) * inv;
-    const float cb = (bw0 * a.c[2] + bw1 * a.c[5] + bw2 * a.c[8]) * inv;
-    const float denz = b.x + b.y + b.z;
-    const bool okz = !(denz * denz < kEffZero);
-    const float invz = rcp_fast(denz);
-    const float z = (b.x * a.iw[0] + b.y * a.iw[1] + b.z * a.iw[2]) * invz;
     const float iom = rcp_fast(1.f - o);
-
     const float drgb_do = ((cr * st.alpha - st.sr) * pg.gr + (cg * st.alpha - st.sg) * pg.gg + (cb * st.alpha - st.sb) * pg.gb -
                            pg.ga * pg.final_alpha) * iom;
     st.alpha = st.alpha * iom;
@@ -606,14 +601,31 @@ __device__ __forceinline__ void backward_state(const float* w, const AttrRec& a,
     const float inv_fw = has_w ? rcp_fast(pg.final_weight) : 0.f;
     const float dd_do = (dud_do - pg.final_depth * ddw_do) * inv_fw * pg.gd;
     const float d_do = drgb_do + (has_w ? dd_do : 0.f);
-
-    f.bx = b.x; f.by = b.y; f.bz = b.z;
     f.o_raw = o_raw; f.cr = cr; f.cg = cg; f.cb = cb; f.z = z;
-    f.uo = ok ? d_do * inv : 0.f;
-    f.ur = ok ? ao * pg.gr * inv : 0.f;
-    f.ug = ok ? ao * pg.gg * inv : 0.f;
-    f.ub = ok ? ao * pg.gb * inv : 0.f;
-    f.uz = (okz && has_w) ? ao * pg.gd * inv_fw * invz : 0.f;
+    f.uo = d_do * inv_den;
+    f.ur = ao * pg.gr * inv_den;
+    f.ug = ao * pg.gg * inv_den;
+    f.ub = ao * pg.gb * inv_den;
+    f.uz = has_w ? ao * pg.gd * inv_fw * inv_denz : 0.f;
+}
+
+// Part A: interpolations of the fragment (approximate reciprocals), then the recurrence.
+__device__ __forceinline__ void backward_state(const float* w, const AttrRec& a, const Bary& b, const PixelGrad& pg,
+                                               BackState& st, QueuedFragment& f) {
+    const float bw0 = b.x * w[0], bw1 = b.y * w[1], bw2 = b.z * w[2];
+    const float den = bw0 + bw1 + bw2;
+    const bool ok = !(den * den < kEffZero);
+    const float inv = rcp_fast(den);
+    const float o_raw = (bw0 * a.o[0] + bw1 * a.o[1] + bw2 * a.o[2]) * inv;
+    const float cr = (bw0 * a.c[0] + bw1 * a.c[3] + bw2 * a.c[6]) * inv;
+    const float cg = (bw0 * a.c[1] + bw1 * a.c[4] + bw2 * a.c[7]) * inv;
+    const float cb = (bw0 * a.c[2] + bw1 * a.c[5] + bw2 * a.c[8]) * inv;
+    const float denz = b.x + b.y + b.z;
+    const bool okz = !(denz * denz < kEffZero);
+    const float invz = rcp_fast(denz);
+    const float z = (b.x * a.iw[0] + b.y * a.iw[1] + b.z * a.iw[2]) * invz;
+    f.bx = b.x; f.by = b.y; f.bz = b.z;
+    backward_recurrence(o_raw, cr, cg, cb, z, ok ? inv : 0.f, okz ? invz : 0.f, pg, st, f);
 }
 
 // Part B: from the upstream gradients to the contribution for the triangle's three vertices.
@@ -800,6 +812,106 @@ __global__ void __launch_bounds__(MAXT, 4) blend_backward_queued_kernel(BlendPar
             backward_state(w, a, b, pg, st, f);
             const int slot = queued + __popc(pushing & ((1u << lane) - 1u));
             q[0][slot] = c.px; q[1][slot] = c.py; q[2][slot] = __int_as_float(id);
+            q[3][slot] = f.bx; q[4][slot] = f.by; q[5][slot] = f.bz;
+            q[6][slot] = f.o_raw; q[7][slot] = f.cr; q[8][slot] = f.cg; q[9][slot] = f.cb; q[10][slot] = f.z;
+            q[11][slot] = f.uo; q[12][slot] = f.ur; q[13][slot] = f.ug; q[14][slot] = f.ub; q[15][slot] = f.uz;
+        }
+        queued += __popc(pushing);
+        __syncwarp();
+        if (queued >= 32) {
+            queued -= 32;
+            drain_queue(P, q, queued, 32, gpack);
+            __syncwarp();
+        }
+    }
+    if (queued > 0) drain_queue(P, q, 0, queued, gpack);
+}
+
+// ---- one optimisation step of one view in a single kernel -------------------------------------------
+// Forward compositing (default mode, max_layers <= 32: a single batch) followed, in the same thread, by
+// the backward of mean((image - target)^2).  The values the forward interpolates for every blended
+// fragment (opacity, colour, 1/w, barycentrics) are kept in local memory and feed the recurrence
+// directly: no second pass over geometry and attributes for it, no selection planes, no re-read of the
+// image; the per-vertex outputs go through the per-warp queue as in blend_backward_queued_kernel.
+template <int MAXT>
+__global__ void __launch_bounds__(MAXT, 4) blend_step_l2_kernel(BlendParams P, float4* __restrict__ image,
+                                                                float* __restrict__ depthmap, float* __restrict__ final_w,
+                                                                int* __restrict__ ends, const float4* __restrict__ target,
+                                                                float grad_scale, float* __restrict__ l2_partials,
+                                                                float4* __restrict__ gpack) {
+    static_assert(MAXT == 256, "the per-warp queues are sized for 8 warps");
+    __shared__ float4 s_geo[kChunk * 4];
+    __shared__ int s_id[kChunk];
+    __shared__ float s_coord[kMaxTileCoords];
+    __shared__ float s_queue[MAXT / 32][kQueueFields][kQueueSlots];
+    const TileCtx c = tile_context(P, s_coord);
+    const int lane = lane_id();
+    PixelAcc acc;
+    float4 kept[kBatchLayers][3];   // per blended fragment: (b.x, b.y, b.z, o_raw), (cr, cg, cb, z), (1/den, 1/denz, id, -)
+    int n = 0;
+    {
+        float dl[kBatchLayers];
+        int jl[kBatchLayers];
+        const bool go = c.active && acc.alpha > P.thr && P.max_layers > 0;
+        if (__syncthreads_or(go)) {
+            const int bs = min(kBatchLayers, P.max_layers);
+            const int found = select_sweep(P, c, go, bs, -INFINITY, -1, dl, jl, s_geo, s_id);
+            if (go) {
+                n = min(found, P.max_layers);
+                for (int i = 0; i < n; i++) {
+                    const int id = P.ids[jl[i]];
+                    float m[9], w[3];
+                    load_geo(P.geo, id, m, w);
+                    const Bary b = apply_bary(m, c.px, c.py);
+                    const AttrRec a = load_attr<false>(P.attr, id);
+                    const BlendedValues v = blend_one(b, w, a, acc);
+                    const float denz = b.x + b.y + b.z;
+                    kept[i][0] = make_float4(b.x, b.y, b.z, v.o_raw);
+                    kept[i][1] = make_float4(v.cr, v.cg, v.cb, v.z);
+                    kept[i][2] = make_float4((v.den * v.den < kEffZero) ? 0.f : rcp_fast(v.den),
+                                             (denz * denz < kEffZero) ? 0.f : rcp_fast(denz), __int_as_float(id), 0.f);
+                }
+            }
+        }
+    }
+    const float final_alpha = acc.alpha, out_r = acc.r, out_g = acc.g, out_b = acc.b;
+    store_pixel(c, P, acc, image, depthmap, final_w, ends);   // normalises acc.weight to 0 where no depth exists
+
+    // upstream gradient of the image and the pixel's squared error
+    PixelGrad pg = PixelGrad{};
+    BackState st;
+    st.alpha = final_alpha;
+    float sq = 0.f;
+    if (c.active) {
+        const float4 t = target[(size_t)c.iy * P.W + c.ix];
+        const float dr = out_r - t.x, dg = out_g - t.y, db = out_b - t.z, da = final_alpha - t.w;
+        pg.gr = grad_scale * dr; pg.gg = grad_scale * dg; pg.gb = grad_scale * db; pg.ga = grad_scale * da;
+        pg.gd = 0.f;
+        pg.final_alpha = final_alpha;
+        pg.final_weight = acc.weight;
+        pg.final_depth = (acc.weight > kEffZero) ? div(acc.depth, acc.weight) : INFINITY;
+        sq = dr * dr + dg * dg + db * db + da * da;
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, d);
+    if (lane == 0 && sq != 0.f) atomicAdd(l2_partials + ((blockIdx.x * 8 + (threadIdx.x >> 5)) & (kLossPartials - 1)), sq);
+
+    float (*q)[kQueueSlots] = s_queue[threadIdx.x >> 5];
+    int nmax = n;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) nmax = max(nmax, __shfl_xor_sync(0xffffffffu, nmax, d));
+    int queued = 0;                                    // uniform over the warp
+    for (int s = 0; s < nmax; s++) {
+        const int k = n - 1 - s;
+        const bool has = k >= 0;
+        const unsigned pushing = __ballot_sync(0xffffffffu, has);
+        if (has) {
+            const float4 k0 = kept[k][0], k1 = kept[k][1], k2 = kept[k][2];
+            QueuedFragment f;
+            f.bx = k0.x; f.by = k0.y; f.bz = k0.z;
+            backward_recurrence(k0.w, k1.x, k1.y, k1.z, k1.w, k2.x, k2.y, pg, st, f);
+            const int slot = queued + __popc(pushing & ((1u << lane) - 1u));
+            q[0][slot] = c.px; q[1][slot] = c.py; q[2][slot] = k2.z;
             q[3][slot] = f.bx; q[4][slot] = f.by; q[5][slot] = f.bz;
             q[6][slot] = f.o_raw; q[7][slot] = f.cr; q[8][slot] = f.cg; q[9][slot] = f.cb; q[10][slot] = f.z;
             q[11][slot] = f.uo; q[12][slot] = f.ur; q[13][slot] = f.ug; q[14][slot] = f.ub; q[15][slot] = f.uz;
@@ -1012,6 +1124,41 @@ static int backward_impl(const float* tri_geo, const float* tri_attr, const int3
     tg::unpack_gradients_kernel<<<(V + 255) / 256, 256, 0, s>>>(gpack, V, (float4*)grad_vertices, grad_colors,
                                                               grad_opacities, accumulate, partials, l2_loss_scale,
                                                               l2_target ? l2_loss_out : nullptr);
+    TG_LAUNCH_CHECK("unpack_gradients_kernel");
+    return TG_OK;
+}
+
+int tg_blend_step_l2(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids, const int32_t* offsets, int V,
+                     int W, int H, int tw, int th, float thr, int max_layers, const float* target, float grad_scale,
+                     float loss_scale, float* loss_out, float* image, float* depthmap, float* final_weights, int32_t* ends,
+                     float* grad_vertices, float* grad_colors, float* grad_opacities, int accumulate, void* scratch,
+                     size_t scratch_bytes, tg_stream_t stream) {
+    if (int s = blend_args(W, H, tw, th, max_layers)) return s;
+    TG_REQUIRE(tw * th <= 256 && max_layers <= tg::kBatchLayers,
+               "the one-kernel step needs tiles of at most 256 pixels and max_layers <= 32 "
+               "(otherwise: tg_blend_forward + tg_blend_backward_l2)");
+    TG_REQUIRE(V > 0, "V must be positive");
+    TG_REQUIRE(offsets && image && depthmap && final_weights && ends && target && loss_out, "null pointer");
+    TG_REQUIRE(grad_vertices && grad_colors && grad_opacities && scratch, "null gradient / scratch pointer");
+    TG_REQUIRE(((uintptr_t)image & 15) == 0 && ((uintptr_t)target & 15) == 0 && ((uintptr_t)tri_geo & 15) == 0 &&
+                   ((uintptr_t)tri_attr & 15) == 0 && ((uintptr_t)grad_vertices & 15) == 0 && ((uintptr_t)scratch & 15) == 0,
+               "image / target / tri_geo / tri_attr / grad_vertices / scratch must be 16-byte aligned");
+    if (scratch_bytes < tg_backward_scratch_bytes(V)) {
+        tg_host::set_error("backward scratch: need %zu bytes, got %zu", tg_backward_scratch_bytes(V), scratch_bytes);
+        return TG_ERR_WORKSPACE;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    float4* gpack = (float4*)scratch;
+    float* partials = (float*)((char*)scratch + (size_t)V * 32);
+    TG_CUDA(cudaMemsetAsync(gpack, 0, (size_t)V * 32 + sizeof(float) * tg::kLossPartials, s));
+    const tg::BlendParams P = make_params(tri_geo, tri_attr, sorted_ids, offsets, W, H, tw, th, thr, max_layers);
+    const int tiles = P.tiles_x * ((H + th - 1) / th);
+    const int threads = ((tw * th + 31) / 32) * 32;
+    tg::blend_step_l2_kernel<256><<<tiles, threads, 0, s>>>(P, (float4*)image, depthmap, final_weights, ends,
+                                                            (const float4*)target, grad_scale, partials, gpack);
+    TG_LAUNCH_CHECK("blend_step_l2_kernel");
+    tg::unpack_gradients_kernel<<<(V + 255) / 256, 256, 0, s>>>(gpack, V, (float4*)grad_vertices, grad_colors,
+                                                              grad_opacities, accumulate, partials, loss_scale, loss_out);
     TG_LAUNCH_CHECK("unpack_gradients_kernel");
     return TG_OK;
 }

@@ -144,6 +144,28 @@ def blend_forward(sc, geo, attr, ids, offsets, thr=1 / 256, per_pixel_sort=True,
     return image, depth, fw, ends, sel
 
 
+def blend_step_l2(sc, geo, attr, ids, offsets, target, thr=1 / 256, max_layers=32):
+    """Forward + backward of mean((image - target)^2) in one kernel.
+    Returns (image, depthmap, final_weights, ends), (gV, gC, gO), loss."""
+    H, W, V = sc.height, sc.width, sc.num_vertices
+    image = torch.empty((H, W, 4), dtype=torch.float32, device="cuda")
+    depth = torch.empty((H, W), dtype=torch.float32, device="cuda")
+    fw = torch.empty((H, W), dtype=torch.float32, device="cuda")
+    ends = torch.empty((H, W), dtype=torch.int32, device="cuda")
+    gV = torch.zeros((V, 4), dtype=torch.float32, device="cuda")
+    gC = torch.zeros((V, 3), dtype=torch.float32, device="cuda")
+    gO = torch.zeros((V,), dtype=torch.float32, device="cuda")
+    loss = torch.zeros((), dtype=torch.float32, device="cuda")
+    nscratch = N.lib().tg_backward_scratch_bytes(V)
+    scratch = torch.empty(nscratch, dtype=torch.uint8, device="cuda")
+    npix = float(W * H * 4)
+    N.check("blend_step_l2", N.lib().tg_blend_step_l2(
+        ptr(geo), ptr(attr), ptr(ids), ptr(offsets), V, W, H, sc.tile_width, sc.tile_height, float(thr), int(max_layers),
+        ptr(target), 2.0 / npix, 1.0 / npix, ptr(loss), ptr(image), ptr(depth), ptr(fw), ptr(ends), ptr(gV), ptr(gC),
+        ptr(gO), 0, ptr(scratch), nscratch, stream()))
+    return (image, depth, fw, ends), (gV, gC, gO), loss
+
+
 def blend_backward(sc, geo, attr, ids, offsets, fwd, gimage, gdepth, per_pixel_sort=True, max_layers=32):
     image, depth, fw, ends, sel = fwd
     V = sc.num_vertices

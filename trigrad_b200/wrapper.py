@@ -169,6 +169,62 @@ def backward_l2_native(target, saved, V, width, height, tile_width, tile_height,
     return gV, gC, gO
 
 
+def step_l2_native(vertices, indices, colors, opacities, target, width, height, tile_width, tile_height,
+                   early_stopping_threshold, max_layers, out, loss_out, accumulate=True, record_timing=False):
+    """One view of an optimisation step in one native call: tile lists, forward, ``mean((image - target)**2)``
+    and its gradients (forward and backward run in a single kernel).
+
+    Default per-pixel mode with ``1 <= max_layers <= 32`` and tiles of at most 256 pixels.  ``out`` = (gV [V,4],
+    gC [V,3], gO [V]) and the 0-d float32 ``loss_out`` are overwritten, or added to when ``accumulate`` is true.
+    Returns (image, depthmap, final_weights, ends, timings).
+    """
+    lib = N.lib()
+    device = vertices.device
+    T, V = indices.shape[0], vertices.shape[0]
+    tiles = ((width + tile_width - 1) // tile_width) * ((height + tile_height - 1) // tile_height)
+    npix = float(width * height * 4)
+    with torch.cuda.device(device):
+        st = _state(device)
+        stream = torch.cuda.current_stream(device).cuda_stream
+        f32 = dict(dtype=torch.float32, device=device)
+        image = torch.empty((height, width, 4), **f32)
+        depthmap = torch.empty((height, width), **f32)
+        final_weights = torch.empty((height, width), **f32)
+        ends = torch.empty((height, width), dtype=torch.int32, device=device)
+        tri_geo = torch.empty((T, N.GEO_WORDS), **f32)
+        tri_attr = torch.empty((T, N.ATTR_WORDS), **f32)
+        offsets = torch.empty(tiles + 1, dtype=torch.int32, device=device)
+        nscratch = lib.tg_backward_scratch_bytes(V)
+        scratch = torch.empty(nscratch, dtype=torch.uint8, device=device)
+        stage_ms = (C.c_float * 5)() if record_timing else None
+        gV, gC, gO = out
+        target = target.contiguous()
+        cap = max(int(st.k_estimate * 1.25) + 1024, 2 * T + 1024)
+        while True:
+            sorted_ids = torch.empty(cap, dtype=torch.int32, device=device)
+            ws = st.ensure_workspace(lib.tg_forward_workspace_bytes(T, tiles, cap))
+            base = (ws.data_ptr() + 255) // 256 * 256
+            info = st.info[st.next_slot()]
+            status = lib.tg_render_step_l2(
+                _ptr(vertices), _ptr(indices), _ptr(colors), _ptr(opacities), T, V, width, height, tile_width, tile_height,
+                float(early_stopping_threshold), int(max_layers), _ptr(target), 2.0 / npix, 1.0 / npix, _ptr(loss_out),
+                _ptr(image), _ptr(depthmap), _ptr(final_weights), _ptr(ends), _ptr(tri_geo), _ptr(tri_attr),
+                _ptr(sorted_ids), cap, _ptr(offsets), _ptr(gV), _ptr(gC), _ptr(gO), int(bool(accumulate)),
+                C.c_void_p(base), ws.numel() - (base - ws.data_ptr()), _ptr(scratch), nscratch,
+                C.c_void_p(info.data_ptr()), stage_ms, C.c_void_p(stream))
+            K = int(info[0])
+            if status == N.TG_ERR_CAPACITY:
+                cap = int(K * 1.25) + 1024
+                continue
+            N.check("render_step_l2", status)
+            break
+        st.k_estimate = K
+        timings = None
+        if record_timing:
+            timings = {k: float(stage_ms[i]) / 1000.0 for i, k in enumerate(TIMING_KEYS)}
+    return image, depthmap, final_weights, ends, timings
+
+
 class Renderer(Function):
     @staticmethod
     def forward(ctx, vertices: torch.Tensor, indices: torch.Tensor, colors: torch.Tensor, opacities: torch.Tensor,
