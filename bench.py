@@ -237,8 +237,8 @@ def main() -> None:
     B = max(1, args.views_per_gpu)
     # rank r renders views [r*B, (r+1)*B) of the same mesh; every view has its own target image.
     # Random-triangle scenes: a view is the NDC vertex array rotated in the image plane.  Camera-ring scene
-    # (cfg4): a view is a 4x4 projection*view matrix and the world -> NDC projection runs in torch (outside
-    # the hot path, as in the reference viewer), so the gradients are world-space.
+    # (cfg4): a view is a 4x4 projection*view matrix (kept on the host, passed by value to the projection
+    # kernel and to its VJP), so the gradients are world-space.
     camera_ring = "mesh" in scene.meta
     if camera_ring:
         views_np = [scene.meta["pvs"][(rank * B + b) % 64] for b in range(B)]
@@ -253,7 +253,7 @@ def main() -> None:
     i = torch.from_numpy(scene.indices).to(dev)
     c = torch.from_numpy(scene.colors).to(dev)
     o = torch.from_numpy(scene.opacities).to(dev)
-    dv = [torch.from_numpy(x).to(dev) for x in views_np]
+    dv = list(views_np) if camera_ring else [torch.from_numpy(x).to(dev) for x in views_np]
     dt = [torch.from_numpy(x).to(dev) for x in targets_np]
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)    # > L2 (126 MB)
     pos_comp = 3 if camera_ring else 4
@@ -270,16 +270,11 @@ def main() -> None:
 
         Random-triangle scenes go through ``views.l2_view_step`` (forward, then the backward with the
         mean-squared-error gradient formed inside the kernel).  The camera-ring scene adds the world -> NDC
-        projection and its VJP in torch around the same two calls.
+        projection kernel and its VJP kernel around the same calls (``views.l2_world_view_step``).
         """
         if camera_ring:
-            p = points.detach().requires_grad_(True)
-            verts = Vw.project(p, v)
-            gverts = torch.zeros_like(verts)
-            Vw.l2_view_step(verts.detach(), i, c, o, target, W, H, gverts, grads.colors, grads.opacities, grads.loss,
-                            scene.tile_width, scene.tile_height, one_kernel=args.one_kernel)
-            (gp,) = torch.autograd.grad(verts, p, grad_outputs=gverts)
-            grads.points.add_(gp)
+            Vw.l2_world_view_step(points, v, i, c, o, target, W, H, grads.points, grads.colors, grads.opacities,
+                                  grads.loss, scene.tile_width, scene.tile_height, one_kernel=args.one_kernel)
         else:
             Vw.l2_view_step(v, i, c, o, target, W, H, grads.points, grads.colors, grads.opacities, grads.loss,
                             scene.tile_width, scene.tile_height, one_kernel=args.one_kernel)
@@ -306,7 +301,8 @@ def main() -> None:
             with torch.cuda.stream(stream):
                 if ready is not None:
                     stream.wait_event(ready)
-                    v.record_stream(stream)
+                    if isinstance(v, torch.Tensor):
+                        v.record_stream(stream)
                     t.record_stream(stream)
                 render_view(v, t, grads if si == 0 else side_grads[si - 1])
         for st, gb in zip(side_streams, side_grads):
@@ -360,7 +356,7 @@ def main() -> None:
     # view b+1 run on a second stream while view b renders.
     hi, hc, ho = (torch.from_numpy(x).pin_memory() for x in (scene.indices, scene.colors, scene.opacities))
     hp = torch.from_numpy(scene.meta["mesh"].points).pin_memory() if camera_ring else None
-    hv = [torch.from_numpy(x).pin_memory() for x in views_np]
+    hv = [] if camera_ring else [torch.from_numpy(x).pin_memory() for x in views_np]   # camera matrices stay on the host
     ht = [torch.from_numpy(x).pin_memory() for x in targets_np]
     out_g = torch.empty_like(grads.flat, device="cpu").pin_memory()      # gradients and, last element, the loss
     h2d = sum(t.numel() * t.element_size() for t in [hi, hc, ho] + hv + ht + ([hp] if camera_ring else []))
@@ -378,7 +374,8 @@ def main() -> None:
             c = hc.to(dev, non_blocking=True)
             o = ho.to(dev, non_blocking=True)
             for b in range(B):
-                vb, tb = hv[b].to(dev, non_blocking=True), ht[b].to(dev, non_blocking=True)
+                vb = views_np[b] if camera_ring else hv[b].to(dev, non_blocking=True)
+                tb = ht[b].to(dev, non_blocking=True)
                 ev = torch.cuda.Event()
                 ev.record(copy_stream)
                 staged.append((vb, tb, ev))

@@ -218,6 +218,19 @@ int tg_render_step_l2(const float* vertices, const int32_t* indices, const float
                       float* grad_colors, float* grad_opacities, int accumulate, void* workspace, size_t workspace_bytes,
                       void* scratch, size_t scratch_bytes, uint32_t* info_host, float* stage_ms_host, tg_stream_t stream);
 
+/* ---- the step before the path: world -> render-space vertices and the VJP ------------------------------
+ * points [V,3] world positions, pv_host: 16 floats in HOST memory, the row-major projection * view
+ * matrix.  vertices[v] = (clip.x / clip.w, clip.y / clip.w, clip.z / clip.w, 1 / clip.w) with
+ * clip = PV * (x, y, z, 1): the tensor operations of the reference's viewer (viewer.py:271-278) in one
+ * kernel.  tg_project_backward: grad_points [V,3] receives (accumulate = 0) or is increased by
+ * (accumulate = 1) the vector-Jacobian product with grad_vertices [V,4] - what torch autograd does for
+ * those tensor operations.  No near-plane handling: points with clip.w = 0 give infinities, as in the
+ * reference.
+ */
+int tg_project(const float* points, int V, const float* pv_host, float* vertices, tg_stream_t stream);
+int tg_project_backward(const float* points, int V, const float* pv_host, const float* grad_vertices, float* grad_points,
+                        int accumulate, tg_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -263,3 +263,33 @@ def render_l2(scene, dtype=np.float32, per_pixel_sort=True, max_layers=32, thr=1
     g = backward(v, scene.indices, c, o, scene.width, scene.height, f, gi, gd, scene.tile_width, scene.tile_height,
                  per_pixel_sort, max_layers, tile_stride=tile_stride)
     return loss, f, g
+
+
+def project(points, pv):
+    """World points [V,3] -> render vertices (x/w, y/w, z/w, 1/w) with clip = PV (x, y, z, 1); in the dtype of `points`.
+
+    Restates the tensor operations of the reference's viewer (``viewer.py:271-278``).
+    """
+    pts = np.asarray(points)
+    dt = pts.dtype
+    h = np.concatenate([pts, np.ones((pts.shape[0], 1), dt)], axis=1)
+    clip = h @ np.asarray(pv, dt).T
+    out = np.empty_like(clip)
+    out[:, :3] = clip[:, :3] / clip[:, 3:4]
+    out[:, 3] = dt.type(1) / clip[:, 3]
+    return out
+
+
+def project_vjp(points, pv, grad_vertices):
+    """Vector-Jacobian product of `project`: gradient w.r.t. the points [V,3] given the gradient w.r.t. the vertices [V,4]."""
+    pts = np.asarray(points)
+    dt = pts.dtype
+    pvm = np.asarray(pv, dt)
+    g = np.asarray(grad_vertices, dt)
+    h = np.concatenate([pts, np.ones((pts.shape[0], 1), dt)], axis=1)
+    clip = h @ pvm.T
+    iw = dt.type(1) / clip[:, 3]
+    d = np.empty_like(clip)
+    d[:, :3] = g[:, :3] * iw[:, None]
+    d[:, 3] = -(np.sum(d[:, :3] * clip[:, :3], axis=1) + g[:, 3] * iw) * iw
+    return (d @ pvm)[:, :3]

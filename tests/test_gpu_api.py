@@ -238,3 +238,53 @@ def test_live_reference_leg(make, sort):
         assert Hh.rel_l2(gV, r_gV.cpu().numpy()) <= 1e-4
         assert Hh.rel_l2(gC, r_gC.cpu().numpy()) <= 1e-4
         assert Hh.rel_l2(gO, r_gO.cpu().numpy()) <= 1e-4
+
+
+def test_projection_kernels_vs_oracle_and_autograd():
+    """tg_project / tg_project_backward against the numpy restatement of the viewer's tensor operations
+    (fp64) and against torch autograd on views.project."""
+    from trigrad_b200 import views
+    mesh = S.displaced_sphere(4)
+    pv = S.camera_ring(8)[3]
+    pts = Hh.cuda(mesh.points)
+    verts = views.project_native(pts, pv)
+    ref = O.project(mesh.points.astype(np.float64), pv)
+    assert Hh.rel_err(verts.cpu().numpy(), ref) <= 1e-6
+    rng = np.random.default_rng(5)
+    g = rng.normal(size=ref.shape).astype(np.float32)
+    gp = torch.zeros_like(pts)
+    views.project_backward_native(pts, pv, Hh.cuda(g), gp, accumulate=False)
+    views.project_backward_native(pts, pv, Hh.cuda(g), gp, accumulate=True)          # twice: accumulation
+    ref_g = 2 * O.project_vjp(mesh.points.astype(np.float64), pv, g.astype(np.float64))
+    assert Hh.rel_l2(gp.cpu().numpy(), ref_g) <= 1e-6
+    p = pts.clone().requires_grad_()
+    (ga,) = torch.autograd.grad(views.project(p, Hh.cuda(pv)), p, grad_outputs=Hh.cuda(g))
+    assert Hh.rel_l2(gp.cpu().numpy(), 2 * ga.cpu().numpy()) <= 1e-5
+
+
+def test_world_space_view_step_matches_autograd():
+    """views.l2_world_view_step (projection kernel, rendering step, projection VJP kernel) against
+    render() + torch autograd through views.project."""
+    from trigrad_b200 import views
+    mesh = S.displaced_sphere(4)
+    pv = S.camera_ring(8)[1]
+    W, H = 320, 192
+    pts, i, c, o = Hh.cuda(mesh.points), Hh.cuda(mesh.indices), Hh.cuda(mesh.colors), Hh.cuda(mesh.opacities)
+    V = pts.shape[0]
+    target = torch.rand((H, W, 4), device="cuda")
+    gP, gC, gO = torch.zeros((V, 3), device="cuda"), torch.zeros((V, 3), device="cuda"), torch.zeros((V,), device="cuda")
+    loss = torch.zeros((), device="cuda")
+    img = views.l2_world_view_step(pts, pv, i, c, o, target, W, H, gP, gC, gO, loss)
+    # reference: the same render-space vertices through render() + autograd, then the VJP of the torch projection
+    vv = views.project_native(pts, pv).requires_grad_()
+    cc, oo = c.clone().requires_grad_(), o.clone().requires_grad_()
+    image, _ = trigrad_b200.render(vv, i, cc, oo, W, H)
+    l = torch.mean((image - target) ** 2)
+    gv, gc, go = torch.autograd.grad(l, (vv, cc, oo))
+    p = pts.clone().requires_grad_()
+    (gp,) = torch.autograd.grad(views.project(p, Hh.cuda(pv)), p, grad_outputs=gv)
+    torch.cuda.synchronize()
+    assert torch.equal(img, image)
+    assert abs(float(loss) - float(l)) <= 1e-5 * float(l)
+    for a, b in zip((gP, gC, gO), (gp, gc, go)):
+        assert Hh.rel_l2(a.cpu().numpy(), b.cpu().numpy()) <= 1e-5

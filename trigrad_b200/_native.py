@@ -44,6 +44,8 @@ SIGNATURES = {
     "tg_forward_workspace_bytes": (_sz, [_i, _i, _u32]),
     "tg_render_forward": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                _u32, _vp, _vp, _sz, _vp, _vp, _vp]),
+    "tg_project": (_i, [_vp, _i, _vp, _vp, _vp]),
+    "tg_project_backward": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp]),
     "tg_render_step_l2": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _f, _f, _vp, _vp, _vp, _vp, _vp, _vp,
                                _vp, _vp, _u32, _vp, _vp, _vp, _vp, _i, _vp, _sz, _vp, _sz, _vp, _vp, _vp]),
 }

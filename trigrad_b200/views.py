@@ -126,6 +126,71 @@ def l2_view_step(vertices: torch.Tensor, indices: torch.Tensor, colors: torch.Te
     return image
 
 
+def _pv_host(pv):
+    """Row-major 4x4 float32 matrix in host memory (a CUDA tensor is copied down, which synchronises)."""
+    import numpy as np
+
+    if isinstance(pv, torch.Tensor):
+        pv = pv.detach().cpu().numpy()
+    m = np.ascontiguousarray(pv, dtype=np.float32)
+    if m.shape != (4, 4):
+        raise ValueError("pv must be a 4x4 matrix")
+    return m
+
+
+def project_native(points: torch.Tensor, pv) -> torch.Tensor:
+    """World points (V,3) -> render vertices (V,4) in one kernel (``tg_project``); ``pv`` best given on the host."""
+    import ctypes as C
+
+    from . import _native as N
+
+    _w.check_tensor(points, "points", (points.shape[0], 3))
+    m = _pv_host(pv)
+    out = torch.empty((points.shape[0], 4), dtype=torch.float32, device=points.device)
+    with torch.cuda.device(points.device):
+        stream = torch.cuda.current_stream(points.device).cuda_stream
+        N.check("project", N.lib().tg_project(C.c_void_p(points.data_ptr()), points.shape[0], m.ctypes.data_as(C.c_void_p),
+                                              C.c_void_p(out.data_ptr()), C.c_void_p(stream)))
+    return out
+
+
+def project_backward_native(points: torch.Tensor, pv, grad_vertices: torch.Tensor, grad_points: torch.Tensor,
+                            accumulate: bool = True) -> torch.Tensor:
+    """``grad_points (V,3)`` += (or =) the vector-Jacobian product of ``project_native`` with ``grad_vertices (V,4)``."""
+    import ctypes as C
+
+    from . import _native as N
+
+    V = points.shape[0]
+    _w.check_tensor(points, "points", (V, 3))
+    _w.check_tensor(grad_vertices, "grad_vertices", (V, 4))
+    _w.check_tensor(grad_points, "grad_points", (V, 3))
+    m = _pv_host(pv)
+    with torch.cuda.device(points.device):
+        stream = torch.cuda.current_stream(points.device).cuda_stream
+        N.check("project_backward", N.lib().tg_project_backward(
+            C.c_void_p(points.data_ptr()), V, m.ctypes.data_as(C.c_void_p), C.c_void_p(grad_vertices.data_ptr()),
+            C.c_void_p(grad_points.data_ptr()), int(bool(accumulate)), C.c_void_p(stream)))
+    return grad_points
+
+
+def l2_world_view_step(points: torch.Tensor, pv, indices: torch.Tensor, colors: torch.Tensor, opacities: torch.Tensor,
+                       target: torch.Tensor, width: int, height: int, grad_points: torch.Tensor, grad_colors: torch.Tensor,
+                       grad_opacities: torch.Tensor, loss: torch.Tensor, tile_width: int = 16, tile_height: int = 16,
+                       early_stopping_threshold: float = 1 / 256, max_layers: int = 32,
+                       one_kernel: bool = False) -> torch.Tensor:
+    """``l2_view_step`` for a mesh in world space seen through the 4x4 matrix ``pv``: projection, rendering step and
+    the projection's VJP without torch tensor operations.  ``grad_points [V,3]`` accumulates the world-space
+    gradient; the other arguments are those of ``l2_view_step``.  Returns the rendered image."""
+    m = _pv_host(pv)
+    verts = project_native(points, m)
+    gverts = torch.zeros_like(verts)
+    image = l2_view_step(verts, indices, colors, opacities, target, width, height, gverts, grad_colors, grad_opacities, loss,
+                         tile_width, tile_height, early_stopping_threshold, max_layers, one_kernel)
+    project_backward_native(points, m, gverts, grad_points, accumulate=True)
+    return image
+
+
 def allreduce_gradients(grads: GradBuffer, loss: torch.Tensor | None = None, group=None) -> None:
     """Sum the gradient buffer (and optionally the loss) over all ranks, in place, with one collective each."""
     import torch.distributed as dist
