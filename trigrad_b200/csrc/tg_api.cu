@@ -11,7 +11,7 @@ struct ForwardWorkspace {
     uint64_t* entries;
     // Everything from `status` up to `clear_end` must be zero when the kernels start: one memset.
     uint32_t* status;
-    void* scan_scratch;        // fused preprocess + scan: ticket, finished-CTA counter, look-back words
+    void* scan_scratch;        // binning kernel: finished-CTA counter, totals of its CTAs
     void* tile_scan_scratch;   // device-wide scan of the tile counts (only beyond kTileScanByLastCta tiles)
     uint32_t* long_list;       // work lists of the per-tile sort; only their four head words need clearing
     uint32_t* tile_cursor;     // [tiles]
@@ -107,8 +107,8 @@ static int build_tile_lists(const float* vertices, const int32_t* indices, const
     TG_CUDA(cudaEventRecord(k_ready, s));
     // Entries are written while K travels to the host: the kernel drops those beyond the capacity, and
     // nothing that reads them is launched before K has been checked.
-    st = tg_host::emit_entries(vertices, indices, T, W, H, tw, th, ws.tri_offsets, ws.tile_cursor, ws.entries,
-                               list_capacity, s);
+    st = tg_host::emit_entries(vertices, indices, T, W, H, tw, th, ws.tri_offsets, ws.scan_scratch, ws.tile_cursor,
+                               ws.entries, list_capacity, s);
     if (st) return st;
     TG_CUDA(cudaEventSynchronize(k_ready));
     const uint32_t K = info_host[0];

@@ -193,20 +193,23 @@ __global__ void __launch_bounds__(kScanThreads) scan_kernel(const uint32_t* __re
     }
 }
 
-// Stages 1 and 2 in one kernel (the forward path uses this): the CTA that preprocesses 256 triangles
-// scans their tile counts and resolves its prefix by look-back, so the counts never travel through
-// memory and one launch is saved.  Partitions are taken in ticket order.
+// Stages 1 and 2 as the forward path runs them: the CTA that preprocesses 256 triangles scans their
+// tile counts among themselves (`tri_offsets[t]` = entries of the CTA's earlier triangles) and leaves
+// its total in `part_total`; no CTA waits for another.  The writer of the entries only needs these local
+// offsets, because it places every entry through its tile's cursor.
 //
-// With `bin.tile_cursor` set the CTA also counts its (triangle, tile) entries per tile, one thread per
-// entry, and the CTA that finishes last turns the counts into the exclusive tile offsets, in place
+// The CTA also counts its (triangle, tile) entries per tile, one thread per entry, and the CTA that
+// finishes last adds up the totals (K) and turns the tile counts into the exclusive tile offsets, in place
 // (`tile_cursor[t]` = first slot of tile t, advanced later by the entry writer) and in `bin.offsets`.
 struct TileBinArgs {
-    uint32_t* tile_cursor;   // [tiles], zero on entry; nullptr: no per-tile counting
+    uint32_t* tile_cursor;   // [tiles], zero on entry
     int32_t* offsets;        // [tiles + 1], written when scan_here
     uint32_t* done;          // zero on entry: counts finished CTAs
     int tiles;
     int scan_here;           // 1: the last CTA scans the tile counts; 0: the host launches a scan
     uint32_t* longest;       // written when scan_here: the largest tile count
+    uint32_t* part_total;    // [CTAs] entries of each CTA's triangles
+    uint32_t* k_out;         // K = all entries
 };
 
 // Exclusive scan of cursor[0..tiles) by one CTA of 256 threads, in place, copy in offsets[0..tiles].
@@ -278,26 +281,21 @@ __device__ void tile_offsets_by_one_cta(uint32_t* cursor, int32_t* offsets, int 
     }
 }
 
-__global__ void __launch_bounds__(256, 6) preprocess_scan_kernel(const float4* __restrict__ vertices,
-                                                              const int* __restrict__ indices,
-                                                              const float* __restrict__ colors,
-                                                              const float* __restrict__ opacities, int T, int W, int H,
-                                                              int tw, int th, int tiles_x, int tiles_y,
-                                                              float4* __restrict__ tri_geo, float4* __restrict__ tri_attr,
-                                                              uint32_t* __restrict__ tri_offsets /*[T+1]*/,
-                                                              uint32_t* ticket, uint64_t* part_status, uint32_t* status,
-                                                              TileBinArgs bin) {
-    __shared__ uint32_t s_part;
+__global__ void __launch_bounds__(256, 6) preprocess_count_kernel(const float4* __restrict__ vertices,
+                                                               const int* __restrict__ indices,
+                                                               const float* __restrict__ colors,
+                                                               const float* __restrict__ opacities, int T, int W, int H,
+                                                               int tw, int th, int tiles_x, int tiles_y,
+                                                               float4* __restrict__ tri_geo, float4* __restrict__ tri_attr,
+                                                               uint32_t* __restrict__ tri_offsets /*[T], CTA-local*/,
+                                                               TileBinArgs bin) {
     __shared__ uint32_t s_warp[8];
-    __shared__ uint32_t s_excl;
     __shared__ uint32_t s_buf[kTileScanRound];
     uint32_t* s_loc = s_buf;                 // [257] exclusive offsets of the CTA's triangles within the CTA
     int* s_rect = (int*)s_buf + 257;         // [768] x0, y0, rows of each triangle's tile rectangle
     __shared__ bool s_last;
     const int tid = threadIdx.x;
-    if (tid == 0) s_part = atomicAdd(ticket, 1u);
-    __syncthreads();
-    const int p = (int)s_part, num_parts = gridDim.x;
+    const int p = blockIdx.x, num_parts = gridDim.x;
     const int t = p * 256 + tid;
     Rect r = {0, 0, 0, 0};
     const uint32_t count = (t < T) ? preprocess_triangle(t, vertices, indices, colors, opacities, W, H, tw, th, tiles_x,
@@ -320,23 +318,16 @@ __global__ void __launch_bounds__(256, 6) preprocess_scan_kernel(const float4* _
         total += x;
     }
     const uint32_t local_excl = warp_off + incl - count;
-    if (bin.tile_cursor) {
-        s_loc[tid] = local_excl;
-        if (tid == 0) s_loc[256] = total;
-        s_rect[3 * tid] = r.x0;
-        s_rect[3 * tid + 1] = r.y0;
-        s_rect[3 * tid + 2] = r.y1 - r.y0 + 1;
+    s_loc[tid] = local_excl;
+    s_rect[3 * tid] = r.x0;
+    s_rect[3 * tid + 1] = r.y0;
+    s_rect[3 * tid + 2] = r.y1 - r.y0 + 1;
+    if (tid == 0) {
+        s_loc[256] = total;
+        bin.part_total[p] = total;
     }
-    if (warp == 0) {
-        const uint32_t excl = lookback_exclusive(p, total, part_status, status);
-        if (lane_id() == 0) {
-            s_excl = excl;
-            if (p == num_parts - 1) tri_offsets[T] = excl + total;
-        }
-    }
+    if (t < T) tri_offsets[t] = local_excl;
     __syncthreads();
-    if (t < T) tri_offsets[t] = s_excl + local_excl;
-    if (!bin.tile_cursor) return;
 
     for (uint32_t e = tid; e < total; e += 256) {
         int lo = 0, hi = 256;                 // largest i with s_loc[i] <= e
@@ -349,7 +340,6 @@ __global__ void __launch_bounds__(256, 6) preprocess_scan_kernel(const float4* _
         const int tx = s_rect[3 * lo] + (int)(local / ny), ty = s_rect[3 * lo + 1] + (int)(local % ny);
         atomicAdd(&bin.tile_cursor[ty * tiles_x + tx], 1u);
     }
-    if (!bin.scan_here) return;
     __syncthreads();                          // the CTA's counts are issued; one cumulative fence publishes them
     if (tid == 0) {
         __threadfence();
@@ -358,7 +348,21 @@ __global__ void __launch_bounds__(256, 6) preprocess_scan_kernel(const float4* _
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    tile_offsets_by_one_cta(bin.tile_cursor, bin.offsets, bin.tiles, bin.longest, s_buf, s_warp);
+    // K: sum of the CTA totals
+    uint32_t k = 0;
+    for (int i = tid; i < num_parts; i += 256) k += __ldcg(bin.part_total + i);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) k += __shfl_xor_sync(0xffffffffu, k, d);
+    __syncthreads();
+    if (lane_id() == 0) s_warp[warp] = k;
+    __syncthreads();
+    if (tid == 0) {
+        k = 0;
+#pragma unroll
+        for (int w = 0; w < 8; w++) k += s_warp[w];
+        *bin.k_out = k;
+    }
+    if (bin.scan_here) tile_offsets_by_one_cta(bin.tile_cursor, bin.offsets, bin.tiles, bin.longest, s_buf, s_warp);
 }
 
 // ================================================================================================
@@ -464,7 +468,8 @@ __global__ void __launch_bounds__(kEmitThreads) emit_keys_kernel(const float4* _
                                                                  const uint32_t* __restrict__ tri_offsets,
                                                                  uint64_t* __restrict__ keys, uint32_t* __restrict__ ids,
                                                                  uint32_t capacity, HistArgs hist,
-                                                                 uint32_t* __restrict__ tile_cursor) {
+                                                                 uint32_t* __restrict__ tile_cursor,
+                                                                 const uint32_t* __restrict__ part_total) {
     __shared__ EmitTri s_tri[kEmitThreads];
     __shared__ uint32_t s_off[kEmitThreads + 1];
     __shared__ uint32_t s_hist[kMaxPasses * kRadix];
@@ -492,7 +497,8 @@ __global__ void __launch_bounds__(kEmitThreads) emit_keys_kernel(const float4* _
         s_tri[tid] = e;
         s_off[tid] = tri_offsets[t];
     }
-    if (tid == 0) s_off[ntri] = tri_offsets[t0 + ntri];
+    // DIRECT: the offsets are local to the 256 triangles of the CTA and its total stands in a separate array
+    if (tid == 0) s_off[ntri] = DIRECT ? part_total[blockIdx.x] : tri_offsets[t0 + ntri];
     __syncthreads();
     const uint32_t first = s_off[0], total = s_off[ntri] - first;
     for (uint32_t e = tid; e < total; e += kEmitThreads) {
@@ -565,40 +571,39 @@ static int check_dims_internal(int T, int W, int H, int tw, int th) {
     return TG_OK;
 }
 
-// ticket (4) + finished-CTA counter (4) + one look-back word per partition
-size_t preprocess_scan_scratch_bytes(int T) { return 8 + 8 * ((size_t)(T > 0 ? (T + 255) / 256 : 0) + 1); }
+// finished-CTA counter (4, zero on entry) + pad (4) + one total per CTA of 256 triangles
+size_t preprocess_scan_scratch_bytes(int T) { return 8 + 4 * ((size_t)(T > 0 ? (T + 255) / 256 : 0) + 1); }
 
-// `scratch` (ticket, counter and partition words) and, when given, `tile_cursor[tiles]` must have been
-// zeroed by the caller.  With `tile_cursor` the tile offsets are produced as well (in `tile_cursor` itself
-// and in `offsets[tiles + 1]`) and `tri_offsets` has T + 2 words: [T + 1] receives the longest tile list.
-// Beyond kTileScanByLastCta tiles a device-wide scan makes the offsets, for which `tile_scan_scratch`
+// Per-triangle records, CTA-local triangle offsets (`tri_offsets[T + 2]`: [t] local to the triangle's
+// CTA of 256, [T] = K, [T + 1] = longest tile list), tile offsets in `tile_cursor[tiles]` and
+// `offsets[tiles + 1]`.  The first word of `scratch` and `tile_cursor` must have been zeroed by the caller.
+// Beyond kTileScanByLastCta tiles a device-wide scan makes the tile offsets, for which `tile_scan_scratch`
 // (zeroed, tg_scan_scratch_bytes(tiles) bytes) is needed, and [T + 1] is set to UINT32_MAX (not known).
 int preprocess_scan(const float* vertices, const int32_t* indices, const float* colors, const float* opacities, int T,
                     int W, int H, int tw, int th, float* tri_geo, float* tri_attr, uint32_t* tri_offsets, void* scratch,
                     uint32_t* status, uint32_t* tile_cursor, int32_t* offsets, void* tile_scan_scratch,
                     cudaStream_t stream) {
     if (int s = check_dims_internal(T, W, H, tw, th)) return s;
-    TG_REQUIRE(tri_offsets && scratch && status, "null pointer");
+    TG_REQUIRE(tri_offsets && scratch && status && tile_cursor && offsets, "null pointer");
     const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
     const int tiles = tiles_x * tiles_y;
     if (T == 0) {
-        TG_CUDA(cudaMemsetAsync(tri_offsets, 0, sizeof(uint32_t) * (tile_cursor ? 2 : 1), stream));
-        if (tile_cursor) TG_CUDA(cudaMemsetAsync(offsets, 0, sizeof(int32_t) * ((size_t)tiles + 1), stream));
+        TG_CUDA(cudaMemsetAsync(tri_offsets, 0, sizeof(uint32_t) * 2, stream));
+        TG_CUDA(cudaMemsetAsync(offsets, 0, sizeof(int32_t) * ((size_t)tiles + 1), stream));
         return TG_OK;
     }
     TG_REQUIRE(vertices && indices && colors && opacities && tri_geo && tri_attr, "null pointer");
     TG_REQUIRE(((uintptr_t)vertices & 15) == 0 && ((uintptr_t)tri_geo & 15) == 0 && ((uintptr_t)tri_attr & 15) == 0,
                "vertices / tri_geo / tri_attr must be 16-byte aligned");
-    TG_REQUIRE(!tile_cursor || offsets, "null offsets");
     const bool by_last_cta = tiles <= tg::kTileScanByLastCta;
-    TG_REQUIRE(!tile_cursor || by_last_cta || tile_scan_scratch, "null tile scan scratch");
-    const tg::TileBinArgs bin = {tile_cursor, offsets, (uint32_t*)scratch + 1, tiles, by_last_cta ? 1 : 0,
-                                 tri_offsets + T + 1};
-    tg::preprocess_scan_kernel<<<(T + 255) / 256, 256, 0, stream>>>(
+    TG_REQUIRE(by_last_cta || tile_scan_scratch, "null tile scan scratch");
+    const tg::TileBinArgs bin = {tile_cursor, offsets, (uint32_t*)scratch, tiles, by_last_cta ? 1 : 0,
+                                 tri_offsets + T + 1, (uint32_t*)scratch + 2, tri_offsets + T};
+    tg::preprocess_count_kernel<<<(T + 255) / 256, 256, 0, stream>>>(
         (const float4*)vertices, indices, colors, opacities, T, W, H, tw, th, tiles_x, tiles_y, (float4*)tri_geo,
-        (float4*)tri_attr, tri_offsets, (uint32_t*)scratch, (uint64_t*)((char*)scratch + 8), status, bin);
-    TG_LAUNCH_CHECK("preprocess_scan_kernel");
-    if (tile_cursor && !by_last_cta) {
+        (float4*)tri_attr, tri_offsets, bin);
+    TG_LAUNCH_CHECK("preprocess_count_kernel");
+    if (!by_last_cta) {
         // counts -> offsets by the device-wide scan, then the cursors start at the offsets
         const int parts = (tiles + tg::kScanTile - 1) / tg::kScanTile;
         tg::scan_kernel<<<parts, tg::kScanThreads, 0, stream>>>(tile_cursor, (uint32_t*)offsets, tiles, parts,
@@ -620,23 +625,24 @@ int emit_keys(const float* vertices, const int32_t* indices, int T, int W, int H
     const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
     tg::emit_keys_kernel<false><<<(T + tg::kEmitThreads - 1) / tg::kEmitThreads, tg::kEmitThreads, 0, stream>>>(
         (const float4*)vertices, indices, T, W, H, tw, th, tiles_x, tiles_y, tri_offsets, keys, ids, capacity, hist,
-        nullptr);
+        nullptr, nullptr);
     TG_LAUNCH_CHECK("emit_keys_kernel");
     return TG_OK;
 }
 
 // Entries written straight into their tile's segment of `entries` (capacity slots), unsorted within it.
+// `tri_offsets` and `scan_scratch` as preprocess_scan left them (CTA-local offsets, CTA totals).
 int emit_entries(const float* vertices, const int32_t* indices, int T, int W, int H, int tw, int th,
-                 const uint32_t* tri_offsets, uint32_t* tile_cursor, uint64_t* entries, uint32_t capacity,
-                 cudaStream_t stream) {
+                 const uint32_t* tri_offsets, const void* scan_scratch, uint32_t* tile_cursor, uint64_t* entries,
+                 uint32_t capacity, cudaStream_t stream) {
     if (int s = check_dims_internal(T, W, H, tw, th)) return s;
     if (T == 0 || capacity == 0) return TG_OK;
-    TG_REQUIRE(vertices && indices && tri_offsets && tile_cursor && entries, "null pointer");
+    TG_REQUIRE(vertices && indices && tri_offsets && scan_scratch && tile_cursor && entries, "null pointer");
     const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
     const tg::HistArgs none = {nullptr, nullptr, 0, 0, 0};
     tg::emit_keys_kernel<true><<<(T + tg::kEmitThreads - 1) / tg::kEmitThreads, tg::kEmitThreads, 0, stream>>>(
         (const float4*)vertices, indices, T, W, H, tw, th, tiles_x, tiles_y, tri_offsets, entries, nullptr, capacity, none,
-        tile_cursor);
+        tile_cursor, (const uint32_t*)scan_scratch + 2);
     TG_LAUNCH_CHECK("emit_entries_kernel");
     return TG_OK;
 }
