@@ -288,3 +288,26 @@ def test_world_space_view_step_matches_autograd():
     assert abs(float(loss) - float(l)) <= 1e-5 * float(l)
     for a, b in zip((gP, gC, gO), (gp, gc, go)):
         assert Hh.rel_l2(a.cpu().numpy(), b.cpu().numpy()) <= 1e-5
+
+
+@pytest.mark.parametrize("one_kernel", [False, True])
+def test_triangles_without_any_tile_entry(one_kernel):
+    """T > 0 but K = 0 (all triangles degenerate): background image, zero gradients, through both step paths."""
+    from trigrad_b200 import views
+    v = np.array([[0.1, 0.1, 1.0, 1.0]] * 3 + [[-0.5, -0.5, 2.0, 0.5], [0.0, 0.0, 2.0, 0.5], [0.5, 0.5, 2.0, 0.5]], np.float32)
+    idx = np.array([[0, 1, 2], [3, 4, 5]], np.int32)
+    c = np.full((6, 3), 0.5, np.float32)
+    o = np.full((6,), 0.5, np.float32)
+    W, H = 37, 21
+    image, depth = trigrad_b200.render(Hh.cuda(v), Hh.cuda(idx), Hh.cuda(c), Hh.cuda(o), W, H)
+    assert torch.equal(image[..., :3], torch.zeros_like(image[..., :3])) and torch.all(image[..., 3] == 1)
+    assert torch.all(torch.isinf(depth))
+    gV, gC, gO = torch.zeros((6, 4), device="cuda"), torch.zeros((6, 3), device="cuda"), torch.zeros((6,), device="cuda")
+    loss = torch.zeros((), device="cuda")
+    target = torch.rand((H, W, 4), device="cuda")
+    img = views.l2_view_step(Hh.cuda(v), Hh.cuda(idx), Hh.cuda(c), Hh.cuda(o), target, W, H, gV, gC, gO, loss,
+                             one_kernel=one_kernel)
+    torch.cuda.synchronize()
+    assert torch.equal(img, image)
+    assert abs(float(loss) - float(torch.mean((image - target) ** 2))) <= 1e-6
+    assert float(gV.abs().max()) == 0 and float(gC.abs().max()) == 0 and float(gO.abs().max()) == 0
