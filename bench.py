@@ -497,11 +497,11 @@ def measure_stages(torch, St, scene, verts_np, flush, reps: int) -> dict:
     fwd = (image, depth, fw, ends, sel)
     res = {}
     res["init"] = {"kernel": "memset", "ms": med["init"], "bytes": 4 * tiles + 8 * ((T + 255) // 256)}
-    res["binning"] = {"kernel": "preprocess_scan_kernel", "ms": med["bary_transforms"],
+    res["binning"] = {"kernel": "preprocess_count_kernel", "ms": med["bary_transforms"],
                       "bytes": 12 * T + 32 * V + 164 * T + 8 * tiles}
     res["emit_entries"] = {"kernel": "emit_keys_kernel<direct> (with the read-back of K)", "ms": med["per_tile_lists"],
                            "bytes": 16 * T + 16 * V + 8 * K + 8 * tiles}
-    res["tile_sort"] = {"kernel": "tile_sort_kernel + tile_sort_long_kernel", "ms": med["sorting"],
+    res["tile_sort"] = {"kernel": "tile_sort_kernel (+ tile_sort_mid_kernel, tile_sort_long_kernel when needed)", "ms": med["sorting"],
                         "bytes": 12 * K + 8 * tiles}
     res["blend_forward"] = {"kernel": "blend_forward_kernel", "ms": med["rasterization"], "bytes": 100 * K + 28 * W * H}
     gi = torch.randn((H, W, 4), device="cuda")

@@ -40,7 +40,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
     objdir = os.path.join(HERE, "build")
     os.makedirs(objdir, exist_ok=True)
     flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if ptxas_info else [])
-    flags += os.environ.get("TG_EXTRA_NVCC_FLAGS", "").split()   # experiments only, e.g. -DTG_NO_RED
+    flags += os.environ.get("TG_EXTRA_NVCC_FLAGS", "").split()   # extra compiler flags for experiments
 
     def one(src: str) -> str:
         obj = os.path.join(objdir, src + ".o")

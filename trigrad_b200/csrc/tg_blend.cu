@@ -352,10 +352,6 @@ struct Contrib {
 
 // Packed per-vertex gradient accumulator: slot 0 = (d/dx, d/dy, d/dw, d/dopacity), slot 1 = (d/dr, d/dg, d/db, 0).
 __device__ __forceinline__ void red_add_v4(float4* addr, float a, float b, float c, float d) {
-#ifdef TG_NO_RED   // timing experiment only: results are wrong without the reductions
-    if (a == 123456.f && b == c) *reinterpret_cast<volatile float*>(addr) = d;
-    return;
-#endif
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d));
 }
 

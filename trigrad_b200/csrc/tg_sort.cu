@@ -70,14 +70,6 @@ constexpr int kSmallItems = 16;
 constexpr int kSmallTile = kSmallThreads * kSmallItems;
 using SortSmemSmall = SortSmemT<kSmallThreads, kSmallItems>;
 
-#ifdef TG_SORT_TRACE
-__device__ unsigned long long g_trace[64 * 16];
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define TRACE(slot) do { if (threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) g_trace[((blockIdx.x ? 1 : 0) * 8 + g_pass) * 16 + (slot)] = gtime(); } while (0)
-__device__ int g_pass_dummy;
-#else
-#define TRACE(slot)
-#endif
 
 // One tile of one pass.  `p` is the tile's position in the order in which tiles resolve their prefixes.
 // PIPE marks the single-launch (all passes) variant.
@@ -87,8 +79,7 @@ __device__ __forceinline__ void onesweep_tile(SortSmemT<THREADS, ITEMS>& sm, uin
                                               uint32_t* __restrict__ vals_out, uint32_t n, int shift, int bits,
                                               const uint32_t* __restrict__ digit_offsets,
                                               uint64_t* __restrict__ lookback /*[parts][256]*/,
-                                              uint32_t* __restrict__ status, int g_pass = 0) {
-    TRACE(0);
+                                              uint32_t* __restrict__ status) {
     const int tid = threadIdx.x, warp = tid >> 5;
     const unsigned lane = lane_id();
     const uint32_t digit_mask = (1u << bits) - 1u;
@@ -118,7 +109,6 @@ __device__ __forceinline__ void onesweep_tile(SortSmemT<THREADS, ITEMS>& sm, uin
             val[i] = 0;
         }
     }
-    TRACE(1);
     // Stable ranking inside the warp.  The lanes holding the same digit are found with one ballot per
     // digit bit (match.any costs several times more on this part when the digits of a warp are mostly
     // distinct).  Slots past the end of the input take the largest digit: they sit at the end of the last
@@ -146,7 +136,6 @@ __device__ __forceinline__ void onesweep_tile(SortSmemT<THREADS, ITEMS>& sm, uin
         __syncwarp();
     }
     __syncthreads();
-    TRACE(2);
 
     // per digit (thread d < 256): offsets of each warp inside the digit, CTA count, CTA start, look-back
     uint32_t cta_count = 0;
@@ -189,7 +178,6 @@ __device__ __forceinline__ void onesweep_tile(SortSmemT<THREADS, ITEMS>& sm, uin
         sm.bin_offset[tid] = digit_offsets[tid] + excl - dstart;   // modulo 2^32 on purpose
     }
     __syncthreads();
-    TRACE(3);
     if (sm.fail) return;   // uniform: nothing is written by this tile
 
     // scatter into CTA-sorted order in shared memory
@@ -204,7 +192,6 @@ __device__ __forceinline__ void onesweep_tile(SortSmemT<THREADS, ITEMS>& sm, uin
         }
     }
     __syncthreads();
-    TRACE(4);
     // coalesced runs out to global memory
     for (uint32_t k = tid; k < valid; k += THREADS) {
         const uint64_t kk = sm.keys[k];
@@ -213,7 +200,6 @@ __device__ __forceinline__ void onesweep_tile(SortSmemT<THREADS, ITEMS>& sm, uin
         keys_out[dst] = kk;
         vals_out[dst] = sm.vals[k];
     }
-    TRACE(5);
 }
 
 // One pass, tiles taken in ticket order: a tile only ever waits for tiles that already run.
@@ -271,11 +257,8 @@ __global__ void __launch_bounds__(kSmallThreads, 1) onesweep_all_passes_kernel(
         const bool odd = pass & 1;
         onesweep_tile<kSmallThreads, kSmallItems, true>(sm, blockIdx.x, odd ? keys_b : keys_a, odd ? vals_b : vals_a, odd ? keys_a : keys_b,
                       odd ? vals_a : vals_b, n, shift, bits, digit_offsets + pass * kRadix,
-                      lookback + (size_t)pass * parts * kRadix, status, pass);
+                      lookback + (size_t)pass * parts * kRadix, status);
         if (pass + 1 < passes && !grid_barrier(barrier_counter, (uint32_t)(pass + 1) * parts, status)) return;
-#ifdef TG_SORT_TRACE
-        { const int g_pass = pass; TRACE(6); }
-#endif
     }
 }
 
@@ -372,11 +355,6 @@ int sort_pairs(uint64_t* keys_a, uint64_t* keys_b, uint32_t* vals_a, uint32_t* v
 
 extern "C" {
 
-#ifdef TG_SORT_TRACE
-int tg_sort_trace(unsigned long long* out_host) {
-    return (int)cudaMemcpyFromSymbol(out_host, tg::g_trace, sizeof(unsigned long long) * 64 * 16);
-}
-#endif
 
 size_t tg_sort_scratch_bytes(uint32_t n) { return tg_host::sort_scratch_clear_bytes(n, tg::kMaxPasses); }
 
