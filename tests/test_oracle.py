@@ -333,3 +333,28 @@ def test_primitive_vjps_match_reference_host_functions():
         rv = ref.interpolate3_vector_backward_torch(torch.from_numpy(g3), torch.from_numpy(bary), torch.from_numpy(A3),
                                                     torch.from_numpy(B3), torch.from_numpy(C3), torch.from_numpy(w))
         assert np.allclose(o15, np.concatenate([t.numpy() for t in rv]), rtol=2e-5, atol=1e-5)
+
+
+def test_projection_restatement_and_its_vjp():
+    """oracle.project restates the viewer's tensor operations (viewer.py:271-278); its VJP is checked against
+    torch autograd on the same operations (CPU, float64) and against central differences."""
+    import torch
+    rng = np.random.default_rng(9)
+    pts = rng.normal(size=(50, 3))
+    pv = rng.normal(size=(4, 4))
+    pv[3] = [0.1, -0.2, 0.3, 4.0]                     # keeps clip.w away from zero
+    g = rng.normal(size=(50, 4))
+    out = O.project(pts, pv)
+    p = torch.tensor(pts, requires_grad=True)
+    h = torch.cat([p, torch.ones((50, 1), dtype=torch.float64)], dim=1)
+    cam = (torch.tensor(pv) @ h.T).T
+    ndc = torch.cat([cam[:, :3] / cam[:, 3:4], 1 / cam[:, 3:4]], dim=1)
+    assert np.allclose(out, ndc.detach().numpy(), rtol=1e-12, atol=1e-12)
+    (gp,) = torch.autograd.grad(ndc, p, grad_outputs=torch.tensor(g))
+    assert np.allclose(O.project_vjp(pts, pv, g), gp.numpy(), rtol=1e-10, atol=1e-12)
+    eps = 1e-6
+    k = (7, 1)
+    d = np.zeros_like(pts)
+    d[k] = eps
+    fd = np.sum((O.project(pts + d, pv) - O.project(pts - d, pv)) * g) / (2 * eps)
+    assert abs(fd - O.project_vjp(pts, pv, g)[k]) <= 1e-6 * max(1.0, abs(fd))
