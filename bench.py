@@ -260,7 +260,11 @@ def main() -> None:
     grads = Vw.GradBuffer.allocate(V, dev, position_components=pos_comp)
     n_streams = max(1, min(args.streams, B))
     side_streams = [torch.cuda.Stream(device=dev) for _ in range(n_streams - 1)]
-    side_grads = [Vw.GradBuffer.allocate(V, dev, position_components=pos_comp) for _ in side_streams]
+    # Random-triangle scenes: all views of a step, on all streams, add into ONE packed accumulator (atomic vector
+    # reductions), cleared and unpacked once per step.  Camera ring: every view needs its own render-space vertex
+    # gradient for the projection VJP, so each stream sums world-space gradients into a buffer of its own.
+    packed = None if camera_ring else Vw.PackedGradients(V, dev)
+    side_grads = [Vw.GradBuffer.allocate(V, dev, position_components=pos_comp) for _ in side_streams] if camera_ring else []
 
     lib = N.lib()
     inv_n = 1.0 / float(W * H * 4)
@@ -276,8 +280,8 @@ def main() -> None:
             Vw.l2_world_view_step(points, v, i, c, o, target, W, H, grads.points, grads.colors, grads.opacities,
                                   grads.loss, scene.tile_width, scene.tile_height, one_kernel=args.one_kernel)
         else:
-            Vw.l2_view_step(v, i, c, o, target, W, H, grads.points, grads.colors, grads.opacities, grads.loss,
-                            scene.tile_width, scene.tile_height, one_kernel=args.one_kernel)
+            Vw.l2_view_step(v, i, c, o, target, W, H, None, None, None, None, scene.tile_width, scene.tile_height,
+                            one_kernel=args.one_kernel, packed=packed)
         return None
 
     def run_views(items):
@@ -285,16 +289,20 @@ def main() -> None:
         (a view into the gradient buffer).
 
         Views are independent, so view b+1's binning and sorting (small, latency-bound kernels) overlap with
-        view b's compositing on another stream.  Each stream sums into its own gradient buffer.
+        view b's compositing on another stream.
         """
         main = torch.cuda.current_stream(dev)
-        grads.zero_()
+        if packed is not None:
+            packed.zero_()
+        else:
+            grads.zero_()
         start = torch.cuda.Event()
         start.record(main)
-        for si, (st, gb) in enumerate(zip(side_streams, side_grads)):
+        for si, st in enumerate(side_streams):
             st.wait_event(start)
-            with torch.cuda.stream(st):
-                gb.zero_()
+            if packed is None:
+                with torch.cuda.stream(st):
+                    side_grads[si].zero_()
         for b, (v, t, ready) in enumerate(items):
             si = b % n_streams
             stream = main if si == 0 else side_streams[si - 1]
@@ -304,12 +312,15 @@ def main() -> None:
                     if isinstance(v, torch.Tensor):
                         v.record_stream(stream)
                     t.record_stream(stream)
-                render_view(v, t, grads if si == 0 else side_grads[si - 1])
-        for st, gb in zip(side_streams, side_grads):
+                render_view(v, t, grads if (si == 0 or packed is not None) else side_grads[si - 1])
+        for si, st in enumerate(side_streams):
             done = torch.cuda.Event()
             done.record(st)
             main.wait_event(done)
-            grads.flat.add_(gb.flat)
+            if packed is None:
+                grads.flat.add_(side_grads[si].flat)
+        if packed is not None:
+            packed.unpack(W, H, grads.points, grads.colors, grads.opacities, grads.loss, accumulate=False)
         return grads.loss
 
     def step(vs, ts):

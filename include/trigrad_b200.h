@@ -168,6 +168,21 @@ int tg_blend_backward_l2(const float* tri_geo, const float* tri_attr, const int3
                          float* grad_vertices, float* grad_colors, float* grad_opacities, int accumulate, void* scratch,
                          size_t scratch_bytes, tg_stream_t stream);
 
+/* ---- gradients of several views in one packed accumulator ------------------------------------------
+ * With accumulate = TG_ACCUMULATE_PACKED the backward entry points (tg_blend_backward, tg_blend_backward_l2,
+ * tg_blend_step_l2, tg_render_step_l2) neither clear `scratch` nor write the three gradient tensors
+ * (which may then be NULL, like loss_out): the packed per-vertex sums and the loss partials stay in
+ * `scratch` and keep growing call after call - also from calls on several streams, the additions are
+ * atomic.  The caller clears the tg_backward_scratch_bytes(V) bytes once (cudaMemsetAsync), runs the
+ * views, orders the streams, and calls tg_unpack_gradients once: grad_* = (accumulate ? grad_* : 0) +
+ * sums, loss_out likewise with loss_scale (loss_out may be NULL).  No counterpart in the reference, which
+ * writes three gradient tensors per call (src/trigrad/render.cu:789-791).
+ */
+#define TG_ACCUMULATE_PACKED 2
+int tg_unpack_gradients(const void* scratch, size_t scratch_bytes, int V, float loss_scale, float* loss_out,
+                        float* grad_vertices, float* grad_colors, float* grad_opacities, int accumulate,
+                        tg_stream_t stream);
+
 /* ---- forward + backward of mean((image - target)^2) in one kernel --------------------------------
  * No counterpart in the reference: tg_blend_forward followed by tg_blend_backward_l2 for the default
  * mode (per-pixel sort, 1 <= max_layers <= 32, tiles of at most 256 pixels), fused so that the values

@@ -311,3 +311,45 @@ def test_triangles_without_any_tile_entry(one_kernel):
     assert torch.equal(img, image)
     assert abs(float(loss) - float(torch.mean((image - target) ** 2))) <= 1e-6
     assert float(gV.abs().max()) == 0 and float(gC.abs().max()) == 0 and float(gO.abs().max()) == 0
+
+
+def test_packed_accumulator_over_views_and_streams():
+    """views.PackedGradients: three views on two streams add into one accumulator that is unpacked once;
+    equal to the per-view accumulation of l2_view_step."""
+    from trigrad_b200 import views
+    sc = S.config2_random10k()
+    V = sc.num_vertices
+    i, c, o = Hh.cuda(sc.indices), Hh.cuda(sc.colors), Hh.cuda(sc.opacities)
+    rng = np.random.default_rng(23)
+    vs, ts = [], []
+    for k in range(3):
+        verts = sc.vertices.copy()
+        verts[:, 1] += 0.02 * k
+        vs.append(Hh.cuda(verts))
+        ts.append(Hh.cuda(rng.random((sc.height, sc.width, 4), dtype=np.float32)))
+    ref = [torch.zeros((V, 4), device="cuda"), torch.zeros((V, 3), device="cuda"), torch.zeros((V,), device="cuda")]
+    ref_loss = torch.zeros((), device="cuda")
+    for v, t in zip(vs, ts):
+        views.l2_view_step(v, i, c, o, t, sc.width, sc.height, ref[0], ref[1], ref[2], ref_loss)
+    torch.cuda.synchronize()
+    packed = views.PackedGradients(V, "cuda")
+    side = torch.cuda.Stream()
+    for one_kernel in (False, True):
+        packed.zero_()
+        start = torch.cuda.Event()
+        start.record()
+        side.wait_event(start)
+        for k, (v, t) in enumerate(zip(vs, ts)):
+            with torch.cuda.stream(side if k == 1 else torch.cuda.current_stream()):
+                views.l2_view_step(v, i, c, o, t, sc.width, sc.height, None, None, None, None, one_kernel=one_kernel,
+                                   packed=packed)
+        done = torch.cuda.Event()
+        done.record(side)
+        torch.cuda.current_stream().wait_event(done)
+        got = [torch.full((V, 4), 7.0, device="cuda"), torch.full((V, 3), 7.0, device="cuda"), torch.full((V,), 7.0, device="cuda")]
+        loss = torch.full((), 7.0, device="cuda")
+        packed.unpack(sc.width, sc.height, got[0], got[1], got[2], loss, accumulate=False)     # overwrites
+        torch.cuda.synchronize()
+        assert abs(float(loss) - float(ref_loss)) <= 1e-5 * float(ref_loss)
+        for a, b in zip(got, ref):
+            assert Hh.rel_l2(a.cpu().numpy(), b.cpu().numpy()) <= 1e-5

@@ -11,6 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libtrigrad_b200.so")
 
 TG_OK, TG_ERR_BAD_ARG, TG_ERR_WORKSPACE, TG_ERR_CAPACITY, TG_ERR_DEVICE_FLAG, TG_ERR_CUDA = range(6)
+TG_ACCUMULATE_PACKED = 2   # accumulate mode of the backward entry points: the sums stay in the scratch
 GEO_WORDS = 16
 ATTR_WORDS = 24
 
@@ -44,6 +45,7 @@ SIGNATURES = {
     "tg_forward_workspace_bytes": (_sz, [_i, _i, _u32]),
     "tg_render_forward": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                _u32, _vp, _vp, _sz, _vp, _vp, _vp]),
+    "tg_unpack_gradients": (_i, [_vp, _sz, _i, _f, _vp, _vp, _vp, _vp, _i, _vp]),
     "tg_project": (_i, [_vp, _i, _vp, _vp, _vp]),
     "tg_project_backward": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp]),
     "tg_render_step_l2": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _f, _f, _vp, _vp, _vp, _vp, _vp, _vp,

@@ -179,7 +179,7 @@ int tg_render_step_l2(const float* vertices, const int32_t* indices, const float
                       uint32_t list_capacity, int32_t* offsets, float* grad_vertices, float* grad_colors,
                       float* grad_opacities, int accumulate, void* workspace, size_t workspace_bytes, void* scratch,
                       size_t scratch_bytes, uint32_t* info_host, float* stage_ms_host, tg_stream_t stream) {
-    TG_REQUIRE(image && depthmap && final_weights && ends && target && loss_out, "null pointer");
+    TG_REQUIRE(image && depthmap && final_weights && ends && target, "null pointer");
     TG_REQUIRE(tw * th <= 256 && max_layers <= 32, "the one-kernel step needs tiles of at most 256 pixels and max_layers <= 32");
     cudaStream_t s = (cudaStream_t)stream;
     StageTimer timer(stage_ms_host != nullptr, s);

@@ -1087,7 +1087,8 @@ static int backward_impl(const float* tri_geo, const float* tri_attr, const int3
     TG_REQUIRE(offsets && image && depthmap && final_weights && ends, "null pointer");
     TG_REQUIRE(l2_target || (grad_image && grad_depthmap), "null upstream gradient");
     if (V == 0) return TG_OK;
-    TG_REQUIRE(grad_vertices && grad_colors && grad_opacities && scratch, "null gradient / scratch pointer");
+    const bool packed = accumulate == TG_ACCUMULATE_PACKED;   // gradients stay in the scratch, which keeps accumulating
+    TG_REQUIRE(scratch && (packed || (grad_vertices && grad_colors && grad_opacities)), "null gradient / scratch pointer");
     TG_REQUIRE(((uintptr_t)image & 15) == 0 && ((uintptr_t)grad_image & 15) == 0 && ((uintptr_t)l2_target & 15) == 0 &&
                    ((uintptr_t)tri_geo & 15) == 0 && ((uintptr_t)tri_attr & 15) == 0 &&
                    ((uintptr_t)grad_vertices & 15) == 0 && ((uintptr_t)scratch & 15) == 0,
@@ -1101,7 +1102,7 @@ static int backward_impl(const float* tri_geo, const float* tri_attr, const int3
     cudaStream_t s = (cudaStream_t)stream;
     float4* gpack = (float4*)scratch;
     float* partials = (float*)((char*)scratch + (size_t)V * 32);
-    TG_CUDA(cudaMemsetAsync(gpack, 0, (size_t)V * 32 + sizeof(float) * tg::kLossPartials, s));
+    if (!packed) TG_CUDA(cudaMemsetAsync(gpack, 0, (size_t)V * 32 + sizeof(float) * tg::kLossPartials, s));
     const tg::BlendParams P = make_params(tri_geo, tri_attr, sorted_ids, offsets, W, H, tw, th, 0.f, max_layers);
     const int tiles = P.tiles_x * ((H + th - 1) / th);
     const int threads = ((tw * th + 31) / 32) * 32;
@@ -1117,6 +1118,7 @@ static int backward_impl(const float* tri_geo, const float* tri_attr, const int3
         else tg::blend_backward_kernel<false, 1024><<<tiles, threads, 0, s>>>(P, in, gpack);
     }
     TG_LAUNCH_CHECK("blend_backward_kernel");
+    if (packed) return TG_OK;
     tg::unpack_gradients_kernel<<<(V + 255) / 256, 256, 0, s>>>(gpack, V, (float4*)grad_vertices, grad_colors,
                                                               grad_opacities, accumulate, partials, l2_loss_scale,
                                                               l2_target ? l2_loss_out : nullptr);
@@ -1134,8 +1136,9 @@ int tg_blend_step_l2(const float* tri_geo, const float* tri_attr, const int32_t*
                "the one-kernel step needs tiles of at most 256 pixels and max_layers <= 32 "
                "(otherwise: tg_blend_forward + tg_blend_backward_l2)");
     TG_REQUIRE(V > 0, "V must be positive");
-    TG_REQUIRE(offsets && image && depthmap && final_weights && ends && target && loss_out, "null pointer");
-    TG_REQUIRE(grad_vertices && grad_colors && grad_opacities && scratch, "null gradient / scratch pointer");
+    const bool packed = accumulate == TG_ACCUMULATE_PACKED;
+    TG_REQUIRE(offsets && image && depthmap && final_weights && ends && target && (packed || loss_out), "null pointer");
+    TG_REQUIRE(scratch && (packed || (grad_vertices && grad_colors && grad_opacities)), "null gradient / scratch pointer");
     TG_REQUIRE(((uintptr_t)image & 15) == 0 && ((uintptr_t)target & 15) == 0 && ((uintptr_t)tri_geo & 15) == 0 &&
                    ((uintptr_t)tri_attr & 15) == 0 && ((uintptr_t)grad_vertices & 15) == 0 && ((uintptr_t)scratch & 15) == 0,
                "image / target / tri_geo / tri_attr / grad_vertices / scratch must be 16-byte aligned");
@@ -1146,15 +1149,36 @@ int tg_blend_step_l2(const float* tri_geo, const float* tri_attr, const int32_t*
     cudaStream_t s = (cudaStream_t)stream;
     float4* gpack = (float4*)scratch;
     float* partials = (float*)((char*)scratch + (size_t)V * 32);
-    TG_CUDA(cudaMemsetAsync(gpack, 0, (size_t)V * 32 + sizeof(float) * tg::kLossPartials, s));
+    if (!packed) TG_CUDA(cudaMemsetAsync(gpack, 0, (size_t)V * 32 + sizeof(float) * tg::kLossPartials, s));
     const tg::BlendParams P = make_params(tri_geo, tri_attr, sorted_ids, offsets, W, H, tw, th, thr, max_layers);
     const int tiles = P.tiles_x * ((H + th - 1) / th);
     const int threads = ((tw * th + 31) / 32) * 32;
     tg::blend_step_l2_kernel<256><<<tiles, threads, 0, s>>>(P, (float4*)image, depthmap, final_weights, ends,
                                                             (const float4*)target, grad_scale, partials, gpack);
     TG_LAUNCH_CHECK("blend_step_l2_kernel");
+    if (packed) return TG_OK;
     tg::unpack_gradients_kernel<<<(V + 255) / 256, 256, 0, s>>>(gpack, V, (float4*)grad_vertices, grad_colors,
                                                               grad_opacities, accumulate, partials, loss_scale, loss_out);
+    TG_LAUNCH_CHECK("unpack_gradients_kernel");
+    return TG_OK;
+}
+
+int tg_unpack_gradients(const void* scratch, size_t scratch_bytes, int V, float loss_scale, float* loss_out,
+                        float* grad_vertices, float* grad_colors, float* grad_opacities, int accumulate,
+                        tg_stream_t stream) {
+    TG_REQUIRE(V > 0, "V must be positive");
+    TG_REQUIRE(scratch && grad_vertices && grad_colors && grad_opacities, "null pointer");
+    TG_REQUIRE(accumulate == 0 || accumulate == 1, "accumulate must be 0 or 1");
+    TG_REQUIRE(((uintptr_t)grad_vertices & 15) == 0 && ((uintptr_t)scratch & 15) == 0,
+               "grad_vertices / scratch must be 16-byte aligned");
+    if (scratch_bytes < tg_backward_scratch_bytes(V)) {
+        tg_host::set_error("backward scratch: need %zu bytes, got %zu", tg_backward_scratch_bytes(V), scratch_bytes);
+        return TG_ERR_WORKSPACE;
+    }
+    const float* partials = (const float*)((const char*)scratch + (size_t)V * 32);
+    tg::unpack_gradients_kernel<<<(V + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+        (const float4*)scratch, V, (float4*)grad_vertices, grad_colors, grad_opacities, accumulate, partials, loss_scale,
+        loss_out);
     TG_LAUNCH_CHECK("unpack_gradients_kernel");
     return TG_OK;
 }
@@ -1176,7 +1200,7 @@ int tg_blend_backward_l2(const float* tri_geo, const float* tri_attr, const int3
                          const float* final_weights, const int32_t* ends, const int32_t* selection, float* grad_vertices,
                          float* grad_colors, float* grad_opacities, int accumulate, void* scratch, size_t scratch_bytes,
                          tg_stream_t stream) {
-    TG_REQUIRE(target && loss_out, "null target / loss pointer");
+    TG_REQUIRE(target && (loss_out || accumulate == TG_ACCUMULATE_PACKED), "null target / loss pointer");
     return backward_impl(tri_geo, tri_attr, sorted_ids, offsets, V, W, H, tw, th, per_pixel_sort, max_layers, nullptr,
                          nullptr, target, grad_scale, loss_scale, loss_out, image, depthmap, final_weights, ends, selection,
                          grad_vertices, grad_colors, grad_opacities, accumulate, scratch, scratch_bytes, stream);

@@ -58,6 +58,30 @@ class GradBuffer:
         self.flat.zero_()
 
 
+class PackedGradients:
+    """One accumulator for the gradients and the loss of all views of a step (``tg_unpack_gradients``).
+
+    The gradient kernels add into it with atomic vector reductions, from any number of streams; it is cleared once
+    per step and unpacked once per step instead of once per view.  Render-space gradients only: views that need
+    their own vertex gradient (a projection VJP per view) cannot share it for the positions.
+    """
+
+    def __init__(self, num_vertices: int, device):
+        from . import _native as N
+
+        self.num_vertices = num_vertices
+        self.scratch = torch.zeros(N.lib().tg_backward_scratch_bytes(num_vertices), dtype=torch.uint8, device=device)
+
+    def zero_(self) -> None:
+        self.scratch.zero_()
+
+    def unpack(self, width: int, height: int, grad_vertices: torch.Tensor, grad_colors: torch.Tensor,
+               grad_opacities: torch.Tensor, loss: torch.Tensor, accumulate: bool = False) -> None:
+        """Writes (or adds) the sums; ``loss`` receives the sum of the views' mean squared errors."""
+        _w.unpack_gradients_native(self.scratch, self.num_vertices, width, height,
+                                   (grad_vertices, grad_colors, grad_opacities), loss, accumulate)
+
+
 def render_views_l2(points: torch.Tensor, indices: torch.Tensor, colors: torch.Tensor, opacities: torch.Tensor,
                     pvs: torch.Tensor, targets: Sequence[torch.Tensor] | torch.Tensor, view_ids: Sequence[int],
                     width: int, height: int, grads: GradBuffer, render_fn: Callable = _render,
@@ -86,7 +110,8 @@ def render_views_l2(points: torch.Tensor, indices: torch.Tensor, colors: torch.T
 def l2_view_step(vertices: torch.Tensor, indices: torch.Tensor, colors: torch.Tensor, opacities: torch.Tensor,
                  target: torch.Tensor, width: int, height: int, grad_vertices: torch.Tensor, grad_colors: torch.Tensor,
                  grad_opacities: torch.Tensor, loss: torch.Tensor, tile_width: int = 16, tile_height: int = 16,
-                 early_stopping_threshold: float = 1 / 256, max_layers: int = 32, one_kernel: bool = False) -> torch.Tensor:
+                 early_stopping_threshold: float = 1 / 256, max_layers: int = 32, one_kernel: bool = False,
+                 packed: "PackedGradients | None" = None) -> torch.Tensor:
     """One view of a multi-view optimisation step without autograd: forward, then the backward of
     ``mean((image - target)**2)`` fused into the gradient kernel.  With ``one_kernel`` (tiles of up to 256 pixels)
     both directions run in one compositing kernel: a few percent faster for a single stream of views and on scenes
@@ -96,6 +121,9 @@ def l2_view_step(vertices: torch.Tensor, indices: torch.Tensor, colors: torch.Te
     ``grad_opacities [V]`` and its loss to the 0-d float32 tensor ``loss`` - no gradient image, no per-view
     gradient tensors, no elementwise kernels.  Default per-pixel mode only (``max_layers`` in 1..32); use
     ``render`` with autograd for anything else.  Returns the rendered image.
+
+    With ``packed`` the gradients and the loss go into that accumulator instead (the four gradient / loss arguments
+    may be None): no clearing and no unpacking per view, see ``PackedGradients``.
     """
     if not (1 <= max_layers <= 32):
         raise ValueError("l2_view_step needs 1 <= max_layers <= 32")
@@ -109,6 +137,8 @@ def l2_view_step(vertices: torch.Tensor, indices: torch.Tensor, colors: torch.Te
     if tile_width * tile_height > 1024:
         raise ValueError("tile_width * tile_height must be <= 1024")
     if m < 1:
+        if packed is not None:
+            raise ValueError("a mesh without triangles cannot use the packed accumulator")
         loss += torch.mean((torch.tensor([0.0, 0.0, 0.0, 1.0], device=target.device) - target) ** 2)
         return None
     grads = (grad_vertices, grad_colors, grad_opacities)
@@ -116,13 +146,14 @@ def l2_view_step(vertices: torch.Tensor, indices: torch.Tensor, colors: torch.Te
         # forward, loss and gradients in one native call (one compositing kernel for both directions)
         return _w.step_l2_native(vertices.contiguous(), indices.contiguous(), colors.contiguous(), opacities.contiguous(),
                                  target, width, height, tile_width, tile_height, early_stopping_threshold, max_layers,
-                                 grads, loss, accumulate=True)[0]
+                                 grads, loss, accumulate=True,
+                                 packed_scratch=None if packed is None else packed.scratch)[0]
     (image, depthmap, final_weights, sorted_ids, offsets, tri_geo, tri_attr, ends, selection, _) = _w.forward_native(
         vertices.contiguous(), indices.contiguous(), colors.contiguous(), opacities.contiguous(), width, height,
         tile_width, tile_height, early_stopping_threshold, False, True, max_layers)
     saved = (sorted_ids, offsets, tri_geo, tri_attr, image, depthmap, final_weights, ends, selection)
     _w.backward_l2_native(target, saved, n, width, height, tile_width, tile_height, True, max_layers, grads, loss,
-                          accumulate=True)
+                          accumulate=True, packed_scratch=None if packed is None else packed.scratch)
     return image
 
 

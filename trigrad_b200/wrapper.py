@@ -142,12 +142,14 @@ def backward_native(grad_image, grad_depthmap, saved, V, width, height, tile_wid
 
 
 def backward_l2_native(target, saved, V, width, height, tile_width, tile_height, per_pixel_sort, max_layers, out,
-                       loss_out, accumulate=True):
+                       loss_out, accumulate=True, packed_scratch=None):
     """Backward of ``mean((image - target)**2)`` fused into the gradient kernel (no gradient image is formed).
 
     ``saved`` is the tuple ``forward_native`` returned for backward (it must contain the selection, i.e. the
     default per-pixel mode with ``max_layers <= 32``); ``out`` = (gV [V,4], gC [V,3], gO [V]) and the 0-d float32
-    ``loss_out`` are overwritten, or added to when ``accumulate`` is true.
+    ``loss_out`` are overwritten, or added to when ``accumulate`` is true.  With ``packed_scratch`` (a zeroed uint8
+    tensor of ``tg_backward_scratch_bytes(V)`` bytes shared by the views of a step) nothing is written but that
+    accumulator; ``unpack_gradients_native`` turns it into the three tensors later.
     """
     lib = N.lib()
     sorted_ids, offsets, tri_geo, tri_attr, image, depthmap, final_weights, ends, selection = saved
@@ -158,19 +160,35 @@ def backward_l2_native(target, saved, V, width, height, tile_width, tile_height,
     with torch.cuda.device(device):
         stream = torch.cuda.current_stream(device).cuda_stream
         nscratch = lib.tg_backward_scratch_bytes(V)
-        scratch = torch.empty(nscratch, dtype=torch.uint8, device=device)
-        gV, gC, gO = out
+        if packed_scratch is not None:
+            scratch, mode, (gV, gC, gO), loss_out = packed_scratch, N.TG_ACCUMULATE_PACKED, (None, None, None), None
+        else:
+            scratch, mode, (gV, gC, gO) = torch.empty(nscratch, dtype=torch.uint8, device=device), int(bool(accumulate)), out
         status = lib.tg_blend_backward_l2(
             _ptr(tri_geo), _ptr(tri_attr), _ptr(sorted_ids), _ptr(offsets), V, width, height, tile_width, tile_height,
             int(bool(per_pixel_sort)), int(max_layers), _ptr(target.contiguous()), 2.0 / n, 1.0 / n, _ptr(loss_out),
             _ptr(image), _ptr(depthmap), _ptr(final_weights), _ptr(ends), _ptr(selection), _ptr(gV), _ptr(gC), _ptr(gO),
-            int(bool(accumulate)), _ptr(scratch), nscratch, C.c_void_p(stream))
+            mode, _ptr(scratch), nscratch, C.c_void_p(stream))
         N.check("blend_backward_l2", status)
     return gV, gC, gO
 
 
+def unpack_gradients_native(packed_scratch, V, width, height, out, loss_out, accumulate=False):
+    """Packed accumulator of a step's views -> (gV [V,4], gC [V,3], gO [V]) and the summed mean squared error."""
+    lib = N.lib()
+    gV, gC, gO = out
+    device = gV.device
+    with torch.cuda.device(device):
+        stream = torch.cuda.current_stream(device).cuda_stream
+        N.check("unpack_gradients", lib.tg_unpack_gradients(
+            _ptr(packed_scratch), packed_scratch.numel(), V, 1.0 / float(width * height * 4), _ptr(loss_out), _ptr(gV),
+            _ptr(gC), _ptr(gO), int(bool(accumulate)), C.c_void_p(stream)))
+    return out
+
+
 def step_l2_native(vertices, indices, colors, opacities, target, width, height, tile_width, tile_height,
-                   early_stopping_threshold, max_layers, out, loss_out, accumulate=True, record_timing=False):
+                   early_stopping_threshold, max_layers, out, loss_out, accumulate=True, record_timing=False,
+                   packed_scratch=None):
     """One view of an optimisation step in one native call: tile lists, forward, ``mean((image - target)**2)``
     and its gradients (forward and backward run in a single kernel).
 
@@ -195,9 +213,11 @@ def step_l2_native(vertices, indices, colors, opacities, target, width, height, 
         tri_attr = torch.empty((T, N.ATTR_WORDS), **f32)
         offsets = torch.empty(tiles + 1, dtype=torch.int32, device=device)
         nscratch = lib.tg_backward_scratch_bytes(V)
-        scratch = torch.empty(nscratch, dtype=torch.uint8, device=device)
+        if packed_scratch is not None:   # the views of a step share one accumulator, see backward_l2_native
+            scratch, mode, (gV, gC, gO), loss_out = packed_scratch, N.TG_ACCUMULATE_PACKED, (None, None, None), None
+        else:
+            scratch, mode, (gV, gC, gO) = torch.empty(nscratch, dtype=torch.uint8, device=device), int(bool(accumulate)), out
         stage_ms = (C.c_float * 5)() if record_timing else None
-        gV, gC, gO = out
         target = target.contiguous()
         cap = max(int(st.k_estimate * 1.25) + 1024, 2 * T + 1024)
         while True:
@@ -209,7 +229,7 @@ def step_l2_native(vertices, indices, colors, opacities, target, width, height, 
                 _ptr(vertices), _ptr(indices), _ptr(colors), _ptr(opacities), T, V, width, height, tile_width, tile_height,
                 float(early_stopping_threshold), int(max_layers), _ptr(target), 2.0 / npix, 1.0 / npix, _ptr(loss_out),
                 _ptr(image), _ptr(depthmap), _ptr(final_weights), _ptr(ends), _ptr(tri_geo), _ptr(tri_attr),
-                _ptr(sorted_ids), cap, _ptr(offsets), _ptr(gV), _ptr(gC), _ptr(gO), int(bool(accumulate)),
+                _ptr(sorted_ids), cap, _ptr(offsets), _ptr(gV), _ptr(gC), _ptr(gO), mode,
                 C.c_void_p(base), ws.numel() - (base - ws.data_ptr()), _ptr(scratch), nscratch,
                 C.c_void_p(info.data_ptr()), stage_ms, C.c_void_p(stream))
             K = int(info[0])
