@@ -113,7 +113,8 @@ int tg_tile_ranges(const uint64_t* sorted_keys, uint32_t n, int tiles, int32_t* 
 /* ---- stages 3-5 as the forward entry point runs them: segmented sort --------------------------------
  * entries: uint64 words (ordered depth << 32 | triangle), grouped by tile: tile t owns
  * entries[offsets[t] .. offsets[t+1]).  Every segment is sorted ascending in place and its low words
- * are written to sorted_ids at the same positions.  A triangle occurs at most once per tile, so the
+ * are written to sorted_ids at the same positions.  The words of one segment must differ from one
+ * another (short segments are sorted by counting smaller words).  A triangle occurs at most once per tile, so the
  * result equals the stable sort of (tile << 32 | depth) keys that
  * cub::DeviceSegmentedSort::StableSortPairs produces for entries emitted in triangle order
  * (src/trigrad/render.cu:272-284).  scratch: tg_tile_sort_scratch_bytes(tiles) bytes (work lists of the
