@@ -13,7 +13,7 @@ struct ForwardWorkspace {
     uint32_t* status;
     void* scan_scratch;        // binning kernel: finished-CTA counter, totals of its CTAs
     void* tile_scan_scratch;   // device-wide scan of the tile counts (only beyond kTileScanByLastCta tiles)
-    uint32_t* long_list;       // work lists of the per-tile sort; only their four head words need clearing
+    uint32_t* long_list;       // work lists of the per-tile sort; only their six head words need clearing
     uint32_t* tile_cursor;     // [tiles]
     char* clear_end;
     size_t total;
@@ -32,7 +32,7 @@ struct ForwardWorkspace {
         tile_scan_scratch = take(tiles > tg::kTileScanByLastCta ? tg_scan_scratch_bytes(tiles) : 0);
         tile_cursor = (uint32_t*)take(sizeof(uint32_t) * (size_t)tiles);
         long_list = (uint32_t*)take(tg_host::tile_sort_scratch_bytes(tiles));
-        clear_end = (char*)long_list + 4 * sizeof(uint32_t);
+        clear_end = (char*)long_list + 6 * sizeof(uint32_t);
         total = off;
     }
 };

@@ -162,11 +162,12 @@ __device__ __forceinline__ int log2_at_least(uint32_t n) {
     return b;
 }
 
-// Work lists in the sort's scratch: [0] long tiles, [1] next long item to hand out, [2] mid tiles,
-// [3] next mid item (all zero before tile_sort_kernel), then `tiles` slots of long items and `tiles`
-// slots of mid items.
-__device__ __forceinline__ uint32_t* long_items(uint32_t* lists) { return lists + 4; }
-__device__ __forceinline__ uint32_t* mid_items(uint32_t* lists, int tiles) { return lists + 4 + tiles; }
+// Work lists in the sort's scratch: [0] long tiles, [1] next long item to hand out in the first round,
+// [2] mid tiles, [3] next mid item, [4] next long item of the second round, [5] unused (all zero before
+// tile_sort_kernel), then `tiles` slots of long items and `tiles` slots of mid items.
+constexpr int kListHead = 6;
+__device__ __forceinline__ uint32_t* long_items(uint32_t* lists) { return lists + kListHead; }
+__device__ __forceinline__ uint32_t* mid_items(uint32_t* lists, int tiles) { return lists + kListHead + tiles; }
 
 // Rank sort of n <= 32 * PER words by one warp: every lane counts, for each of its PER words, the words
 // of the segment that are smaller, which is the word's final position (all words differ).
@@ -273,8 +274,11 @@ __global__ void __launch_bounds__(kTileSortLongThreads) tile_sort_long_kernel(ui
     static_assert((1 << kLogChunk) == kTileSortChunk && kTileSortLongThreads == 1024, "chunk = 1024 threads x 16 words");
     const int tid = threadIdx.x;
     const uint32_t count = lists[0];
+    // Two rounds over the list: the tiles above 8192 entries first, the shorter ones afterwards, so that
+    // the kernel does not end on a few SMs that drew a long tile late.
+    for (int round = 0; round < 2; round++)
     while (true) {
-        if (tid == 0) s_item = atomicAdd(&lists[1], 1u);
+        if (tid == 0) s_item = atomicAdd(&lists[round == 0 ? 1 : 4], 1u);
         __syncthreads();
         const uint32_t w = s_item;
         __syncthreads();
@@ -282,6 +286,7 @@ __global__ void __launch_bounds__(kTileSortLongThreads) tile_sort_long_kernel(ui
         const int tile = (int)long_items(lists)[w];
         const int beg = offsets[tile];
         const uint32_t n = (uint32_t)(offsets[tile + 1] - beg);
+        if ((n > 8192u) != (round == 0)) continue;
         uint64_t* seg = entries + beg;
         if (n <= 8192u) {            // 8 words per thread: 256, 512 or 1024 threads take part
             sort_segment_in_smem<3, kTileSortLongThreads>(s_long, seg, n, log2_at_least(n), sorted_ids + beg,
@@ -322,9 +327,9 @@ __global__ void __launch_bounds__(kTileSortLongThreads) tile_sort_long_kernel(ui
 
 namespace tg_host {
 
-size_t tile_sort_scratch_bytes(int tiles) { return sizeof(uint32_t) * (2 * (size_t)(tiles > 0 ? tiles : 0) + 4); }
+size_t tile_sort_scratch_bytes(int tiles) { return sizeof(uint32_t) * (2 * (size_t)(tiles > 0 ? tiles : 0) + tg::kListHead); }
 
-// `scratch_prepared`: the caller has zeroed the first four words of `lists`.  `longest`: an upper bound
+// `scratch_prepared`: the caller has zeroed the first six words of `lists`.  `longest`: an upper bound
 // of the longest tile list when the caller knows one (the kernels of the length classes above it are
 // not launched), UINT32_MAX otherwise.
 int sort_tile_lists(uint64_t* entries, const int32_t* offsets, int tiles, int32_t* sorted_ids, uint32_t* lists,
@@ -332,7 +337,7 @@ int sort_tile_lists(uint64_t* entries, const int32_t* offsets, int tiles, int32_
     TG_REQUIRE(tiles >= 0, "tiles < 0");
     if (tiles == 0) return TG_OK;
     TG_REQUIRE(entries && offsets && sorted_ids && lists, "null pointer");
-    if (!scratch_prepared) TG_CUDA(cudaMemsetAsync(lists, 0, 4 * sizeof(uint32_t), s));
+    if (!scratch_prepared) TG_CUDA(cudaMemsetAsync(lists, 0, tg::kListHead * sizeof(uint32_t), s));
     tg::tile_sort_kernel<<<(tiles + tg::kTileSortWarps - 1) / tg::kTileSortWarps, tg::kTileSortThreads, 0, s>>>(
         entries, offsets, tiles, sorted_ids, lists, write_back ? 1 : 0);
     TG_LAUNCH_CHECK("tile_sort_kernel");
