@@ -335,6 +335,11 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    if world > 1:
+        # the first collectives on a communicator set up channels and buffers: keep that out of the steps
+        for _ in range(5):
+            Vw.allreduce_gradients(grads)
+        barrier()
     for _ in range(max(args.warmup, 3)):
         step(dv, dt)
     barrier()
