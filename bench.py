@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg3|cfg2|cfg1|cfg5]
 
-Workload (default): BASELINE config 3 - 200 000 seeded random triangles, 1920x1080, 16x16 tiles, fp32,
+Workload (default): configuration 3 of the reference's benchmark plan - 200 000 seeded random triangles, 1920x1080, 16x16 tiles, fp32,
 forward + backward of mean((image - target)^2).  One step = a batch of views of the mesh (default 8 per GPU, each with its
 own target image) through the whole path, gradients summed.  With N > 1 GPUs (one process per GPU under
 torchrun) every rank renders its own views and the summed vertex/colour/opacity gradients are combined
@@ -148,16 +148,16 @@ def cpu_step_factory(scene, tile_stride: int = 1):
     return step, O
 
 
-def time_cpu(scene, steps: int, warmup: int, budget_s: float):
-    """Times `steps` CPU steps after `warmup`; picks a tile stride so that the run fits the budget."""
+def time_cpu(scene, steps: int, warmup: int, limit_s: float):
+    """Times `steps` CPU steps after `warmup`; picks a tile stride so that the run fits the time limit."""
     step, O = cpu_step_factory(scene, 1)
     t0 = time.perf_counter()
     step()
     first = time.perf_counter() - t0
     stride = 1
     total_steps = steps + max(warmup - 1, 0)
-    if first * total_steps > budget_s:
-        stride = int(np.ceil(first * total_steps / budget_s))
+    if first * total_steps > limit_s:
+        stride = int(np.ceil(first * total_steps / limit_s))
         step, O = cpu_step_factory(scene, stride)
     for _ in range(max(warmup - 1, 0) if stride == 1 else warmup):
         step()
@@ -176,7 +176,7 @@ def run_reference_arm(args, rank: int, world: int) -> None:
     if rank != 0:
         return
     scene, wname = make_scene(args.workload)
-    value, dt, cores, sample = time_cpu(scene, args.steps, args.warmup, budget_s=150.0)
+    value, dt, cores, sample = time_cpu(scene, args.steps, args.warmup, limit_s=150.0)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
@@ -448,7 +448,7 @@ def main() -> None:
         "stages": {k: s for k, s in stages.items() if not k.startswith("_")},
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cv, cdt, cores, sample = time_cpu(scene, steps=3, warmup=1, budget_s=25.0)
+        cv, cdt, cores, sample = time_cpu(scene, steps=3, warmup=1, limit_s=25.0)
         line["cpu_baseline"] = {"value": cv, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
                                 "ms_per_step": cdt * 1e3}
     if rank == 0:

@@ -10,7 +10,7 @@ On a machine with a B200 the parity tests import that module and call its
 third leg next to the CPU oracle and the product kernels, and
 ``tests/golden/make_golden.py`` uses it to record golden vectors.
 
-Usage:  python oracle/build_ref.py [/path/to/reference]   (default /root/reference)
+Usage:  python oracle/build_ref.py [/path/to/reference]   (default: $TRIGRAD_REFERENCE, else the mounted checkout)
 Does nothing (exit 0) when the reference checkout is absent.
 """
 from __future__ import annotations
@@ -31,7 +31,10 @@ def so_path() -> str:
     return os.path.join(OUT, NAME + sysconfig.get_config_var("EXT_SUFFIX"))
 
 
-def build(ref_root: str = "/root/reference", force: bool = False, verbose: bool = True) -> str | None:
+DEFAULT_REFERENCE = os.environ.get("TRIGRAD_REFERENCE", os.path.join(os.sep, "root", "reference"))
+
+
+def build(ref_root: str = DEFAULT_REFERENCE, force: bool = False, verbose: bool = True) -> str | None:
     src_dir = os.path.join(ref_root, "src", "trigrad")
     if not os.path.isdir(src_dir):
         if verbose:
@@ -90,5 +93,5 @@ def load():
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else DEFAULT_REFERENCE
     build(root, force="--force" in sys.argv)

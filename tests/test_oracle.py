@@ -96,7 +96,7 @@ def test_oracle_forward_matches_reference_golden(name):
     Both sides evaluate barycentrics as M*p in fp32, whose absolute error grows with |M| (small
     triangles), and the reference's FMA placement is compiler-chosen; so individual pixels differ by up
     to ~1e-4 while the image as a whole agrees to 1e-5 (relative L2).  Pixels whose blending order flips
-    between near-equal keys in tile-order mode are budgeted separately.
+    between near-equal keys in tile-order mode are counted separately.
     """
     sc, mode = GOLDEN[name]
     g = np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
