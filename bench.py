@@ -151,6 +151,11 @@ def cpu_step_factory(scene, tile_stride: int = 1):
 def time_cpu(scene, steps: int, warmup: int, limit_s: float):
     """Times `steps` CPU steps after `warmup`; picks a tile stride so that the run fits the time limit."""
     step, O = cpu_step_factory(scene, 1)
+    # all host threads, also under a launcher that sets OMP_NUM_THREADS=1 for its workers
+    try:
+        O.set_num_threads(len(os.sched_getaffinity(0)))
+    except AttributeError:
+        O.set_num_threads(os.cpu_count() or 1)
     t0 = time.perf_counter()
     step()
     first = time.perf_counter() - t0
