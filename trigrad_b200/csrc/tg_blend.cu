@@ -262,6 +262,19 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 256 ? 5 : 1) blend_forward_kerne
     __shared__ float4 s_geo[kChunk * 4];
     __shared__ int s_id[kChunk];
     __shared__ float s_coord[kMaxTileCoords];
+    if (P.offsets[blockIdx.x] == P.offsets[blockIdx.x + 1]) {
+        // a tile without entries: background, and no need for pixel-centre coordinates (any pixel order will do)
+        const int tx = blockIdx.x % P.tiles_x, ty = blockIdx.x / P.tiles_x;
+        const int ix = tx * P.tw + (int)threadIdx.x % P.tw, iy = ty * P.th + (int)threadIdx.x / P.tw;
+        if ((int)threadIdx.x < P.tw * P.th && ix < P.W && iy < P.H) {
+            const size_t index = (size_t)iy * P.W + ix;
+            depthmap[index] = INFINITY;
+            final_w[index] = 0.f;
+            ends[index] = 0;
+            image[index] = make_float4(0.f, 0.f, 0.f, 1.f);
+        }
+        return;
+    }
     const TileCtx c = tile_context(P, s_coord);
     PixelAcc acc;
 
