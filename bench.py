@@ -1,6 +1,6 @@
 """Benchmark of the differentiable-rasterisation hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg3|cfg2|cfg1|cfg5]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg3|cfg1|cfg2|cfg4|cfg5|sort]
 
 Workload (default): configuration 3 of the reference's benchmark plan - 200 000 seeded random triangles, 1920x1080, 16x16 tiles, fp32,
 forward + backward of mean((image - target)^2).  One step = a batch of views of the mesh (default 8 per GPU, each with its
@@ -8,13 +8,18 @@ own target image) through the whole path, gradients summed.  With N > 1 GPUs (on
 torchrun) every rank renders its own views and the summed vertex/colour/opacity gradients are combined
 with one NCCL all-reduce per step (weak scaling: per-GPU work is fixed).
 
-Prints ONE JSON line (rank 0).  `value` is fwd+bwd Mpix/s with inputs resident in HBM, timed with CUDA
-events per step with an L2 flush between steps; `e2e` is the same through ``trigrad_b200.render`` from
-pinned HOST buffers (inputs copied in, loss and gradients copied out, every step); `roofline` describes
-the dominant kernel; `cpu_baseline` is the CPU oracle timed on this machine's host cores.
+Prints ONE JSON line (rank 0).  `value` is fwd+bwd Mpix/s with inputs resident in HBM through
+``trigrad_b200.views.l2_view_step`` (forward, then the backward with the loss gradient formed inside the kernel), the
+views of a step spread over CUDA streams, timed with CUDA events per step with an L2 flush between steps; `e2e` is the
+same call from pinned HOST buffers (inputs copied in, loss and gradients copied out, every step); `single_view` is ONE
+view on ONE stream, both through ``trigrad_b200.render`` + torch autograd (the reference's signature) and through
+``l2_view_step``; `other_configs` gives milliseconds per view of the other configurations; `cfg4_sharded` is the
+64-camera ring split over the ranks with its all-reduce (the multi-GPU configuration); `roofline` describes the
+dominant kernel; `cpu_baseline` is the CPU oracle timed on this machine's host cores.
 
 `--impl reference` times the reference algorithm on the host cores (the reference has no CPU path and
 only exists as CUDA; the CPU restatement under ``oracle/`` stands in), with all host threads.
+`--workload sort --pairs N` times the device-wide radix sort alone and prints its algorithmic GB/s.
 """
 from __future__ import annotations
 
@@ -198,18 +203,294 @@ def run_reference_arm(args, rank: int, world: int) -> None:
 
 
 # ----------------------------------------------------------------------------------------------------
+def bind_host_to_gpu_numa_node(index: int):
+    """Run the calling thread on the CPUs of the NUMA node the GPU hangs off, so that pinned host buffers allocated
+    next land in that node's memory (first touch).  Returns the previous affinity to restore, or None when the
+    topology cannot be read.  Reads sysfs and NVML only; changes nothing on the GPU."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(index)).busId
+        bus = (bus.decode() if isinstance(bus, bytes) else bus).lower()
+        if len(bus.split(":")[0]) == 8:
+            bus = bus[4:]
+        node = int(open(f"/sys/bus/pci/devices/{bus}/numa_node").read())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        old = os.sched_getaffinity(0)
+        cpus &= old
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return old
+    except Exception:
+        return None
+
+
+class ViewBatch:
+    """A batch of views of one mesh on one GPU: the views are spread round-robin over CUDA streams (they are
+    independent, so view b+1's binning overlaps with view b's compositing) and their gradients are summed.
+
+    Random-triangle scenes (a view = the NDC vertex array rotated in the image plane): all views, on all streams,
+    add into ONE packed accumulator, cleared and unpacked once per batch.  Camera-ring scene (a view = a 4x4
+    projection*view matrix passed by value to the projection kernel): every stream has a packed accumulator of its
+    own that one kernel per view carries through the projection's VJP into the shared world-space buffer with
+    atomic additions.  Either way the summed gradients and the loss end up in ``self.grads`` (one contiguous fp32
+    buffer, the object of the all-reduce)."""
+
+    def __init__(self, torch, Vw, scene, dev, n_streams, one_kernel=False):
+        self.torch, self.Vw, self.scene, self.dev, self.one_kernel = torch, Vw, scene, dev, one_kernel
+        self.camera_ring = "mesh" in scene.meta
+        self.W, self.H = scene.width, scene.height
+        self.V = scene.num_vertices
+        self.i = torch.from_numpy(scene.indices).to(dev)
+        self.c = torch.from_numpy(scene.colors).to(dev)
+        self.o = torch.from_numpy(scene.opacities).to(dev)
+        self.points = torch.from_numpy(scene.meta["mesh"].points).to(dev) if self.camera_ring else None
+        self.pos_comp = 3 if self.camera_ring else 4
+        self.grads = Vw.GradBuffer.allocate(self.V, dev, position_components=self.pos_comp)
+        self.n_streams = max(1, n_streams)
+        self.side_streams = [torch.cuda.Stream(device=dev) for _ in range(self.n_streams - 1)]
+        n_packed = self.n_streams if self.camera_ring else 1
+        self.packed = [Vw.PackedGradients(self.V, dev) for _ in range(n_packed)]
+
+    def render_view(self, v, target, si):
+        """fwd + bwd of one view on the current stream (stream slot `si`)."""
+        sc, Vw, g = self.scene, self.Vw, self.grads
+        if self.camera_ring:
+            Vw.l2_world_view_step(self.points, v, self.i, self.c, self.o, target, self.W, self.H, g.points, g.colors,
+                                  g.opacities, g.loss, sc.tile_width, sc.tile_height, one_kernel=self.one_kernel,
+                                  packed=self.packed[si])
+        else:
+            Vw.l2_view_step(v, self.i, self.c, self.o, target, self.W, self.H, None, None, None, None, sc.tile_width,
+                            sc.tile_height, one_kernel=self.one_kernel, packed=self.packed[0])
+
+    def run(self, items):
+        """Render (vertices or matrix, target, ready_event) items; returns the summed loss (a view into ``grads``)."""
+        torch = self.torch
+        main = torch.cuda.current_stream(self.dev)
+        if self.camera_ring:
+            self.grads.zero_()          # the packed accumulators are left zero by every view
+        else:
+            self.packed[0].zero_()
+        start = torch.cuda.Event()
+        start.record(main)
+        for st in self.side_streams:
+            st.wait_event(start)
+        for b, (v, t, ready) in enumerate(items):
+            si = b % self.n_streams
+            stream = main if si == 0 else self.side_streams[si - 1]
+            with torch.cuda.stream(stream):
+                if ready is not None:
+                    stream.wait_event(ready)
+                    if isinstance(v, torch.Tensor):
+                        v.record_stream(stream)
+                    t.record_stream(stream)
+                self.render_view(v, t, si)
+        for st in self.side_streams:
+            done = torch.cuda.Event()
+            done.record(st)
+            main.wait_event(done)
+        if not self.camera_ring:
+            g = self.grads
+            self.packed[0].unpack(self.W, self.H, g.points, g.colors, g.opacities, g.loss, accumulate=False)
+        return self.grads.loss
+
+
+def median_ms(torch, fn, flush, reps: int, warmup: int = 3):
+    """Median device time of fn() over `reps` runs, L2 flushed before each, CUDA events on the current stream."""
+    for _ in range(warmup):
+        fn()
+    ms = []
+    for _ in range(reps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        ms.append(a.elapsed_time(b))
+    return statistics.median(ms)
+
+
+def single_view_times(torch, Vw, scene, verts_np, dev, flush, reps: int) -> dict:
+    """ONE view on ONE stream: (a) through ``trigrad_b200.render`` + torch autograd of mean((image - target)^2), the
+    reference's own signature and caller pattern; (b) through ``views.l2_view_step`` (loss fused into the backward)."""
+    import trigrad_b200
+
+    W, H = scene.width, scene.height
+    v = torch.from_numpy(verts_np).to(dev)
+    i = torch.from_numpy(scene.indices).to(dev)
+    c = torch.from_numpy(scene.colors).to(dev)
+    o = torch.from_numpy(scene.opacities).to(dev)
+    target = torch.from_numpy(scene.target()).to(dev)
+    V = scene.num_vertices
+
+    def autograd_step():
+        vv, cc, oo = v.detach().requires_grad_(), c.detach().requires_grad_(), o.detach().requires_grad_()
+        image, _ = trigrad_b200.render(vv, i, cc, oo, W, H, scene.tile_width, scene.tile_height)
+        torch.mean((image - target) ** 2).backward()
+
+    gV = torch.zeros((V, 4), device=dev)
+    gC = torch.zeros((V, 3), device=dev)
+    gO = torch.zeros((V,), device=dev)
+    loss = torch.zeros((), device=dev)
+
+    def fused_step():
+        Vw.l2_view_step(v, i, c, o, target, W, H, gV, gC, gO, loss, scene.tile_width, scene.tile_height)
+
+    out = {}
+    for key, fn in (("render_autograd", autograd_step), ("l2_view_step", fused_step)):
+        ms = median_ms(torch, fn, flush, reps)
+        out[key] = {"ms": ms, "mpix_s": W * H / (ms * 1e-3) / 1e6}
+    out["note"] = ("one view, one stream, median of %d, L2 flushed before each; render_autograd = trigrad_b200.render + "
+                   "torch autograd of mean((image-target)^2), gradients of vertices, colours and opacities") % reps
+    return out
+
+
+def other_config_times(torch, Vw, dev, flush, skip: str, reps: int = 5) -> dict:
+    """fwd+bwd milliseconds per view of the other benchmark configurations (one view, one stream, fused loss)."""
+    out = {}
+    for name in ("cfg1", "cfg2", "cfg4", "cfg5"):
+        if name == skip:
+            continue
+        scene, wname = make_scene(name)
+        batch = ViewBatch(torch, Vw, scene, dev, 1)
+        W, H = scene.width, scene.height
+        if batch.camera_ring:
+            view = scene.meta["pvs"][0]
+        else:
+            view = torch.from_numpy(scene.vertices).to(dev)
+        target = torch.from_numpy(scene.target()).to(dev)
+        ms = median_ms(torch, lambda: batch.run([(view, target, None)]), flush, reps, warmup=2)
+        out[name] = {"workload": wname, "triangles": scene.num_triangles, "width": W, "height": H, "ms_per_view": ms,
+                     "mpix_s": W * H / (ms * 1e-3) / 1e6}
+        del batch, scene, view, target
+        torch.cuda.empty_cache()
+    return out
+
+
+def cfg4_sharded_block(torch, dist, Vw, dev, rank: int, world: int, n_streams: int, flush, batches: int = 3) -> dict:
+    """The multi-GPU configuration: the 64 cameras of the ring split in contiguous blocks over the ranks (strong
+    scaling), world-space gradients through the projection VJP into one buffer, ONE in-place all-reduce of it."""
+    scene, wname = make_scene("cfg4")
+    pvs = scene.meta["pvs"]
+    mine = list(Vw.shard_views(len(pvs), rank, world))
+    batch = ViewBatch(torch, Vw, scene, dev, min(n_streams, max(1, len(mine))))
+    W, H = scene.width, scene.height
+    rng = np.random.default_rng(100 + rank)
+    # a handful of distinct targets reused round-robin (64 full-size fp32 targets would be 2 GB of nothing new)
+    targets = [torch.from_numpy(rng.random((H, W, 4), dtype=np.float32)).to(dev) for _ in range(min(4, len(mine)))]
+    items = [(pvs[k], targets[n % len(targets)], None) for n, k in enumerate(mine)]
+
+    def one_batch(ev=None):
+        batch.run(items)
+        if ev is not None:
+            ev[1].record()
+        if world > 1:
+            Vw.allreduce_gradients(batch.grads)
+        if ev is not None:
+            ev[2].record()
+
+    one_batch()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    tot, red = [], []
+    for _ in range(batches):
+        flush.zero_()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        if world > 1:
+            dist.barrier()
+        ev[0].record()
+        one_batch(ev)
+        ev[2].synchronize()
+        tot.append(ev[0].elapsed_time(ev[2]))
+        red.append(ev[1].elapsed_time(ev[2]))
+    t = torch.tensor([statistics.median(tot), statistics.median(red)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_batch, ms_red = float(t[0]), float(t[1])
+    V = scene.num_vertices
+    return {"workload": wname, "cameras": len(pvs), "views_per_rank": len(mine), "scaling": "strong",
+            "triangles": scene.num_triangles, "vertices": V, "streams": batch.n_streams,
+            "ms_per_batch": ms_batch, "mpix_s": W * H * len(pvs) / (ms_batch * 1e-3) / 1e6,
+            "triangles_per_s": scene.num_triangles * len(pvs) / (ms_batch * 1e-3),
+            "ms_allreduce": ms_red if world > 1 else 0.0,
+            "allreduce_share": (ms_red / ms_batch) if world > 1 else 0.0,
+            "allreduce_bytes": (7 * V + 1) * 4 if world > 1 else 0,
+            "note": "max over ranks of the median of %d batches; all-reduce timed with CUDA events around it "
+                    "(includes waiting for the slowest rank)" % batches}
+
+
+def run_sort_workload(args) -> None:
+    """``--workload sort --pairs N``: the device-wide onesweep radix sort (``tg_sort_pairs``) on N random
+    (uint64 key, uint32 value) pairs, 45 significant key bits (6 passes, as tile << 32 | depth keys of a 1080p frame).
+    Prints algorithmic GB/s = (8 + 24 * passes) * N bytes / time against the measured HBM peak."""
+    import torch
+
+    from trigrad_b200 import _native as N
+    from trigrad_b200 import stages as St
+
+    torch.cuda.set_device(0)
+    n = int(args.pairs)
+    bits = 45
+    passes = (bits + 7) // 8
+    g = torch.Generator(device="cuda").manual_seed(0)
+    keys = torch.randint(0, 1 << bits, (n,), dtype=torch.int64, device="cuda", generator=g)
+    vals = torch.arange(n, dtype=torch.int32, device="cuda")
+    buf = St.SortBuffers(n)
+    ms = []
+    launches0 = N.lib().tg_launch_count()
+    with ClockSampler(0) as clk:
+        for it in range(max(args.warmup, 3) + args.steps):
+            buf.load(keys, vals)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            sk, sv = buf.sort(0, bits)
+            b.record()
+            b.synchronize()
+            if it >= max(args.warmup, 3):
+                ms.append(a.elapsed_time(b))
+    assert int(buf.status[0]) == 0
+    check = min(n, 1 << 20)
+    assert bool((sk[1:check] >= sk[:check - 1]).all()), "not sorted"
+    t = statistics.median(ms)
+    peaks = load_peaks()
+    nbytes = (8 + 24 * passes) * n
+    gbs = nbytes / (t * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "onesweep radix sort, algorithmic GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": t, "higher_is_better": True, "dtype": "u64+u32", "data": "synthetic",
+        "config": {"workload": "sort", "pairs": n, "key_bits": bits, "passes": passes,
+                   "l2": "inputs of %d MB per buffer (larger than L2 from 2^24 pairs on)" % (12 * n >> 20)},
+        "pairs_per_s": n / (t * 1e-3),
+        "roofline": {"kernel": "sort_histogram_kernel + %d x onesweep_pass_kernel" % passes, "bound": "hbm", "achieved": gbs,
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                     "peak_source": peaks["source"], "algorithmic_bytes_per_launch": nbytes, "ms_per_launch": t},
+        "gpu_launches": int(N.lib().tg_launch_count() - launches0), "clocks": clk.summary()}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg3")
+    ap.add_argument("--workload", default="cfg3", help="cfg1..cfg5, or `sort` (radix sort alone, see --pairs)")
+    ap.add_argument("--pairs", type=float, default=float(1 << 25), help="--workload sort: number of pairs")
     ap.add_argument("--streams", type=int, default=4,
                     help="CUDA streams the views of a step are spread over (independent views overlap on the GPU)")
     ap.add_argument("--views-per-gpu", type=int, default=8,
                     help="views of the mesh rendered per GPU per step (a batch of views; gradients are summed)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the single-view, other-configuration and sharded camera-ring blocks of the line")
     ap.add_argument("--one-kernel", action="store_true",
                     help="forward and backward of a view in one compositing kernel (tg_render_step_l2)")
     args = ap.parse_args()
@@ -220,11 +501,15 @@ def main() -> None:
     if args.impl == "reference":
         run_reference_arm(args, rank, world)
         return
+    if args.workload == "sort":
+        if rank == 0:
+            run_sort_workload(args)
+        return
 
     import torch
     import torch.distributed as dist
 
-    import trigrad_b200
+    import trigrad_b200  # noqa: F401
     from trigrad_b200 import _native as N
     from trigrad_b200 import stages as St
     from trigrad_b200 import views as Vw
@@ -241,96 +526,27 @@ def main() -> None:
     T, V = scene.num_triangles, scene.num_vertices
     B = max(1, args.views_per_gpu)
     # rank r renders views [r*B, (r+1)*B) of the same mesh; every view has its own target image.
-    # Random-triangle scenes: a view is the NDC vertex array rotated in the image plane.  Camera-ring scene
-    # (cfg4): a view is a 4x4 projection*view matrix (kept on the host, passed by value to the projection
-    # kernel and to its VJP), so the gradients are world-space.
     camera_ring = "mesh" in scene.meta
     if camera_ring:
         views_np = [scene.meta["pvs"][(rank * B + b) % 64] for b in range(B)]
-        points = torch.from_numpy(scene.meta["mesh"].points).to(dev)
     else:
         views_np = [view_vertices(scene.vertices, rank * B + b) for b in range(B)]
-        points = None
     rng = np.random.default_rng(3 + rank)
     targets_np = [scene.target() if b == 0 else rng.random((H, W, 4), dtype=np.float32) for b in range(B)]
     verts_np = S_project(scene, views_np[0]) if camera_ring else views_np[0]
 
-    i = torch.from_numpy(scene.indices).to(dev)
-    c = torch.from_numpy(scene.colors).to(dev)
-    o = torch.from_numpy(scene.opacities).to(dev)
+    n_streams = max(1, min(args.streams, B))
+    batch = ViewBatch(torch, Vw, scene, dev, n_streams, one_kernel=args.one_kernel)
+    grads = batch.grads
+    pos_comp = batch.pos_comp
     dv = list(views_np) if camera_ring else [torch.from_numpy(x).to(dev) for x in views_np]
     dt = [torch.from_numpy(x).to(dev) for x in targets_np]
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)    # > L2 (126 MB)
-    pos_comp = 3 if camera_ring else 4
-    grads = Vw.GradBuffer.allocate(V, dev, position_components=pos_comp)
-    n_streams = max(1, min(args.streams, B))
-    side_streams = [torch.cuda.Stream(device=dev) for _ in range(n_streams - 1)]
-    # Random-triangle scenes: all views of a step, on all streams, add into ONE packed accumulator (atomic vector
-    # reductions), cleared and unpacked once per step.  Camera ring: every view needs its own render-space vertex
-    # gradient for the projection VJP, so each stream sums world-space gradients into a buffer of its own.
-    packed = None if camera_ring else Vw.PackedGradients(V, dev)
-    side_grads = [Vw.GradBuffer.allocate(V, dev, position_components=pos_comp) for _ in side_streams] if camera_ring else []
-
     lib = N.lib()
-    inv_n = 1.0 / float(W * H * 4)
-
-    def render_view(v, target, grads=grads):
-        """fwd + bwd of one view; gradients and loss are added into the given buffer.
-
-        Random-triangle scenes go through ``views.l2_view_step`` (forward, then the backward with the
-        mean-squared-error gradient formed inside the kernel).  The camera-ring scene adds the world -> NDC
-        projection kernel and its VJP kernel around the same calls (``views.l2_world_view_step``).
-        """
-        if camera_ring:
-            Vw.l2_world_view_step(points, v, i, c, o, target, W, H, grads.points, grads.colors, grads.opacities,
-                                  grads.loss, scene.tile_width, scene.tile_height, one_kernel=args.one_kernel)
-        else:
-            Vw.l2_view_step(v, i, c, o, target, W, H, None, None, None, None, scene.tile_width, scene.tile_height,
-                            one_kernel=args.one_kernel, packed=packed)
-        return None
-
-    def run_views(items):
-        """Render (vertices, target, ready_event) items, spread round-robin over the streams; returns the summed loss
-        (a view into the gradient buffer).
-
-        Views are independent, so view b+1's binning and sorting (small, latency-bound kernels) overlap with
-        view b's compositing on another stream.
-        """
-        main = torch.cuda.current_stream(dev)
-        if packed is not None:
-            packed.zero_()
-        else:
-            grads.zero_()
-        start = torch.cuda.Event()
-        start.record(main)
-        for si, st in enumerate(side_streams):
-            st.wait_event(start)
-            if packed is None:
-                with torch.cuda.stream(st):
-                    side_grads[si].zero_()
-        for b, (v, t, ready) in enumerate(items):
-            si = b % n_streams
-            stream = main if si == 0 else side_streams[si - 1]
-            with torch.cuda.stream(stream):
-                if ready is not None:
-                    stream.wait_event(ready)
-                    if isinstance(v, torch.Tensor):
-                        v.record_stream(stream)
-                    t.record_stream(stream)
-                render_view(v, t, grads if (si == 0 or packed is not None) else side_grads[si - 1])
-        for si, st in enumerate(side_streams):
-            done = torch.cuda.Event()
-            done.record(st)
-            main.wait_event(done)
-            if packed is None:
-                grads.flat.add_(side_grads[si].flat)
-        if packed is not None:
-            packed.unpack(W, H, grads.points, grads.colors, grads.opacities, grads.loss, accumulate=False)
-        return grads.loss
 
     def step(vs, ts):
         """One step: B views, then (N > 1) one all-reduce of the summed gradients."""
-        loss = run_views([(v, t, None) for v, t in zip(vs, ts)])
+        loss = batch.run([(v, t, None) for v, t in zip(vs, ts)])
         if world > 1:
             Vw.allreduce_gradients(grads)
         return loss
@@ -374,36 +590,40 @@ def main() -> None:
     # ---- end to end from host buffers through the public API -----------------------------------------
     # Every step copies all of its inputs from pinned host memory (shared mesh attributes once, per-view
     # vertices and target for each view) and copies the loss and the summed gradients back.  The copies of
-    # view b+1 run on a second stream while view b renders.
+    # view b+1 run on a second stream while view b renders.  Targets travel as 8-bit RGBA (what an image on
+    # the host is; the loss reads value / 255): a quarter of the bytes of a float32 target.  The pinned buffers
+    # are allocated from the NUMA node the GPU hangs off.
+    old_affinity = bind_host_to_gpu_numa_node(local_rank)
     hi, hc, ho = (torch.from_numpy(x).pin_memory() for x in (scene.indices, scene.colors, scene.opacities))
     hp = torch.from_numpy(scene.meta["mesh"].points).pin_memory() if camera_ring else None
     hv = [] if camera_ring else [torch.from_numpy(x).pin_memory() for x in views_np]   # camera matrices stay on the host
-    ht = [torch.from_numpy(x).pin_memory() for x in targets_np]
+    ht = [torch.from_numpy(np.round(x * 255).astype(np.uint8)).pin_memory() for x in targets_np]
     out_g = torch.empty_like(grads.flat, device="cpu").pin_memory()      # gradients and, last element, the loss
+    if old_affinity is not None:
+        os.sched_setaffinity(0, old_affinity)
     h2d = sum(t.numel() * t.element_size() for t in [hi, hc, ho] + hv + ht + ([hp] if camera_ring else []))
     d2h = out_g.numel() * 4
     copy_stream = torch.cuda.Stream(device=dev)
     main_stream = torch.cuda.current_stream(dev)
 
     def e2e_step():
-        nonlocal i, c, o, points
         staged = []
         with torch.cuda.stream(copy_stream):
             if camera_ring:
-                points = hp.to(dev, non_blocking=True)
-            i = hi.to(dev, non_blocking=True)
-            c = hc.to(dev, non_blocking=True)
-            o = ho.to(dev, non_blocking=True)
+                batch.points = hp.to(dev, non_blocking=True)
+            batch.i = hi.to(dev, non_blocking=True)
+            batch.c = hc.to(dev, non_blocking=True)
+            batch.o = ho.to(dev, non_blocking=True)
             for b in range(B):
                 vb = views_np[b] if camera_ring else hv[b].to(dev, non_blocking=True)
                 tb = ht[b].to(dev, non_blocking=True)
                 ev = torch.cuda.Event()
                 ev.record(copy_stream)
                 staged.append((vb, tb, ev))
-        loss = run_views(staged)        # each view waits for its own copies (queued after the shared ones)
-        for t in (i, c, o) + ((points,) if camera_ring else ()):
+        batch.run(staged)        # each view waits for its own copies (queued after the shared ones)
+        for t in (batch.i, batch.c, batch.o) + ((batch.points,) if camera_ring else ()):
             t.record_stream(main_stream)
-            for st in side_streams:
+            for st in batch.side_streams:
                 t.record_stream(st)
         if world > 1:
             Vw.allreduce_gradients(grads)
@@ -427,9 +647,11 @@ def main() -> None:
     stages = measure_stages(torch, St, scene, verts_np, flush, reps=max(5, min(20, args.steps)))
     peaks = load_peaks()
     dominant = max((s for s in stages.values() if isinstance(s, dict) and s.get("kernel")), key=lambda s: s["ms"])
+    captured = NCU_DRAM_BYTES.get((dominant["kernel"], args.workload))
     roofline = {
         "kernel": dominant["kernel"], "bound": "hbm", "achieved": dominant["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
-        "frac": dominant["gbs"] / peaks["hbm_gbs"], "traffic": NCU_DRAM_BYTES.get((dominant["kernel"], args.workload)),
+        "frac": dominant["gbs"] / peaks["hbm_gbs"], "traffic": captured[0] if captured else None,
+        "traffic_source": captured[1] if captured else None,
         "peak_source": peaks["source"],
         "algorithmic_bytes_per_launch": dominant["bytes"], "ms_per_launch": dominant["ms"],
     }
@@ -441,6 +663,7 @@ def main() -> None:
         "config": {"workload": wname, "triangles": T, "vertices": V, "width": W, "height": H,
                    "tile": [scene.tile_width, scene.tile_height], "per_pixel_sort": True, "max_layers": 32,
                    "views_per_gpu_per_step": B, "streams": n_streams, "one_kernel_step": bool(args.one_kernel), "K_pairs": stages["_K"], "l2": "256 MB buffer rewritten between timed steps",
+                   "e2e_target_dtype": "u8 rgba (value / 255)",
                    "exchange": "none" if world == 1 else f"one NCCL all_reduce of {pos_comp + 4}V fp32 gradients per step"},
         "triangles_per_s": T * B * world / (ms_per_step * 1e-3),
         "ms_per_view": ms_per_step / B,
@@ -452,6 +675,15 @@ def main() -> None:
         "roofline": roofline,
         "stages": {k: s for k, s in stages.items() if not k.startswith("_")},
     }
+    if not args.no_extras:
+        if rank == 0:
+            line["single_view"] = single_view_times(torch, Vw, scene, verts_np, dev, flush, reps=20)
+            if world == 1:
+                line["other_configs"] = other_config_times(torch, Vw, dev, flush, skip=args.workload)
+        del batch, dv, dt
+        torch.cuda.empty_cache()
+        sharded = cfg4_sharded_block(torch, dist, Vw, dev, rank, world, args.streams, flush)
+        line["cfg4_sharded"] = sharded
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cv, cdt, cores, sample = time_cpu(scene, steps=3, warmup=1, limit_s=25.0)
         line["cpu_baseline"] = {"value": cv, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
@@ -462,10 +694,13 @@ def main() -> None:
         dist.destroy_process_group()
 
 
-# DRAM bytes (read + write) of one launch from an ncu capture of the same kernel on the same workload
-# (see profiles/); None where no capture exists for the workload.
-NCU_DRAM_BYTES = {("blend_backward_queued_kernel (+ memset, unpack_gradients_kernel)", "cfg3"): 182.5e6 + 13.0e6 + 38.4e6,
-                  ("blend_forward_kernel", "cfg3"): 52.6e6 + 48.0e6}
+# DRAM bytes (read + write) of one launch of the dominant kernel from an ncu capture of the same kernel on the same
+# workload, with the summary the figure was read from; the kernels may have changed since that capture.
+NCU_DRAM_BYTES = {
+    ("blend_backward_queued_kernel (+ memset, unpack_gradients_kernel)", "cfg3"):
+        (182.5e6 + 13.0e6 + 38.4e6, "profiles/blend_kernels_cfg3.md"),
+    ("blend_forward_kernel", "cfg3"): (52.6e6 + 48.0e6, "profiles/blend_kernels_cfg3.md"),
+}
 
 
 def load_peaks() -> dict:

@@ -16,6 +16,18 @@
  *   All pointers are device pointers unless named *_host.  `stream` is a cudaStream_t.
  *   Every function returns TG_OK (0) or one of the TG_ERR_* codes; tg_last_error() gives text.
  *   The number of (triangle, tile) pairs K must stay below 2^31.
+ *
+ * Threads and state.  Every entry point may be called from any host thread (the reference runs its
+ * forward on the caller's thread and its backward on an autograd worker thread); work is ordered on
+ * the stream that is passed, the device is the one current on the calling thread.  The library keeps
+ * no state between calls that affects results.  What it caches, all of it invisible to the caller:
+ *   - per host thread: the text behind tg_last_error(); one cudaEvent_t per device (marks "K has
+ *     reached the host" inside tg_render_forward); the occupancy figures of the radix-sort kernels
+ *     for the device last used by that thread;
+ *   - per process: an atomic launch counter (tg_launch_count); per device, atomically, "the opt-in
+ *     shared-memory size of the long tile sort has been set" and the device address of the fixed
+ *     array behind tg_scan_static.  These belong to the device's primary context: a program that
+ *     resets a device (cudaDeviceReset) must not call the library on it afterwards.
  */
 #ifndef TRIGRAD_B200_H
 #define TRIGRAD_B200_H
@@ -82,6 +94,16 @@ int tg_scan(const uint32_t* in, uint32_t* out, int n, void* scratch, size_t scra
  * kernels may overlap on the GPU (different streams) race, so order them on one stream.
  */
 int tg_scan_static(const uint32_t* in, uint32_t* out, int n, uint32_t* status, tg_stream_t stream);
+
+/* Self-test of the bounded device-side waits (the look-back of tg_scan / tg_scan_static and of the sort
+ * gives up after a fixed number of polls, raises `status` and lets the host return
+ * TG_ERR_DEVICE_FLAG instead of hanging).  One warp waits, at most `spin_limit` (1..4096) polls, for a
+ * partition word that nothing ever publishes, so the wait is certain to run out: *status (device
+ * uint32) becomes 1.  scratch: 32 bytes of device memory, 8-byte aligned.  The launch always ends; no
+ * other kernel is involved.  No counterpart in the reference, whose kernels never wait on one another.
+ */
+int tg_selftest_bounded_wait(void* scratch, size_t scratch_bytes, uint32_t* status, uint32_t spin_limit,
+                             tg_stream_t stream);
 
 /* ---- stage 3: key emission --------------------------------------------------------------------
  * For triangle t and every tile (tx outer, ty inner) of its rectangle, entry e = tri_offsets[t] + n:
@@ -169,6 +191,16 @@ int tg_blend_backward_l2(const float* tri_geo, const float* tri_attr, const int3
                          float* grad_vertices, float* grad_colors, float* grad_opacities, int accumulate, void* scratch,
                          size_t scratch_bytes, tg_stream_t stream);
 
+/* The same with the target image as 8-bit RGBA [H,W,4] (4-byte aligned): target = value / 255 (correctly rounded,
+ * i.e. what `u8.float() / 255` gives in torch), a quarter of the bytes to bring to the GPU per view.
+ */
+int tg_blend_backward_l2_u8(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids, const int32_t* offsets,
+                            int V, int W, int H, int tile_w, int tile_h, int per_pixel_sort, int max_layers,
+                            const uint8_t* target_rgba8, float grad_scale, float loss_scale, float* loss_out,
+                            const float* image, const float* depthmap, const float* final_weights, const int32_t* ends,
+                            const int32_t* selection, float* grad_vertices, float* grad_colors, float* grad_opacities,
+                            int accumulate, void* scratch, size_t scratch_bytes, tg_stream_t stream);
+
 /* ---- gradients of several views in one packed accumulator ------------------------------------------
  * With accumulate = TG_ACCUMULATE_PACKED the backward entry points (tg_blend_backward, tg_blend_backward_l2,
  * tg_blend_step_l2, tg_render_step_l2) neither clear `scratch` nor write the three gradient tensors
@@ -246,6 +278,21 @@ int tg_render_step_l2(const float* vertices, const int32_t* indices, const float
 int tg_project(const float* points, int V, const float* pv_host, float* vertices, tg_stream_t stream);
 int tg_project_backward(const float* points, int V, const float* pv_host, const float* grad_vertices, float* grad_points,
                         int accumulate, tg_stream_t stream);
+
+/* One view's packed accumulator (filled by the backward entry points with TG_ACCUMULATE_PACKED) straight to
+ * world space: tg_unpack_gradients and tg_project_backward in one kernel.  The render-space vertex gradient
+ * of every vertex goes through the VJP of tg_project (same points, same pv_host) and is ADDED to
+ * grad_points [V,3]; colour and opacity gradients are ADDED to grad_colors [V,3] / grad_opacities [V]; the
+ * view's loss (sum of its partials * loss_scale) is ADDED to *loss_out (may be NULL).  All additions are
+ * atomic, so views rendered on several streams may add into the same tensors; the caller clears them once
+ * per batch.  The accumulator is zero again when the kernel ends: clear it once
+ * (tg_backward_scratch_bytes(V) bytes) before the first view and reuse it, one accumulator per stream.
+ * What a view through the reference's viewer pays in torch for this: the autograd of viewer.py:271-278 plus
+ * three gradient tensors per view.
+ */
+int tg_unpack_project_backward(void* scratch, size_t scratch_bytes, int V, const float* points, const float* pv_host,
+                               float loss_scale, float* loss_out, float* grad_points, float* grad_colors,
+                               float* grad_opacities, tg_stream_t stream);
 
 #ifdef __cplusplus
 }

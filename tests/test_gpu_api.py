@@ -203,6 +203,16 @@ def test_live_reference_leg(make, sort):
     v, i, c, o = Hh.scene_tensors(sc)
     r_img, r_depth, r_fw, r_ids, r_off, r_bary, r_ends, _ = ref.render_forward(
         v, i, c, o, sc.width, sc.height, sc.tile_width, sc.tile_height, mode["thr"], True, sort, mode["max_layers"])
+    torch.cuda.synchronize()
+    image, depth, _, _, _ = run_render(sc, mode, gi, gd)
+    # Pixels where the two builds decide differently (a pixel centre on a shared edge, two fragments a few ulp
+    # apart in depth) blend different fragments; their upstream gradient is zeroed on BOTH sides so that the
+    # gradient comparison below always runs and covers every other pixel.
+    r_image = r_img.cpu().numpy()
+    diff = np.abs(image.astype(np.float64) - r_image).max(axis=2)
+    flips = diff > 1e-3
+    gi[flips] = 0
+    gd[flips] = 0
     r_gV, r_gC, r_gO = ref.render_backward(Hh.cuda(gi), Hh.cuda(gd), v, i, c, o, r_ids, r_off, r_bary, r_img, r_depth,
                                            r_fw, r_ends, sc.width, sc.height, sc.tile_width, sc.tile_height, mode["thr"],
                                            sort, mode["max_layers"])
@@ -223,9 +233,6 @@ def test_live_reference_leg(make, sort):
         assert np.array_equal(np.sort(mine[off[t]:off[t + 1]]), np.sort(theirs[off[t]:off[t + 1]]))
     # image and gradients
     npx = sc.width * sc.height
-    r_image = r_img.cpu().numpy()
-    diff = np.abs(image.astype(np.float64) - r_image).max(axis=2)
-    flips = diff > 1e-3
     assert int(flips.sum()) <= max(4, int(5e-4 * npx))
     # Both builds evaluate barycentrics as M*(px,py,1) in fp32; that evaluation carries an absolute
     # error of about eps*(|m0|+|m1|+|m2|) per coordinate, which grows as triangles shrink, and the
@@ -233,11 +240,19 @@ def test_live_reference_leg(make, sort):
     # conditioned and the conditioning bound otherwise.
     kappa = float(np.median(np.abs(geo.cpu().numpy()[:, :9]).reshape(-1, 3, 3).sum(axis=2)))
     tol = max(1e-5, 4 * 2.0 ** -24 * kappa)
-    assert Hh.rel_l2(image[~flips], r_image[~flips]) <= tol
-    if not flips.any():
-        assert Hh.rel_l2(gV, r_gV.cpu().numpy()) <= 1e-4
-        assert Hh.rel_l2(gC, r_gC.cpu().numpy()) <= 1e-4
-        assert Hh.rel_l2(gO, r_gO.cpu().numpy()) <= 1e-4
+    img_err = Hh.rel_l2(image[~flips], r_image[~flips])
+    assert img_err <= tol
+    errs = dict(vertices=Hh.rel_l2(gV, r_gV.cpu().numpy()), colors=Hh.rel_l2(gC, r_gC.cpu().numpy()),
+                opacities=Hh.rel_l2(gO, r_gO.cpu().numpy()))
+    path = os.environ.get("TG_PARITY_REPORT")
+    if path:
+        import json
+        with open(path, "a") as f:
+            f.write(json.dumps(dict(test="live_reference", scene=sc.name, per_pixel_sort=bool(sort), pixels=npx,
+                                    flips=int(flips.sum()), kappa=kappa, image_tol=tol, image_rel_l2=img_err,
+                                    grad_rel_l2=errs)) + "\n")
+    for name, err in errs.items():
+        assert err <= 1e-4, f"grad_{name} against the reference's own build: relative L2 error {err:.3e}"
 
 
 def test_projection_kernels_vs_oracle_and_autograd():
@@ -353,3 +368,124 @@ def test_packed_accumulator_over_views_and_streams():
         assert abs(float(loss) - float(ref_loss)) <= 1e-5 * float(ref_loss)
         for a, b in zip(got, ref):
             assert Hh.rel_l2(a.cpu().numpy(), b.cpu().numpy()) <= 1e-5
+
+
+def test_bounded_wait_runs_out_and_is_reported():
+    """A device-side wait that nothing satisfies: the look-back warp polls a partition word that is never published,
+    gives up after its limit, raises the status word and returns - the launch ends, the context stays usable."""
+    import ctypes as C
+    from trigrad_b200 import _native as N
+    scratch = torch.zeros(8, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    st = N.lib().tg_selftest_bounded_wait(C.c_void_p(scratch.data_ptr()), 32, C.c_void_p(status.data_ptr()), 8,
+                                          C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert st == N.TG_OK
+    torch.cuda.synchronize()
+    assert int(status[0]) == 1                      # what TG_ERR_DEVICE_FLAG reports to the host
+    assert int(scratch[2]) == 7 and int(scratch[3]) == 2   # the warp still published its (inclusive) word
+    # the context is fine: an ordinary render right after it
+    sc = S.large_triangles(2)
+    v, i, c, o = Hh.scene_tensors(sc)
+    image, _ = trigrad_b200.render(v, i, c, o, sc.width, sc.height)
+    assert torch.isfinite(image).all()
+
+
+def test_stale_device_error_word_raises_at_the_next_render_and_in_backward():
+    """The error word of a render travels to a pinned slot asynchronously; the next render on the stream, the
+    backward of the same render and ``check_device_errors`` must raise when it is set."""
+    from trigrad_b200 import wrapper as Wr
+    sc = S.large_triangles(2)
+    v, i, c, o = Hh.scene_tensors(sc)
+    trigrad_b200.render(v, i, c, o, sc.width, sc.height)
+    torch.cuda.synchronize()
+    st = Wr._state(v.device)
+    st.info[st.last_slot, 2] = 3                    # as if a kernel of that render had raised the word
+    with pytest.raises(RuntimeError, match="device error word 3"):
+        trigrad_b200.render(v, i, c, o, sc.width, sc.height)
+    torch.cuda.synchronize()
+    st.info[st.last_slot, 2] = 5
+    with pytest.raises(RuntimeError, match="device error word 5"):
+        trigrad_b200.check_device_errors()
+    trigrad_b200.check_device_errors()              # the word was consumed
+    vv = v.clone().requires_grad_()
+    image, _ = trigrad_b200.render(vv, i, c, o, sc.width, sc.height)
+    torch.cuda.synchronize()
+    st.info[st.last_slot, 2] = 9
+    with pytest.raises(RuntimeError, match="device error word 9"):
+        image.sum().backward()
+    trigrad_b200.check_device_errors()
+
+
+def test_render_without_saved_selection_gives_the_same_gradients():
+    """Above ``SELECTION_MAX_BYTES`` the forward saves no per-pixel fragment ids and the backward searches the lists."""
+    from trigrad_b200 import wrapper as Wr
+    sc = S.config2_random10k()
+    mode = dict(thr=1 / 256, per_pixel_sort=True, max_layers=32)
+    rng = np.random.default_rng(9)
+    gi = rng.normal(size=(sc.height, sc.width, 4)).astype(np.float32)
+    gd = rng.normal(size=(sc.height, sc.width)).astype(np.float32)
+    a = run_render(sc, mode, gi, gd)
+    old = Wr.SELECTION_MAX_BYTES
+    Wr.SELECTION_MAX_BYTES = 0
+    try:
+        b = run_render(sc, mode, gi, gd)
+    finally:
+        Wr.SELECTION_MAX_BYTES = old
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+    for x, y in zip(a[2:], b[2:]):
+        assert Hh.rel_l2(x, y) <= 1e-5
+
+
+def test_uint8_target_matches_the_float_target_it_stands_for():
+    """views.l2_view_step with an 8-bit RGBA target against the same call on ``u8.float() / 255``: identical loss and
+    gradients up to the run-dependent order of the float atomics."""
+    from trigrad_b200 import views
+    sc = S.config2_random10k()
+    v, i, c, o = Hh.scene_tensors(sc)
+    V = sc.num_vertices
+    t8 = torch.from_numpy(np.random.default_rng(23).integers(0, 256, (sc.height, sc.width, 4), dtype=np.uint8)).cuda()
+    out = []
+    for target in (t8, t8.float() / 255):
+        gV, gC, gO = torch.zeros((V, 4), device="cuda"), torch.zeros((V, 3), device="cuda"), torch.zeros((V,), device="cuda")
+        loss = torch.zeros((), device="cuda")
+        views.l2_view_step(v, i, c, o, target, sc.width, sc.height, gV, gC, gO, loss)
+        out.append((float(loss), gV.cpu().numpy(), gC.cpu().numpy(), gO.cpu().numpy()))
+    assert abs(out[0][0] - out[1][0]) <= 1e-6 * out[1][0]
+    for a, b in zip(out[0][1:], out[1][1:]):
+        assert Hh.rel_l2(a, b) <= 1e-5
+    with pytest.raises(TypeError):
+        views.l2_view_step(v, i, c, o, t8.short(), sc.width, sc.height, None, None, None, torch.zeros((), device="cuda"))
+    with pytest.raises(ValueError):
+        views.l2_view_step(v, i, c, o, t8, sc.width, sc.height, None, None, None, torch.zeros((), device="cuda"), one_kernel=True)
+
+
+def test_world_space_view_step_with_packed_accumulators_on_two_streams():
+    """Two views on two streams, each with its own packed accumulator, adding atomically into one set of world-space
+    gradient tensors (``tg_unpack_project_backward``) against the same two views through the unpacked path."""
+    from trigrad_b200 import views
+    mesh = S.displaced_sphere(4)
+    pvs = S.camera_ring(8)
+    W, H = 320, 192
+    pts, i, c, o = Hh.cuda(mesh.points), Hh.cuda(mesh.indices), Hh.cuda(mesh.colors), Hh.cuda(mesh.opacities)
+    V = pts.shape[0]
+    targets = [torch.rand((H, W, 4), device="cuda") for _ in range(2)]
+    ref = views.GradBuffer.allocate(V, pts.device, 3)
+    for k in range(2):
+        views.l2_world_view_step(pts, pvs[k + 1], i, c, o, targets[k], W, H, ref.points, ref.colors, ref.opacities, ref.loss)
+    got = views.GradBuffer.allocate(V, pts.device, 3)
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream() for _ in range(2)]
+    packs = [views.PackedGradients(V, pts.device) for _ in range(2)]
+    for rounds in range(2):                                  # second round: the accumulators were left zero by the first
+        got.zero_()
+        torch.cuda.synchronize()
+        for k, st in enumerate(streams):
+            with torch.cuda.stream(st):
+                views.l2_world_view_step(pts, pvs[k + 1], i, c, o, targets[k], W, H, got.points, got.colors, got.opacities,
+                                         got.loss, packed=packs[k])
+        torch.cuda.synchronize()
+        assert abs(float(got.loss) - float(ref.loss)) <= 1e-5 * float(ref.loss)
+        for a, b in zip((got.points, got.colors, got.opacities), (ref.points, ref.colors, ref.opacities)):
+            assert Hh.rel_l2(a.cpu().numpy(), b.cpu().numpy()) <= 1e-5
+        for p in packs:
+            assert not bool(p.scratch.any())

@@ -56,6 +56,37 @@ def test_static_scan_matches_regular_scan_on_two_calls_in_a_row():
         assert int(got[-1]) == int(x.sum())
 
 
+def test_static_scan_at_its_largest_size():
+    """n = 2^24 is the one size that uses the last word of the fixed array."""
+    n = 1 << 24
+    x = torch.from_numpy(np.random.default_rng(1).integers(0, 100, n, dtype=np.int32)).cuda()
+    ref, _ = _scan_regular(x)
+    got, st = _scan_static(x)
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0
+    assert torch.equal(got, ref)
+
+
+def test_static_scan_leaves_free_device_memory_unchanged():
+    """The property in the entry point's name: with outputs allocated beforehand, a call changes neither the
+    driver's figure of free device memory nor the figures of torch's caching allocator."""
+    n = 1_000_000
+    x = torch.ones(n, dtype=torch.int32, device="cuda")
+    out = torch.empty(n + 1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    lib = N.lib()
+    N.check("scan_static", lib.tg_scan_static(_ptr(x), _ptr(out), n, _ptr(status), _stream()))   # first call: address look-up
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    reserved0, allocated0 = torch.cuda.memory_reserved(), torch.cuda.memory_allocated()
+    N.check("scan_static", lib.tg_scan_static(_ptr(x), _ptr(out), n, _ptr(status), _stream()))
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0
+    assert torch.cuda.memory_reserved() == reserved0 and torch.cuda.memory_allocated() == allocated0
+    assert int(out[-1]) == n and int(status[0]) == 0
+
+
 def test_static_scan_rejects_sizes_beyond_its_fixed_array():
     n = (1 << 24) + 1
     x = torch.zeros(n, dtype=torch.int32, device="cuda")

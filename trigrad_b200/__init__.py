@@ -1,5 +1,5 @@
 """trigrad_b200: B200-native (sm_100a) differentiable triangle rasterisation behind trigrad's ``render`` API."""
-from .wrapper import Renderer, precision, render
+from .wrapper import Renderer, check_device_errors, precision, render
 
-__all__ = ["render", "Renderer", "precision"]
+__all__ = ["render", "Renderer", "precision", "check_device_errors"]
 __version__ = "0.1.0"

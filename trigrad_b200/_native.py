@@ -27,6 +27,7 @@ SIGNATURES = {
     "tg_scan_scratch_bytes": (_sz, [_i]),
     "tg_scan": (_i, [_vp, _vp, _i, _vp, _sz, _vp, _vp]),
     "tg_scan_static": (_i, [_vp, _vp, _i, _vp, _vp]),
+    "tg_selftest_bounded_wait": (_i, [_vp, _sz, _vp, _u32, _vp]),
     "tg_emit_keys": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _u32, _vp]),
     "tg_sort_scratch_bytes": (_sz, [_u32]),
     "tg_sort_pairs": (_i, [_vp, _vp, _vp, _vp, _u32, _i, _i, _vp, _sz, _vp, C.POINTER(_i), _vp]),
@@ -40,6 +41,8 @@ SIGNATURES = {
                                _vp, _vp, _i, _vp, _sz, _vp]),
     "tg_blend_backward_l2": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _f, _f, _vp, _vp, _vp, _vp, _vp, _vp,
                                   _vp, _vp, _vp, _i, _vp, _sz, _vp]),
+    "tg_blend_backward_l2_u8": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _f, _f, _vp, _vp, _vp, _vp, _vp, _vp,
+                                     _vp, _vp, _vp, _i, _vp, _sz, _vp]),
     "tg_blend_step_l2": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp, _f, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                               _vp, _i, _vp, _sz, _vp]),
     "tg_forward_workspace_bytes": (_sz, [_i, _i, _u32]),
@@ -48,6 +51,7 @@ SIGNATURES = {
     "tg_unpack_gradients": (_i, [_vp, _sz, _i, _f, _vp, _vp, _vp, _vp, _i, _vp]),
     "tg_project": (_i, [_vp, _i, _vp, _vp, _vp]),
     "tg_project_backward": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp]),
+    "tg_unpack_project_backward": (_i, [_vp, _sz, _i, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp]),
     "tg_render_step_l2": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _f, _f, _vp, _vp, _vp, _vp, _vp, _vp,
                                _vp, _vp, _u32, _vp, _vp, _vp, _vp, _i, _vp, _sz, _vp, _sz, _vp, _vp, _vp]),
 }

@@ -96,8 +96,8 @@ __device__ __forceinline__ uint64_t ld_volatile(const uint64_t* p) { return *(co
 __device__ __forceinline__ void st_volatile(uint64_t* p, uint64_t v) { *(volatile uint64_t*)p = v; }
 
 // Wait (bounded) until the partition word has a non-zero flag.  Returns false if the wait ran out.
-__device__ __forceinline__ bool wait_flag(const uint64_t* p, uint64_t& word) {
-    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+__device__ __forceinline__ bool wait_flag(const uint64_t* p, uint64_t& word, uint32_t spin_limit) {
+    for (uint32_t it = 0; it < spin_limit; ++it) {
         word = ld_volatile(p);
         if ((word >> 32) != 0) return true;
         if (it > 64) __nanosleep(100);
@@ -108,7 +108,8 @@ __device__ __forceinline__ bool wait_flag(const uint64_t* p, uint64_t& word) {
 // Decoupled look-back, executed by ONE WARP of partition p: publishes the partition's total, sums the
 // totals of all earlier partitions (32 words per step) until one of them already carries an inclusive
 // prefix, publishes its own inclusive prefix and returns the exclusive one.
-__device__ __forceinline__ uint32_t lookback_exclusive(int p, uint32_t total, uint64_t* part_status, uint32_t* status) {
+__device__ __forceinline__ uint32_t lookback_exclusive(int p, uint32_t total, uint64_t* part_status, uint32_t* status,
+                                                       uint32_t spin_limit = kSpinLimit) {
     uint32_t excl = 0;
     if (p == 0) {
         if (lane_id() == 0) st_volatile(&part_status[0], (2ull << 32) | total);
@@ -119,7 +120,7 @@ __device__ __forceinline__ uint32_t lookback_exclusive(int p, uint32_t total, ui
     bool failed = false;
     while (true) {
         uint64_t word = 2ull << 32;   // virtual partitions before 0: inclusive prefix 0
-        if (q >= 0 && !wait_flag(&part_status[q], word)) { failed = true; word = 2ull << 32; }
+        if (q >= 0 && !wait_flag(&part_status[q], word, spin_limit)) { failed = true; word = 2ull << 32; }
         const uint32_t flag = (uint32_t)(word >> 32), val = (uint32_t)word;
         const unsigned incl_mask = __ballot_sync(0xffffffffu, flag == 2u);
         uint32_t contrib = val;
@@ -191,6 +192,15 @@ __global__ void __launch_bounds__(kScanThreads) scan_kernel(const uint32_t* __re
         if (base + i < n) out[base + i] = run;
         run += v[i];
     }
+}
+
+// Self-test of the bounded wait: ONE warp plays partition 1 of a scan whose partition 0 never publishes
+// anything (its word stays zero), with a spin limit of a few polls.  The wait runs out, the warp raises the
+// status word and returns; nothing waits for anything else, so the launch always ends.
+__global__ void __launch_bounds__(32) bounded_wait_selftest_kernel(uint64_t* part_status /*[2], zero*/, uint32_t* status,
+                                                                  uint32_t spin_limit, uint32_t* excl_out) {
+    const uint32_t excl = lookback_exclusive(1, 7u, part_status, status, spin_limit);
+    if (lane_id() == 0) *excl_out = excl;
 }
 
 // Stages 1 and 2 as the forward path runs them: the CTA that preprocesses 256 triangles scans their
@@ -776,6 +786,18 @@ int tg_scan_static(const uint32_t* in, uint32_t* out, int n, uint32_t* status, t
     tg::scan_kernel<<<parts, tg::kScanThreads, 0, s>>>(in, out, n, parts, (uint32_t*)scratch,
                                                       (uint64_t*)((char*)scratch + 256), status);
     TG_LAUNCH_CHECK("scan_kernel (static scratch)");
+    return TG_OK;
+}
+
+int tg_selftest_bounded_wait(void* scratch, size_t scratch_bytes, uint32_t* status, uint32_t spin_limit,
+                             tg_stream_t stream) {
+    TG_REQUIRE(scratch && status, "null pointer");
+    TG_REQUIRE(((uintptr_t)scratch & 7) == 0 && scratch_bytes >= 32, "scratch: 32 bytes, 8-byte aligned");
+    TG_REQUIRE(spin_limit >= 1 && spin_limit <= 4096, "spin_limit must be in 1..4096");
+    cudaStream_t s = (cudaStream_t)stream;
+    TG_CUDA(cudaMemsetAsync(scratch, 0, 32, s));
+    tg::bounded_wait_selftest_kernel<<<1, 32, 0, s>>>((uint64_t*)scratch, status, spin_limit, (uint32_t*)scratch + 6);
+    TG_LAUNCH_CHECK("bounded_wait_selftest_kernel");
     return TG_OK;
 }
 

@@ -476,6 +476,9 @@ struct BackwardIn {
     const float4* l2_target;
     float l2_grad_scale;
     float* l2_partials;
+    // the same target as 8-bit RGBA (value / 255, correctly rounded division: what `u8.float() / 255` gives);
+    // at most one of l2_target / l2_target_u8 is set
+    const uchar4* l2_target_u8;
 };
 constexpr int kLossPartials = 64;
 
@@ -487,8 +490,15 @@ __device__ __forceinline__ int load_pixel_state(const TileCtx& c, const BlendPar
     if (!c.active) return 0;
     const size_t index = (size_t)c.iy * P.W + c.ix;
     const float4 img = in.image[index];
-    if (in.l2_target) {
-        const float4 t = in.l2_target[index];
+    if (in.l2_target || in.l2_target_u8) {
+        float4 t;
+        if (in.l2_target_u8) {
+            const uchar4 u = in.l2_target_u8[index];
+            t = make_float4(__fdiv_rn((float)u.x, 255.f), __fdiv_rn((float)u.y, 255.f), __fdiv_rn((float)u.z, 255.f),
+                            __fdiv_rn((float)u.w, 255.f));
+        } else {
+            t = in.l2_target[index];
+        }
         const float dr = img.x - t.x, dg = img.y - t.y, db = img.z - t.z, da = img.w - t.w;
         pg.gr = in.l2_grad_scale * dr; pg.gg = in.l2_grad_scale * dg; pg.gb = in.l2_grad_scale * db;
         pg.ga = in.l2_grad_scale * da;
@@ -520,7 +530,7 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 256 ? 4 : 1) blend_backward_save
     const int n = load_pixel_state(c, P, in, pg, st, &sq);
     const size_t plane = (size_t)P.W * P.H, index = (size_t)c.iy * P.W + c.ix;
     const int lane = lane_id();
-    if (in.l2_target) {
+    if (in.l2_target || in.l2_target_u8) {
         // loss: warp sum, then one atomic per warp into one of 64 partial sums (spread addresses)
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, d);
@@ -786,7 +796,7 @@ __global__ void __launch_bounds__(MAXT, 4) blend_backward_queued_kernel(BlendPar
     const size_t plane = (size_t)P.W * P.H, index = (size_t)c.iy * P.W + c.ix;
     const int lane = lane_id();
     float (*q)[kQueueSlots] = s_queue[threadIdx.x >> 5];
-    if (in.l2_target) {
+    if (in.l2_target || in.l2_target_u8) {
         // loss: warp sum, then one atomic per warp into one of 64 partial sums (spread addresses)
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, d);
@@ -1090,7 +1100,8 @@ size_t tg_backward_scratch_bytes(int V) { return (size_t)(V > 0 ? V : 0) * 32 + 
 
 static int backward_impl(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids, const int32_t* offsets,
                          int V, int W, int H, int tw, int th, int per_pixel_sort, int max_layers,
-                         const float* grad_image, const float* grad_depthmap, const float* l2_target, float l2_grad_scale,
+                         const float* grad_image, const float* grad_depthmap, const void* l2_target, bool target_u8,
+                         float l2_grad_scale,
                          float l2_loss_scale, float* l2_loss_out, const float* image, const float* depthmap,
                          const float* final_weights, const int32_t* ends, const int32_t* selection, float* grad_vertices,
                          float* grad_colors, float* grad_opacities, int accumulate, void* scratch, size_t scratch_bytes,
@@ -1102,7 +1113,8 @@ static int backward_impl(const float* tri_geo, const float* tri_attr, const int3
     if (V == 0) return TG_OK;
     const bool packed = accumulate == TG_ACCUMULATE_PACKED;   // gradients stay in the scratch, which keeps accumulating
     TG_REQUIRE(scratch && (packed || (grad_vertices && grad_colors && grad_opacities)), "null gradient / scratch pointer");
-    TG_REQUIRE(((uintptr_t)image & 15) == 0 && ((uintptr_t)grad_image & 15) == 0 && ((uintptr_t)l2_target & 15) == 0 &&
+    TG_REQUIRE(((uintptr_t)image & 15) == 0 && ((uintptr_t)grad_image & 15) == 0 &&
+                   ((uintptr_t)l2_target & (target_u8 ? 3 : 15)) == 0 &&
                    ((uintptr_t)tri_geo & 15) == 0 && ((uintptr_t)tri_attr & 15) == 0 &&
                    ((uintptr_t)grad_vertices & 15) == 0 && ((uintptr_t)scratch & 15) == 0,
                "image / grad_image / target / tri_geo / tri_attr / grad_vertices / scratch must be 16-byte aligned");
@@ -1120,7 +1132,8 @@ static int backward_impl(const float* tri_geo, const float* tri_attr, const int3
     const int tiles = P.tiles_x * ((H + th - 1) / th);
     const int threads = ((tw * th + 31) / 32) * 32;
     const tg::BackwardIn in = {(const float4*)grad_image, grad_depthmap, (const float4*)image, depthmap, final_weights,
-                               ends, (const float4*)l2_target, l2_grad_scale, partials};
+                               ends, target_u8 ? nullptr : (const float4*)l2_target, l2_grad_scale, partials,
+                               target_u8 ? (const uchar4*)l2_target : nullptr};
     if (threads <= 256) {
         if (saved) tg::blend_backward_queued_kernel<256><<<tiles, threads, 0, s>>>(P, in, selection, gpack);
         else if (per_pixel_sort) tg::blend_backward_kernel<true, 256><<<tiles, threads, 0, s>>>(P, in, gpack);
@@ -1203,7 +1216,7 @@ int tg_blend_backward(const float* tri_geo, const float* tri_attr, const int32_t
                       float* grad_opacities, int accumulate, void* scratch, size_t scratch_bytes, tg_stream_t stream) {
     TG_REQUIRE(grad_image && grad_depthmap, "null upstream gradient");
     return backward_impl(tri_geo, tri_attr, sorted_ids, offsets, V, W, H, tw, th, per_pixel_sort, max_layers, grad_image,
-                         grad_depthmap, nullptr, 0.f, 0.f, nullptr, image, depthmap, final_weights, ends, selection,
+                         grad_depthmap, nullptr, false, 0.f, 0.f, nullptr, image, depthmap, final_weights, ends, selection,
                          grad_vertices, grad_colors, grad_opacities, accumulate, scratch, scratch_bytes, stream);
 }
 
@@ -1215,8 +1228,20 @@ int tg_blend_backward_l2(const float* tri_geo, const float* tri_attr, const int3
                          tg_stream_t stream) {
     TG_REQUIRE(target && (loss_out || accumulate == TG_ACCUMULATE_PACKED), "null target / loss pointer");
     return backward_impl(tri_geo, tri_attr, sorted_ids, offsets, V, W, H, tw, th, per_pixel_sort, max_layers, nullptr,
-                         nullptr, target, grad_scale, loss_scale, loss_out, image, depthmap, final_weights, ends, selection,
-                         grad_vertices, grad_colors, grad_opacities, accumulate, scratch, scratch_bytes, stream);
+                         nullptr, target, false, grad_scale, loss_scale, loss_out, image, depthmap, final_weights, ends,
+                         selection, grad_vertices, grad_colors, grad_opacities, accumulate, scratch, scratch_bytes, stream);
+}
+
+int tg_blend_backward_l2_u8(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids, const int32_t* offsets,
+                            int V, int W, int H, int tw, int th, int per_pixel_sort, int max_layers,
+                            const uint8_t* target_rgba8, float grad_scale, float loss_scale, float* loss_out,
+                            const float* image, const float* depthmap, const float* final_weights, const int32_t* ends,
+                            const int32_t* selection, float* grad_vertices, float* grad_colors, float* grad_opacities,
+                            int accumulate, void* scratch, size_t scratch_bytes, tg_stream_t stream) {
+    TG_REQUIRE(target_rgba8 && (loss_out || accumulate == TG_ACCUMULATE_PACKED), "null target / loss pointer");
+    return backward_impl(tri_geo, tri_attr, sorted_ids, offsets, V, W, H, tw, th, per_pixel_sort, max_layers, nullptr,
+                         nullptr, target_rgba8, true, grad_scale, loss_scale, loss_out, image, depthmap, final_weights, ends,
+                         selection, grad_vertices, grad_colors, grad_opacities, accumulate, scratch, scratch_bytes, stream);
 }
 
 }  // extern "C"

@@ -1,6 +1,6 @@
 // Per-tile sort of the (depth, triangle) entries: the segmented counterpart of the device-wide radix
 // sort.  The reference sorts (tile << 32 | depth) keys with a stable device-wide sort
-// (render.cu:505-527); because every triangle occurs at most once per tile and entries are emitted in
+// (cub::DeviceSegmentedSort::StableSortPairs, render.cu:272-284); because every triangle occurs at most once per tile and entries are emitted in
 // triangle order, sorting each tile's segment by (depth, triangle) gives the same permutation.
 //
 // Entries are uint64 words (ordered depth << 32 | triangle), already grouped by tile:
@@ -13,6 +13,8 @@
 //   beyond       the same CTA sorts 16384-entry chunks in shared memory and runs the network's wide
 //                steps on the segment in global memory
 // No kernel here waits on another CTA.
+#include <atomic>
+
 #include "tg_radix.cuh"
 
 namespace tg {
@@ -349,15 +351,15 @@ int sort_tile_lists(uint64_t* entries, const int32_t* offsets, int tiles, int32_
     }
     if (longest > (uint32_t)tg::kTileSortShort) {
         constexpr int kMaxDevices = 64;
-        static bool attr_set[kMaxDevices] = {};
+        static std::atomic<bool> attr_set[kMaxDevices];   // zero-initialised; setting the attribute twice is harmless
         const size_t long_smem = sizeof(uint64_t) * tg::kLongSmemWords;
         int dev = 0;
         TG_CUDA(cudaGetDevice(&dev));
         TG_REQUIRE(dev >= 0 && dev < kMaxDevices, "device index outside the supported range");
-        if (!attr_set[dev]) {
+        if (!attr_set[dev].load(std::memory_order_acquire)) {
             TG_CUDA(cudaFuncSetAttribute(tg::tile_sort_long_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)long_smem));
-            attr_set[dev] = true;
+            attr_set[dev].store(true, std::memory_order_release);
         }
         const int grid = tiles < 148 ? tiles : 148;
         tg::tile_sort_long_kernel<<<grid, tg::kTileSortLongThreads, long_smem, s>>>(entries, offsets, sorted_ids, lists,

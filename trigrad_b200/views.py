@@ -5,8 +5,9 @@ batch shards with no data-path exchange: rank r of N renders views [r*B/N, (r+1)
 mesh (every GPU holds the whole mesh).  World-space gradients of positions, colours and opacities
 accumulate over the rank's views into ONE contiguous fp32 buffer laid out as
 ``[gP (V,3) | gC (V,3) | gO (V) | loss]``; a single ``all_reduce(SUM)`` over NCCL then runs in place on that
-buffer.  The projection world -> NDC and its VJP are plain torch ops outside the hot path, as in the
-reference viewer (``viewer.py:274-280``).
+buffer.  The projection world -> NDC (the reference viewer's tensor operations, ``viewer.py:274-280``) and its
+VJP are one kernel each (``tg_project`` / ``tg_project_backward``, used by ``l2_world_view_step``); ``project``
+is the same map in torch operations for callers that want autograd through it.
 """
 from __future__ import annotations
 
@@ -133,13 +134,20 @@ def l2_view_step(vertices: torch.Tensor, indices: torch.Tensor, colors: torch.Te
     _w.check_tensor(opacities, "opacities", (n,))
     m, _ = indices.shape
     _w.check_tensor(indices, "indices", (m, 3), torch.int32)
-    _w.check_tensor(target, "target", (height, width, 4))
+    if target.dtype == torch.uint8:
+        # 8-bit RGBA target (value / 255): a quarter of the bytes per view; the two-kernel path reads it directly
+        if one_kernel:
+            raise ValueError("the one-kernel step takes a float32 target")
+        _w.check_tensor(target, "target", (height, width, 4), torch.uint8)
+    else:
+        _w.check_tensor(target, "target", (height, width, 4))
     if tile_width * tile_height > 1024:
         raise ValueError("tile_width * tile_height must be <= 1024")
     if m < 1:
         if packed is not None:
             raise ValueError("a mesh without triangles cannot use the packed accumulator")
-        loss += torch.mean((torch.tensor([0.0, 0.0, 0.0, 1.0], device=target.device) - target) ** 2)
+        tf = target.float() / 255 if target.dtype == torch.uint8 else target
+        loss += torch.mean((torch.tensor([0.0, 0.0, 0.0, 1.0], device=target.device) - tf) ** 2)
         return None
     grads = (grad_vertices, grad_colors, grad_opacities)
     if one_kernel and tile_width * tile_height <= 256:
@@ -209,12 +217,33 @@ def l2_world_view_step(points: torch.Tensor, pv, indices: torch.Tensor, colors: 
                        target: torch.Tensor, width: int, height: int, grad_points: torch.Tensor, grad_colors: torch.Tensor,
                        grad_opacities: torch.Tensor, loss: torch.Tensor, tile_width: int = 16, tile_height: int = 16,
                        early_stopping_threshold: float = 1 / 256, max_layers: int = 32,
-                       one_kernel: bool = False) -> torch.Tensor:
+                       one_kernel: bool = False, packed: "PackedGradients | None" = None) -> torch.Tensor:
     """``l2_view_step`` for a mesh in world space seen through the 4x4 matrix ``pv``: projection, rendering step and
     the projection's VJP without torch tensor operations.  ``grad_points [V,3]`` accumulates the world-space
-    gradient; the other arguments are those of ``l2_view_step``.  Returns the rendered image."""
+    gradient; the other arguments are those of ``l2_view_step``.  Returns the rendered image.
+
+    With ``packed`` (a ``PackedGradients`` that is all zero, one per stream) the view's gradients stay in that
+    accumulator through the backward kernel and one more kernel (``tg_unpack_project_backward``) carries them
+    through the projection's VJP into the three tensors and ``loss`` with atomic additions and leaves the
+    accumulator zero again: no per-view clear, no render-space gradient tensor, and views on several streams may
+    add into the same tensors."""
     m = _pv_host(pv)
     verts = project_native(points, m)
+    if packed is not None:
+        import ctypes as C
+
+        from . import _native as N
+
+        image = l2_view_step(verts, indices, colors, opacities, target, width, height, None, None, None, None, tile_width,
+                             tile_height, early_stopping_threshold, max_layers, one_kernel, packed=packed)
+        with torch.cuda.device(points.device):
+            stream = torch.cuda.current_stream(points.device).cuda_stream
+            N.check("unpack_project_backward", N.lib().tg_unpack_project_backward(
+                C.c_void_p(packed.scratch.data_ptr()), packed.scratch.numel(), points.shape[0],
+                C.c_void_p(points.data_ptr()), m.ctypes.data_as(C.c_void_p), 1.0 / float(width * height * 4),
+                C.c_void_p(loss.data_ptr()), C.c_void_p(grad_points.data_ptr()), C.c_void_p(grad_colors.data_ptr()),
+                C.c_void_p(grad_opacities.data_ptr()), C.c_void_p(stream)))
+        return image
     gverts = torch.zeros_like(verts)
     image = l2_view_step(verts, indices, colors, opacities, target, width, height, gverts, grad_colors, grad_opacities, loss,
                          tile_width, tile_height, early_stopping_threshold, max_layers, one_kernel)

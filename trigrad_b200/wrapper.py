@@ -23,6 +23,12 @@ check_tensor = create_check("cuda", precision)
 
 TIMING_KEYS = ("init", "per_tile_lists", "sorting", "bary_transforms", "rasterization")
 
+# In the default mode the forward saves, per pixel, the ids of the fragments it blended (max_layers int32 planes
+# of the image size: 265 MB at 1920x1080, 1.06 GB at 3840x2160, alive until the backward of that render has
+# run) so that the backward need not search the tile lists again.  A render whose planes would exceed this many
+# bytes saves nothing and its backward searches the lists as the reference does (same gradients, slower).
+SELECTION_MAX_BYTES = 1 << 30
+
 
 class _DeviceState:
     """Per (device, stream) reusable buffers: workspace, pinned read-back slots, K estimate."""
@@ -34,17 +40,32 @@ class _DeviceState:
         self.workspace = torch.empty(0, dtype=torch.uint8, device=device)
         self.info = torch.zeros((self.SLOTS, 4), dtype=torch.int32).pin_memory()   # K, longest list, error word, -
         self.slot = 0
+        self.last_slot = -1      # slot of the previous native call on this stream (its error word may still travel)
         self.k_estimate = 0
 
     def next_slot(self) -> int:
         s = self.slot
         self.slot = (self.slot + 1) % self.SLOTS
-        stale = int(self.info[s, 2])
-        if stale:
-            self.info[s, 2] = 0
-            raise RuntimeError(f"trigrad_b200: an earlier render reported device error word {stale} "
-                               "(a bounded wait ran out inside a kernel)")
         return s
+
+    def check_error_word(self, slot: int) -> None:
+        """Raise if the kernels of the call that used `slot` raised the device error word (a bounded wait ran
+        out inside a kernel, so its outputs are not valid).  The word arrives by an asynchronous copy at the
+        end of that call: it is certain to be there once a later event of the same stream has completed."""
+        if slot < 0:
+            return
+        stale = int(self.info[slot, 2])
+        if stale:
+            self.info[slot, 2] = 0
+            raise RuntimeError(f"trigrad_b200: an earlier render reported device error word {stale} "
+                               "(a bounded wait ran out inside a kernel); its outputs are not valid")
+
+    def finish_call(self, slot: int) -> None:
+        """After a native forward call that used `slot` has returned: the call waited for an event recorded after
+        the previous call's work on this stream, so the previous call's error word has arrived - check it."""
+        prev, self.last_slot = self.last_slot, slot
+        if prev != slot:
+            self.check_error_word(prev)
 
     def ensure_workspace(self, nbytes: int) -> torch.Tensor:
         if self.workspace.numel() < nbytes:
@@ -64,13 +85,27 @@ def _state(device: torch.device) -> _DeviceState:
     return st
 
 
+def check_device_errors(device=None) -> None:
+    """Synchronise the current stream of `device` and raise if the last render on it reported a device error
+    word.  ``render`` checks the word of a call when the next call on the same stream returns, and (without
+    waiting) when its backward starts; this is the explicit check for the last call of a program."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    torch.cuda.current_stream(device).synchronize()
+    with torch.cuda.device(device):
+        st = _state(device)
+    st.check_error_word(st.last_slot)
+
+
 def _ptr(t: torch.Tensor | None):
     return None if t is None else C.c_void_p(t.data_ptr())
 
 
 def forward_native(vertices, indices, colors, opacities, width, height, tile_width, tile_height,
-                   early_stopping_threshold, record_timing, per_pixel_sort, max_layers):
-    """Run the whole forward path.  Returns the public outputs and the state saved for backward."""
+                   early_stopping_threshold, record_timing, per_pixel_sort, max_layers, save_selection=True):
+    """Run the whole forward path.  Returns the public outputs and the state saved for backward.
+
+    ``save_selection=False`` (or planes larger than ``SELECTION_MAX_BYTES``) skips the per-pixel record of the
+    blended fragment ids; the backward then searches the tile lists again."""
     lib = N.lib()
     device = vertices.device
     T = indices.shape[0]
@@ -87,6 +122,8 @@ def forward_native(vertices, indices, colors, opacities, width, height, tile_wid
         tri_attr = torch.empty((T, N.ATTR_WORDS), **f32)
         offsets = torch.empty(tiles + 1, dtype=torch.int32, device=device)
         planes = lib.tg_selection_planes(int(bool(per_pixel_sort)), int(max_layers))
+        if not save_selection or planes * height * width * 4 > SELECTION_MAX_BYTES:
+            planes = 0
         selection = torch.empty((planes, height, width), dtype=torch.int32, device=device) if planes else None
         stage_ms = (C.c_float * 5)() if record_timing else None
         cap = max(int(st.k_estimate * 1.25) + 1024, 2 * T + 1024)
@@ -107,6 +144,7 @@ def forward_native(vertices, indices, colors, opacities, width, height, tile_wid
                 cap = int(K * 1.25) + 1024
                 continue
             N.check("render_forward", status)
+            st.finish_call(slot)
             break
         st.k_estimate = K
         timings = None
@@ -123,6 +161,10 @@ def backward_native(grad_image, grad_depthmap, saved, V, width, height, tile_wid
     device = image.device
     with torch.cuda.device(device):
         stream = torch.cuda.current_stream(device).cuda_stream
+        # the forward's error word, if it has arrived by now (no waiting here): lists built by a kernel whose
+        # bounded wait ran out must not be walked
+        st = _state(device)
+        st.check_error_word(st.last_slot)
         nscratch = lib.tg_backward_scratch_bytes(V)
         scratch = torch.empty(nscratch, dtype=torch.uint8, device=device)
         grad_image = grad_image.contiguous()
@@ -149,7 +191,8 @@ def backward_l2_native(target, saved, V, width, height, tile_width, tile_height,
     default per-pixel mode with ``max_layers <= 32``); ``out`` = (gV [V,4], gC [V,3], gO [V]) and the 0-d float32
     ``loss_out`` are overwritten, or added to when ``accumulate`` is true.  With ``packed_scratch`` (a zeroed uint8
     tensor of ``tg_backward_scratch_bytes(V)`` bytes shared by the views of a step) nothing is written but that
-    accumulator; ``unpack_gradients_native`` turns it into the three tensors later.
+    accumulator; ``unpack_gradients_native`` turns it into the three tensors later.  ``target`` is float32
+    ``[H,W,4]`` or uint8 ``[H,W,4]`` (8-bit RGBA, read as value / 255).
     """
     lib = N.lib()
     sorted_ids, offsets, tri_geo, tri_attr, image, depthmap, final_weights, ends, selection = saved
@@ -164,7 +207,8 @@ def backward_l2_native(target, saved, V, width, height, tile_width, tile_height,
             scratch, mode, (gV, gC, gO), loss_out = packed_scratch, N.TG_ACCUMULATE_PACKED, (None, None, None), None
         else:
             scratch, mode, (gV, gC, gO) = torch.empty(nscratch, dtype=torch.uint8, device=device), int(bool(accumulate)), out
-        status = lib.tg_blend_backward_l2(
+        entry = lib.tg_blend_backward_l2_u8 if target.dtype == torch.uint8 else lib.tg_blend_backward_l2
+        status = entry(
             _ptr(tri_geo), _ptr(tri_attr), _ptr(sorted_ids), _ptr(offsets), V, width, height, tile_width, tile_height,
             int(bool(per_pixel_sort)), int(max_layers), _ptr(target.contiguous()), 2.0 / n, 1.0 / n, _ptr(loss_out),
             _ptr(image), _ptr(depthmap), _ptr(final_weights), _ptr(ends), _ptr(selection), _ptr(gV), _ptr(gC), _ptr(gO),
@@ -224,7 +268,8 @@ def step_l2_native(vertices, indices, colors, opacities, target, width, height, 
             sorted_ids = torch.empty(cap, dtype=torch.int32, device=device)
             ws = st.ensure_workspace(lib.tg_forward_workspace_bytes(T, tiles, cap))
             base = (ws.data_ptr() + 255) // 256 * 256
-            info = st.info[st.next_slot()]
+            slot = st.next_slot()
+            info = st.info[slot]
             status = lib.tg_render_step_l2(
                 _ptr(vertices), _ptr(indices), _ptr(colors), _ptr(opacities), T, V, width, height, tile_width, tile_height,
                 float(early_stopping_threshold), int(max_layers), _ptr(target), 2.0 / npix, 1.0 / npix, _ptr(loss_out),
@@ -237,6 +282,7 @@ def step_l2_native(vertices, indices, colors, opacities, target, width, height, 
                 cap = int(K * 1.25) + 1024
                 continue
             N.check("render_step_l2", status)
+            st.finish_call(slot)
             break
         st.k_estimate = K
         timings = None
@@ -309,6 +355,10 @@ def render(vertices: torch.Tensor, indices: torch.Tensor, colors: torch.Tensor, 
 
     Returns ``image`` (height, width, 4) whose alpha channel holds the remaining translucency,
     ``depthmap`` (height, width) and, with ``record_timing``, a dict of stage times in seconds.
+
+    Memory: in the default mode (``per_pixel_sort`` and ``max_layers <= 32``) autograd keeps ``max_layers`` int32
+    planes of the image size alive per render until its backward has run (265 MB at 1920x1080), see
+    ``SELECTION_MAX_BYTES`` in this module for the switch to the list-searching backward.
     """
     if tile_width * tile_height > 1024:
         raise ValueError("tile_width * tile_height must be <= 1024")
