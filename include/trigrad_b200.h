@@ -176,6 +176,22 @@ int tg_blend_backward(const float* tri_geo, const float* tri_attr, const int32_t
                       float* grad_colors, float* grad_opacities, int accumulate, void* scratch, size_t scratch_bytes,
                       tg_stream_t stream);
 
+/* Gradients of what the forward pass blended, in every mode (an extension; no counterpart in the reference).
+ * tg_blend_backward restates the reference's backward literally, and that kernel is only consistent with its
+ * forward in the default mode: with per_pixel_sort = 0 it visits the first `ends` list entries front to back
+ * with recurrences written for a back-to-front walk (src/trigrad/render.cu:659-666 against :478-497), and
+ * beyond 32 layers it reverses the order inside each batch of 32 only (:673-693).  This entry point computes
+ * the derivative of the forward outputs with respect to vertices (x, y, w), colours and opacities for any
+ * per_pixel_sort / max_layers; in the default mode it agrees with tg_blend_backward.  Arguments as for
+ * tg_blend_backward without `selection`; accumulate is 0 or 1.
+ */
+int tg_blend_backward_corrected(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids,
+                                const int32_t* offsets, int V, int W, int H, int tile_w, int tile_h, int per_pixel_sort,
+                                int max_layers, const float* grad_image, const float* grad_depthmap, const float* image,
+                                const float* depthmap, const float* final_weights, const int32_t* ends,
+                                float* grad_vertices, float* grad_colors, float* grad_opacities, int accumulate,
+                                void* scratch, size_t scratch_bytes, tg_stream_t stream);
+
 /* Backward of the mean-squared-error loss  loss = loss_scale * sum((image - target)^2)  fused into stage 7:
  * the upstream gradient grad_scale * (image - target) is formed per pixel inside the kernel (depth-map
  * gradient zero), so no gradient image is written or read, and the loss value is reduced on the way.
@@ -243,14 +259,24 @@ int tg_blend_step_l2(const float* tri_geo, const float* tri_attr, const int32_t*
  *                bary_transforms, rasterization} measured with CUDA events (synchronises)
  * If K > list_capacity nothing past the scan is run and TG_ERR_CAPACITY is returned with info_host[0]
  * set; call again with a larger list and workspace.
+ *   flags        0, or TG_FORWARD_CULL_TILES: a (triangle, tile) pair of the bounding rectangle is listed only if
+ *                the triangle can cover the centre of some pixel of that tile - the exact overlap test the
+ *                reference leaves as a TODO (src/trigrad/render.cu:110; its lists hold every tile of the bounding
+ *                box, the useless pairs carrying the key 1e30, :254-261).  The test evaluates each barycentric at
+ *                the corner of the tile's pixel-centre rectangle that maximises it with the operations of the
+ *                per-pixel coverage test, so it never drops a pair that covers a pixel: image, depth map and
+ *                gradients are bit-identical with and without it in the default mode; offsets, sorted_ids and K
+ *                shrink (they then differ from the reference's).  Not for per_pixel_sort = 0, where the
+ *                reference's backward indexes the list by position.  Ignored beyond 65536 tiles.
  */
+#define TG_FORWARD_CULL_TILES 1u
 size_t tg_forward_workspace_bytes(int T, int tiles, uint32_t list_capacity);
 int tg_render_forward(const float* vertices, const int32_t* indices, const float* colors, const float* opacities,
                       int T, int W, int H, int tile_w, int tile_h, float early_stopping_threshold,
                       int per_pixel_sort, int max_layers, float* image, float* depthmap, float* final_weights,
                       int32_t* ends, int32_t* selection, float* tri_geo, float* tri_attr, int32_t* sorted_ids,
                       uint32_t list_capacity, int32_t* offsets, void* workspace, size_t workspace_bytes, uint32_t* info_host,
-                      float* stage_ms_host, tg_stream_t stream);
+                      float* stage_ms_host, unsigned flags, tg_stream_t stream);
 
 /* ---- whole optimisation step of one view ------------------------------------------------------------
  * tg_render_forward with tg_blend_step_l2 in place of the compositing kernel: binning, tile lists,
@@ -264,7 +290,8 @@ int tg_render_step_l2(const float* vertices, const int32_t* indices, const float
                       float* depthmap, float* final_weights, int32_t* ends, float* tri_geo, float* tri_attr,
                       int32_t* sorted_ids, uint32_t list_capacity, int32_t* offsets, float* grad_vertices,
                       float* grad_colors, float* grad_opacities, int accumulate, void* workspace, size_t workspace_bytes,
-                      void* scratch, size_t scratch_bytes, uint32_t* info_host, float* stage_ms_host, tg_stream_t stream);
+                      void* scratch, size_t scratch_bytes, uint32_t* info_host, float* stage_ms_host, unsigned flags,
+                      tg_stream_t stream);
 
 /* ---- the step before the path: world -> render-space vertices and the VJP ------------------------------
  * points [V,3] world positions, pv_host: 16 floats in HOST memory, the row-major projection * view

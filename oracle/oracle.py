@@ -146,17 +146,19 @@ def build_lists_staged(verts, idx, W, H, tw, th) -> Staged:
     return Staged(rects, counts, tri_offsets, keys, tris, keys_sorted, np.ascontiguousarray(ids_sorted), offsets, depth)
 
 
-def build_lists(verts, idx, W, H, tw, th) -> Lists:
+def build_lists(verts, idx, W, H, tw, th, cull: bool = False) -> Lists:
+    """Per-tile sorted lists.  ``cull`` drops the (triangle, tile) pairs whose triangle provably covers no pixel centre of
+    the tile (an extension; the reference lists every tile of the bounding box, ``render.cu:110``)."""
     verts = np.ascontiguousarray(verts)
     idx = np.ascontiguousarray(idx, dtype=np.int32)
     T = idx.shape[0]
     nt = num_tiles(W, H, tw, th)
     offsets = np.empty(nt + 1, np.int32)
     f = _fn("tgo_build_lists", verts.dtype)
-    K = f(_p(verts), _p(idx), T, W, H, tw, th, _p(offsets), None, None, C.c_longlong(0))
+    K = f(_p(verts), _p(idx), T, W, H, tw, th, _p(offsets), None, None, C.c_longlong(0), int(cull))
     ids = np.empty(max(K, 1), np.int32)
     keys = np.empty(max(K, 1), verts.dtype)
-    K2 = f(_p(verts), _p(idx), T, W, H, tw, th, _p(offsets), _p(ids), _p(keys), C.c_longlong(K))
+    K2 = f(_p(verts), _p(idx), T, W, H, tw, th, _p(offsets), _p(ids), _p(keys), C.c_longlong(K), int(cull))
     assert K2 == K
     return Lists(offsets, ids[:K], keys[:K])
 
@@ -212,7 +214,10 @@ def forward(verts, idx, colors, opac, W, H, tw=16, th=16, thr=1 / 256, per_pixel
 
 
 def backward(verts, idx, colors, opac, W, H, fwd: ForwardOut, grad_image, grad_depth, tw=16, th=16,
-             per_pixel_sort=True, max_layers=32, tile_stride: int = 1):
+             per_pixel_sort=True, max_layers=32, tile_stride: int = 1, corrected: bool = False):
+    """Gradients (gV [V,4], gC [V,3], gO [V]).  ``corrected=False`` restates the reference literally, including its
+    behaviour outside the default mode (``render.cu:659-666``, ``:673-693``); ``corrected=True`` visits the blended
+    fragments last to first in every mode (an extension; identical in the default mode)."""
     dt = np.asarray(verts).dtype
     verts = np.ascontiguousarray(verts, dtype=dt)
     idx = np.ascontiguousarray(idx, dtype=np.int32)
@@ -229,7 +234,8 @@ def backward(verts, idx, colors, opac, W, H, fwd: ForwardOut, grad_image, grad_d
     ids = np.ascontiguousarray(fwd.lists.ids)
     _fn("tgo_backward", dt)(_p(verts), _p(idx), _p(colors), _p(opac), T, W, H, tw, th, _p(ids), _p(fwd.lists.offsets),
                             _p(fwd.M), int(bool(per_pixel_sort)), int(max_layers), _p(gi), _p(gd), _p(fwd.image),
-                            _p(fwd.depthmap), _p(fwd.final_weights), _p(fwd.ends), _p(gV), _p(gC), _p(gO), int(tile_stride))
+                            _p(fwd.depthmap), _p(fwd.final_weights), _p(fwd.ends), _p(gV), _p(gC), _p(gO), int(tile_stride),
+                            int(bool(corrected)))
     return gV, gC, gO
 
 

@@ -56,10 +56,12 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
 
     with ThreadPoolExecutor(max_workers=4) as ex:
         objs = list(ex.map(one, SOURCES))
-    cmd = [_nvcc(), "-shared", "-o", LIB] + objs + ["-cudart", "static"]
+    tmp = LIB + ".tmp"     # link beside the target and rename: a reader never sees a half-written library
+    cmd = [_nvcc(), "-shared", "-o", tmp] + objs + ["-cudart", "static"]
     if verbose:
         print(" ".join(cmd), flush=True)
     subprocess.run(cmd, check=True)
+    os.replace(tmp, LIB)
     return LIB
 
 

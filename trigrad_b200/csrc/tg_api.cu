@@ -70,8 +70,8 @@ struct StageTimer {
 static int build_tile_lists(const float* vertices, const int32_t* indices, const float* colors, const float* opacities,
                             int T, int W, int H, int tw, int th, int max_layers, float* tri_geo, float* tri_attr,
                             int32_t* sorted_ids, uint32_t list_capacity, int32_t* offsets, void* workspace,
-                            size_t workspace_bytes, uint32_t* info_host, StageTimer& timer, uint32_t** device_status,
-                            cudaStream_t s) {
+                            size_t workspace_bytes, uint32_t* info_host, unsigned flags, StageTimer& timer,
+                            uint32_t** device_status, cudaStream_t s) {
     TG_REQUIRE(T >= 0 && W > 0 && H > 0 && tw > 0 && th > 0, "sizes");
     TG_REQUIRE(tw * th <= 1024, "tile_width * tile_height must be <= 1024");
     TG_REQUIRE(max_layers >= 1, "max_layers must be >= 1");
@@ -80,6 +80,9 @@ static int build_tile_lists(const float* vertices, const int32_t* indices, const
     TG_REQUIRE(list_capacity < 0x80000000u, "list capacity must stay below 2^31");
     const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
     const int tiles = tiles_x * tiles_y;
+    TG_REQUIRE((flags & ~(unsigned)TG_FORWARD_CULL_TILES) == 0, "unknown flag");
+    // beyond 65536 tiles the tile counts go through the device-wide scan, which the culling variant does not feed
+    const bool cull = (flags & TG_FORWARD_CULL_TILES) != 0 && tiles <= tg::kTileScanByLastCta;
     const ForwardWorkspace ws(workspace, T, tiles, list_capacity);
     *device_status = ws.status;
     if (workspace_bytes < ws.total) {
@@ -100,7 +103,7 @@ static int build_tile_lists(const float* vertices, const int32_t* indices, const
     // per-triangle records, triangle offsets, per-tile counts and tile offsets
     int st = tg_host::preprocess_scan(vertices, indices, colors, opacities, T, W, H, tw, th, tri_geo, tri_attr,
                                       ws.tri_offsets, ws.scan_scratch, ws.status, ws.tile_cursor, offsets,
-                                      ws.tile_scan_scratch, s);
+                                      ws.tile_scan_scratch, cull, s);
     if (st) return st;
     timer.mark();                                                    // [2] start of "per_tile_lists"
     TG_CUDA(cudaMemcpyAsync(&info_host[0], ws.tri_offsets + T, 2 * sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
@@ -108,7 +111,7 @@ static int build_tile_lists(const float* vertices, const int32_t* indices, const
     // Entries are written while K travels to the host: the kernel drops those beyond the capacity, and
     // nothing that reads them is launched before K has been checked.
     st = tg_host::emit_entries(vertices, indices, T, W, H, tw, th, ws.tri_offsets, ws.scan_scratch, ws.tile_cursor,
-                               ws.entries, list_capacity, s);
+                               ws.entries, list_capacity, cull ? tri_geo : nullptr, s);
     if (st) return st;
     TG_CUDA(cudaEventSynchronize(k_ready));
     const uint32_t K = info_host[0];
@@ -154,13 +157,14 @@ int tg_render_forward(const float* vertices, const int32_t* indices, const float
                       int W, int H, int tw, int th, float thr, int per_pixel_sort, int max_layers, float* image,
                       float* depthmap, float* final_weights, int32_t* ends, int32_t* selection, float* tri_geo,
                       float* tri_attr, int32_t* sorted_ids, uint32_t list_capacity, int32_t* offsets, void* workspace,
-                      size_t workspace_bytes, uint32_t* info_host, float* stage_ms_host, tg_stream_t stream) {
+                      size_t workspace_bytes, uint32_t* info_host, float* stage_ms_host, unsigned flags,
+                      tg_stream_t stream) {
     TG_REQUIRE(image && depthmap && final_weights && ends, "null pointer");
     cudaStream_t s = (cudaStream_t)stream;
     StageTimer timer(stage_ms_host != nullptr, s);
     uint32_t* device_status = nullptr;
     int st = build_tile_lists(vertices, indices, colors, opacities, T, W, H, tw, th, max_layers, tri_geo, tri_attr,
-                              sorted_ids, list_capacity, offsets, workspace, workspace_bytes, info_host, timer, &device_status, s);
+                              sorted_ids, list_capacity, offsets, workspace, workspace_bytes, info_host, flags, timer, &device_status, s);
     if (st) return st;
     timer.mark();                                                    // [4] start of "rasterization"
     st = tg_blend_forward(tri_geo, tri_attr, sorted_ids, offsets, W, H, tw, th, thr, per_pixel_sort, max_layers, image,
@@ -178,14 +182,15 @@ int tg_render_step_l2(const float* vertices, const int32_t* indices, const float
                       float* final_weights, int32_t* ends, float* tri_geo, float* tri_attr, int32_t* sorted_ids,
                       uint32_t list_capacity, int32_t* offsets, float* grad_vertices, float* grad_colors,
                       float* grad_opacities, int accumulate, void* workspace, size_t workspace_bytes, void* scratch,
-                      size_t scratch_bytes, uint32_t* info_host, float* stage_ms_host, tg_stream_t stream) {
+                      size_t scratch_bytes, uint32_t* info_host, float* stage_ms_host, unsigned flags,
+                      tg_stream_t stream) {
     TG_REQUIRE(image && depthmap && final_weights && ends && target, "null pointer");
     TG_REQUIRE(tw * th <= 256 && max_layers <= 32, "the one-kernel step needs tiles of at most 256 pixels and max_layers <= 32");
     cudaStream_t s = (cudaStream_t)stream;
     StageTimer timer(stage_ms_host != nullptr, s);
     uint32_t* device_status = nullptr;
     int st = build_tile_lists(vertices, indices, colors, opacities, T, W, H, tw, th, max_layers, tri_geo, tri_attr,
-                              sorted_ids, list_capacity, offsets, workspace, workspace_bytes, info_host, timer, &device_status, s);
+                              sorted_ids, list_capacity, offsets, workspace, workspace_bytes, info_host, flags, timer, &device_status, s);
     if (st) return st;
     timer.mark();                                                    // [4] start of "rasterization" (here: forward + backward)
     st = tg_blend_step_l2(tri_geo, tri_attr, sorted_ids, offsets, V, W, H, tw, th, thr, max_layers, target, grad_scale,

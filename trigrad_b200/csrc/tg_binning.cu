@@ -18,7 +18,7 @@ __device__ __forceinline__ uint32_t preprocess_triangle(int t, const float4* __r
                                                         const float* __restrict__ opacities, int W, int H, int tw,
                                                         int th, int tiles_x, int tiles_y, int4* __restrict__ tri_rects,
                                                         float4* __restrict__ tri_geo, float4* __restrict__ tri_attr,
-                                                        Rect& r) {
+                                                        Rect& r, float* m_out = nullptr) {
     int ia = indices[3 * (size_t)t], ib = indices[3 * (size_t)t + 1], ic = indices[3 * (size_t)t + 2];
     float4 a = vertices[ia], b = vertices[ib], c = vertices[ic];
 
@@ -38,6 +38,10 @@ __device__ __forceinline__ uint32_t preprocess_triangle(int t, const float4* __r
     float m6 = div(sub(a.y, b.y), denom);
     float m7 = div(sub(b.x, a.x), denom);
     float m8 = div(sub(mul(a.x, b.y), mul(b.x, a.y)), denom);
+    if (m_out) {
+        m_out[0] = m0; m_out[1] = m1; m_out[2] = m2; m_out[3] = m3; m_out[4] = m4; m_out[5] = m5; m_out[6] = m6;
+        m_out[7] = m7; m_out[8] = m8;
+    }
 
     // Lower bound of the per-pixel sort depth: with weights of one sign the interpolated depth is
     // a convex combination of the vertex depths; a relative margin covers fp32 rounding.
@@ -227,7 +231,8 @@ struct TileBinArgs {
 // coalesced stores (a single SM issues too few memory requests per clock for anything strided).
 constexpr int kTileScanRound = 2048;
 __device__ void tile_offsets_by_one_cta(uint32_t* cursor, int32_t* offsets, int tiles, uint32_t* longest,
-                                        uint32_t* s_buf /*[2048]*/, uint32_t* s_warp /*[8]*/) {
+                                        uint32_t* s_buf /*[2048]*/, uint32_t* s_warp /*[8]*/,
+                                        uint32_t* k_out = nullptr) {
     constexpr int kPer = kTileScanRound / 256;
     const int tid = threadIdx.x, warp = tid >> 5;
     uint32_t carry = 0, biggest = 0;
@@ -279,7 +284,10 @@ __device__ void tile_offsets_by_one_cta(uint32_t* cursor, int32_t* offsets, int 
         }
         carry += total;
     }
-    if (tid == 0) offsets[tiles] = (int32_t)carry;
+    if (tid == 0) {
+        offsets[tiles] = (int32_t)carry;
+        if (k_out) *k_out = carry;
+    }
     biggest = __reduce_max_sync(0xffffffffu, biggest);
     __syncthreads();
     if (lane_id() == 0) s_warp[warp] = biggest;
@@ -291,6 +299,10 @@ __device__ void tile_offsets_by_one_cta(uint32_t* cursor, int32_t* offsets, int 
     }
 }
 
+// CULL: a (triangle, tile) pair of the bounding rectangle is counted only if the triangle can cover the centre of
+// some pixel of the tile (rect_may_cover on the tile's pixel-centre rectangle): the exact test the reference
+// leaves open (render.cu:110).  K is then the sum of the tile counts, not of the rectangle sizes.
+template <bool CULL>
 __global__ void __launch_bounds__(256, 6) preprocess_count_kernel(const float4* __restrict__ vertices,
                                                                const int* __restrict__ indices,
                                                                const float* __restrict__ colors,
@@ -304,13 +316,19 @@ __global__ void __launch_bounds__(256, 6) preprocess_count_kernel(const float4* 
     uint32_t* s_loc = s_buf;                 // [257] exclusive offsets of the CTA's triangles within the CTA
     int* s_rect = (int*)s_buf + 257;         // [768] x0, y0, rows of each triangle's tile rectangle
     __shared__ bool s_last;
+    __shared__ float s_m[CULL ? 9 * 256 : 1];   // barycentric matrices of the CTA's triangles, component-major
     const int tid = threadIdx.x;
     const int p = blockIdx.x, num_parts = gridDim.x;
     const int t = p * 256 + tid;
     Rect r = {0, 0, 0, 0};
+    float m[9];
     const uint32_t count = (t < T) ? preprocess_triangle(t, vertices, indices, colors, opacities, W, H, tw, th, tiles_x,
-                                                         tiles_y, nullptr, tri_geo, tri_attr, r)
+                                                         tiles_y, nullptr, tri_geo, tri_attr, r, CULL ? m : nullptr)
                                    : 0u;
+    if (CULL && count) {
+#pragma unroll
+        for (int k = 0; k < 9; k++) s_m[k * 256 + tid] = m[k];
+    }
     uint32_t incl = count;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
@@ -348,6 +366,12 @@ __global__ void __launch_bounds__(256, 6) preprocess_count_kernel(const float4* 
         const uint32_t local = e - s_loc[lo];
         const uint32_t ny = (uint32_t)s_rect[3 * lo + 2];
         const int tx = s_rect[3 * lo] + (int)(local / ny), ty = s_rect[3 * lo + 1] + (int)(local % ny);
+        if (CULL) {
+            float mm[9];
+#pragma unroll
+            for (int k = 0; k < 9; k++) mm[k] = s_m[k * 256 + lo];
+            if (!rect_may_cover(mm, tile_pixel_rect(tx, ty, W, H, tw, th))) continue;
+        }
         atomicAdd(&bin.tile_cursor[ty * tiles_x + tx], 1u);
     }
     __syncthreads();                          // the CTA's counts are issued; one cumulative fence publishes them
@@ -366,13 +390,15 @@ __global__ void __launch_bounds__(256, 6) preprocess_count_kernel(const float4* 
     __syncthreads();
     if (lane_id() == 0) s_warp[warp] = k;
     __syncthreads();
-    if (tid == 0) {
+    if (tid == 0 && !CULL) {
         k = 0;
 #pragma unroll
         for (int w = 0; w < 8; w++) k += s_warp[w];
         *bin.k_out = k;
     }
-    if (bin.scan_here) tile_offsets_by_one_cta(bin.tile_cursor, bin.offsets, bin.tiles, bin.longest, s_buf, s_warp);
+    if (bin.scan_here)
+        tile_offsets_by_one_cta(bin.tile_cursor, bin.offsets, bin.tiles, bin.longest, s_buf, s_warp,
+                                CULL ? bin.k_out : nullptr);
 }
 
 // ================================================================================================
@@ -465,13 +491,15 @@ struct __align__(16) EmitTri {
     float A, B, C;
     int x0, y0, ny, pad;
 };
+struct EmitMat { float m[9]; };   // CULL only: the triangle's barycentric matrix (from its packed record)
 constexpr int kEmitThreads = 256;
 
 //
 // DIRECT: the tile offsets are known already; every entry takes the next free slot of its tile
 // (`tile_cursor`, arrival order) and is stored there as (ordered depth << 32 | triangle), ready for the
 // per-tile sort.  `keys` is that array, `ids` is unused.
-template <bool DIRECT>
+// CULL (with DIRECT): pairs that preprocess_count_kernel<true> did not count are skipped by the same test.
+template <bool DIRECT, bool CULL>
 __global__ void __launch_bounds__(kEmitThreads) emit_keys_kernel(const float4* __restrict__ vertices,
                                                                  const int* __restrict__ indices, int T, int W, int H,
                                                                  int tw, int th, int tiles_x, int tiles_y,
@@ -479,8 +507,10 @@ __global__ void __launch_bounds__(kEmitThreads) emit_keys_kernel(const float4* _
                                                                  uint64_t* __restrict__ keys, uint32_t* __restrict__ ids,
                                                                  uint32_t capacity, HistArgs hist,
                                                                  uint32_t* __restrict__ tile_cursor,
-                                                                 const uint32_t* __restrict__ part_total) {
+                                                                 const uint32_t* __restrict__ part_total,
+                                                                 const float4* __restrict__ tri_geo) {
     __shared__ EmitTri s_tri[kEmitThreads];
+    __shared__ EmitMat s_mat[CULL ? kEmitThreads : 1];
     __shared__ uint32_t s_off[kEmitThreads + 1];
     __shared__ uint32_t s_hist[kMaxPasses * kRadix];
     __shared__ uint32_t s_warp_tot[kSortWarps];
@@ -506,6 +536,10 @@ __global__ void __launch_bounds__(kEmitThreads) emit_keys_kernel(const float4* _
         e.x0 = r.x0; e.y0 = r.y0; e.ny = r.y1 - r.y0 + 1; e.pad = 0;
         s_tri[tid] = e;
         s_off[tid] = tri_offsets[t];
+        if (CULL) {
+            const float4 g0 = tri_geo[4 * (size_t)t], g1 = tri_geo[4 * (size_t)t + 1], g2 = tri_geo[4 * (size_t)t + 2];
+            s_mat[tid] = {{g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w, g2.x}};
+        }
     }
     // DIRECT: the offsets are local to the 256 triangles of the CTA and its total stands in a separate array
     if (tid == 0) s_off[ntri] = DIRECT ? part_total[blockIdx.x] : tri_offsets[t0 + ntri];
@@ -522,6 +556,7 @@ __global__ void __launch_bounds__(kEmitThreads) emit_keys_kernel(const float4* _
         const EmitTri& tr = s_tri[lo];
         const uint32_t local = ge - s_off[lo];
         const int tx = tr.x0 + (int)(local / (uint32_t)tr.ny), ty = tr.y0 + (int)(local % (uint32_t)tr.ny);
+        if (CULL && !rect_may_cover(s_mat[lo].m, tile_pixel_rect(tx, ty, W, H, tw, th))) continue;
         const TriXYZ v = {tr.ax, tr.ay, tr.az, tr.bx, tr.by, tr.bz, tr.cx, tr.cy, tr.cz};
         const Plane pl = {tr.A, tr.B, tr.C};
         const float depth = tile_key(v, pl, tx, ty, W, H, tw, th);
@@ -591,7 +626,7 @@ size_t preprocess_scan_scratch_bytes(int T) { return 8 + 4 * ((size_t)(T > 0 ? (
 // (zeroed, tg_scan_scratch_bytes(tiles) bytes) is needed, and [T + 1] is set to UINT32_MAX (not known).
 int preprocess_scan(const float* vertices, const int32_t* indices, const float* colors, const float* opacities, int T,
                     int W, int H, int tw, int th, float* tri_geo, float* tri_attr, uint32_t* tri_offsets, void* scratch,
-                    uint32_t* status, uint32_t* tile_cursor, int32_t* offsets, void* tile_scan_scratch,
+                    uint32_t* status, uint32_t* tile_cursor, int32_t* offsets, void* tile_scan_scratch, bool cull,
                     cudaStream_t stream) {
     if (int s = check_dims_internal(T, W, H, tw, th)) return s;
     TG_REQUIRE(tri_offsets && scratch && status && tile_cursor && offsets, "null pointer");
@@ -609,9 +644,15 @@ int preprocess_scan(const float* vertices, const int32_t* indices, const float* 
     TG_REQUIRE(by_last_cta || tile_scan_scratch, "null tile scan scratch");
     const tg::TileBinArgs bin = {tile_cursor, offsets, (uint32_t*)scratch, tiles, by_last_cta ? 1 : 0,
                                  tri_offsets + T + 1, (uint32_t*)scratch + 2, tri_offsets + T};
-    tg::preprocess_count_kernel<<<(T + 255) / 256, 256, 0, stream>>>(
-        (const float4*)vertices, indices, colors, opacities, T, W, H, tw, th, tiles_x, tiles_y, (float4*)tri_geo,
-        (float4*)tri_attr, tri_offsets, bin);
+    TG_REQUIRE(!cull || by_last_cta, "tile culling is limited to 65536 tiles");
+    if (cull)
+        tg::preprocess_count_kernel<true><<<(T + 255) / 256, 256, 0, stream>>>(
+            (const float4*)vertices, indices, colors, opacities, T, W, H, tw, th, tiles_x, tiles_y, (float4*)tri_geo,
+            (float4*)tri_attr, tri_offsets, bin);
+    else
+        tg::preprocess_count_kernel<false><<<(T + 255) / 256, 256, 0, stream>>>(
+            (const float4*)vertices, indices, colors, opacities, T, W, H, tw, th, tiles_x, tiles_y, (float4*)tri_geo,
+            (float4*)tri_attr, tri_offsets, bin);
     TG_LAUNCH_CHECK("preprocess_count_kernel");
     if (!by_last_cta) {
         // counts -> offsets by the device-wide scan, then the cursors start at the offsets
@@ -633,9 +674,9 @@ int emit_keys(const float* vertices, const int32_t* indices, int T, int W, int H
     if (T == 0) return TG_OK;
     TG_REQUIRE(vertices && indices && tri_offsets && keys && ids, "null pointer");
     const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
-    tg::emit_keys_kernel<false><<<(T + tg::kEmitThreads - 1) / tg::kEmitThreads, tg::kEmitThreads, 0, stream>>>(
+    tg::emit_keys_kernel<false, false><<<(T + tg::kEmitThreads - 1) / tg::kEmitThreads, tg::kEmitThreads, 0, stream>>>(
         (const float4*)vertices, indices, T, W, H, tw, th, tiles_x, tiles_y, tri_offsets, keys, ids, capacity, hist,
-        nullptr, nullptr);
+        nullptr, nullptr, nullptr);
     TG_LAUNCH_CHECK("emit_keys_kernel");
     return TG_OK;
 }
@@ -644,15 +685,21 @@ int emit_keys(const float* vertices, const int32_t* indices, int T, int W, int H
 // `tri_offsets` and `scan_scratch` as preprocess_scan left them (CTA-local offsets, CTA totals).
 int emit_entries(const float* vertices, const int32_t* indices, int T, int W, int H, int tw, int th,
                  const uint32_t* tri_offsets, const void* scan_scratch, uint32_t* tile_cursor, uint64_t* entries,
-                 uint32_t capacity, cudaStream_t stream) {
+                 uint32_t capacity, const float* tri_geo_for_cull, cudaStream_t stream) {
     if (int s = check_dims_internal(T, W, H, tw, th)) return s;
     if (T == 0 || capacity == 0) return TG_OK;
     TG_REQUIRE(vertices && indices && tri_offsets && scan_scratch && tile_cursor && entries, "null pointer");
     const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
     const tg::HistArgs none = {nullptr, nullptr, 0, 0, 0};
-    tg::emit_keys_kernel<true><<<(T + tg::kEmitThreads - 1) / tg::kEmitThreads, tg::kEmitThreads, 0, stream>>>(
-        (const float4*)vertices, indices, T, W, H, tw, th, tiles_x, tiles_y, tri_offsets, entries, nullptr, capacity, none,
-        tile_cursor, (const uint32_t*)scan_scratch + 2);
+    const int grid = (T + tg::kEmitThreads - 1) / tg::kEmitThreads;
+    if (tri_geo_for_cull)
+        tg::emit_keys_kernel<true, true><<<grid, tg::kEmitThreads, 0, stream>>>(
+            (const float4*)vertices, indices, T, W, H, tw, th, tiles_x, tiles_y, tri_offsets, entries, nullptr, capacity,
+            none, tile_cursor, (const uint32_t*)scan_scratch + 2, (const float4*)tri_geo_for_cull);
+    else
+        tg::emit_keys_kernel<true, false><<<grid, tg::kEmitThreads, 0, stream>>>(
+            (const float4*)vertices, indices, T, W, H, tw, th, tiles_x, tiles_y, tri_offsets, entries, nullptr, capacity,
+            none, tile_cursor, (const uint32_t*)scan_scratch + 2, nullptr);
     TG_LAUNCH_CHECK("emit_entries_kernel");
     return TG_OK;
 }

@@ -102,7 +102,7 @@ __device__ __forceinline__ BlendedValues blend_one(const Bary& b, const float* w
 }
 
 // NDC extent (pixel centres) of the active pixels of one warp.
-struct WarpRect { float x0, x1, y0, y1; };
+using WarpRect = PixelRect;
 
 struct TileCtx {
     int tile, start, end, ix, iy;
@@ -150,20 +150,6 @@ __device__ __forceinline__ TileCtx tile_context(const BlendParams& P, float* s_c
     }
     c.rect = {x0, x1, y0, y1};
     return c;
-}
-
-// Can the triangle with matrix m cover any pixel centre inside R?  Each barycentric is evaluated at
-// the corner of R that maximises it, with the very operations of the per-pixel test; correctly
-// rounded FMAs are monotone, so a pixel inside R can never get a larger value than the corner.
-__device__ __forceinline__ bool rect_may_cover(const float* m, const WarpRect& R) {
-#pragma unroll
-    for (int k = 0; k < 3; k++) {
-        const float cx = (m[3 * k] >= 0.f) ? R.x1 : R.x0;
-        const float cy = (m[3 * k + 1] >= 0.f) ? R.y1 : R.y0;
-        const float v = fma_(m[3 * k], cx, fma_(m[3 * k + 1], cy, m[3 * k + 2]));
-        if (v < kEffZero) return false;
-    }
-    return true;
 }
 
 // Stage `n` records of the list starting at `first` into shared memory (ids + geometry).
@@ -1020,6 +1006,143 @@ __global__ void __launch_bounds__(MAXT) blend_backward_kernel(BlendParams P, Bac
     }
 }
 
+// ---- corrected gradients outside the default mode (an extension, not reference behaviour) -----------
+// The reference's recurrences (render.cu:478-497) are written for a walk over a pixel's blended fragments from
+// the last one to the first.  Its kernel does that only in the default mode: with per_pixel_sort = false it
+// visits the first `ends` list entries front to back (render.cu:659-666), and beyond 32 layers it reverses the
+// order inside each batch of 32 only (render.cu:673-693).  This kernel computes the gradient of what the forward
+// pass actually blended, for any mode and any number of layers, without storing the sequence: it walks the
+// fragments in FORWARD order and obtains the sums over the fragments behind the current one - the only thing
+// the back-to-front walk is needed for - as (final value - running prefix), the final values being the forward
+// outputs (image, final weight, depth map * final weight).
+struct PrefixState { float alpha = 1.f, sr = 0.f, sg = 0.f, sb = 0.f, oa = 0.f, zoa = 0.f; };
+struct PixelFinals { float r, g, b, depth_sum; };
+
+__device__ __forceinline__ void backward_one_prefix(const float* w, const AttrRec& a, const Bary& b, float px, float py,
+                                                    const PixelGrad& pg, const PixelFinals& fin, PrefixState& pf,
+                                                    Contrib& out) {
+    const float bw0 = b.x * w[0], bw1 = b.y * w[1], bw2 = b.z * w[2];
+    const float den = bw0 + bw1 + bw2;
+    const bool ok = !(den * den < kEffZero);
+    const float inv = rcp_fast(den);
+    QueuedFragment f;
+    f.px = px; f.py = py; f.id = 0;
+    f.bx = b.x; f.by = b.y; f.bz = b.z;
+    f.o_raw = (bw0 * a.o[0] + bw1 * a.o[1] + bw2 * a.o[2]) * inv;
+    f.cr = (bw0 * a.c[0] + bw1 * a.c[3] + bw2 * a.c[6]) * inv;
+    f.cg = (bw0 * a.c[1] + bw1 * a.c[4] + bw2 * a.c[7]) * inv;
+    f.cb = (bw0 * a.c[2] + bw1 * a.c[5] + bw2 * a.c[8]) * inv;
+    const float denz = b.x + b.y + b.z;
+    const bool okz = !(denz * denz < kEffZero);
+    const float invz = rcp_fast(denz);
+    f.z = (b.x * a.iw[0] + b.y * a.iw[1] + b.z * a.iw[2]) * invz;
+    const float o = fminf(fmaxf(f.o_raw, 0.f), kMaxOpacity);
+    const float iom = rcp_fast(1.f - o);
+    const float alpha = pf.alpha;              // transmittance in front of this fragment
+    const float ao = alpha * o;
+    pf.sr += f.cr * ao; pf.sg += f.cg * ao; pf.sb += f.cb * ao;
+    pf.oa += ao;
+    pf.zoa += f.z * ao;
+    pf.alpha = alpha * (1.f - o);
+    // sums over the fragments behind this one
+    const float sr = fin.r - pf.sr, sg = fin.g - pf.sg, sb = fin.b - pf.sb;
+    const float oa = pg.final_weight - pf.oa, zoa = fin.depth_sum - pf.zoa;
+    const float drgb_do = (f.cr * alpha - sr * iom) * pg.gr + (f.cg * alpha - sg * iom) * pg.gg +
+                          (f.cb * alpha - sb * iom) * pg.gb - pg.ga * pg.final_alpha * iom;
+    const float ddw_do = alpha - oa * iom;
+    const float dud_do = alpha * f.z - zoa * iom;
+    const bool has_w = !(pg.final_weight < kEffZero);
+    const float inv_fw = has_w ? rcp_fast(pg.final_weight) : 0.f;
+    const float d_do = drgb_do + (has_w ? (dud_do - pg.final_depth * ddw_do) * inv_fw * pg.gd : 0.f);
+    const float inv_den = ok ? inv : 0.f;
+    f.uo = d_do * inv_den;
+    f.ur = ao * pg.gr * inv_den;
+    f.ug = ao * pg.gg * inv_den;
+    f.ub = ao * pg.gb * inv_den;
+    f.uz = (has_w && okz) ? ao * pg.gd * inv_fw * invz : 0.f;
+    backward_outputs(w, a, f, out);
+}
+
+template <bool SORT, int MAXT>
+__global__ void __launch_bounds__(MAXT) blend_backward_corrected_kernel(BlendParams P, BackwardIn in,
+                                                                        float4* __restrict__ gpack) {
+    __shared__ float4 s_geo[kChunk * 4];
+    __shared__ int s_id[kChunk];
+    __shared__ float s_coord[kMaxTileCoords];
+    const TileCtx c = tile_context(P, s_coord);
+    PixelGrad pg;
+    BackState unused;
+    const int limit = load_pixel_state(c, P, in, pg, unused);
+    PixelFinals fin = {0.f, 0.f, 0.f, 0.f};
+    if (c.active) {
+        const float4 img = in.image[(size_t)c.iy * P.W + c.ix];
+        fin.r = img.x; fin.g = img.y; fin.b = img.z;
+        fin.depth_sum = (pg.final_weight < kEffZero) ? 0.f : pg.final_depth * pg.final_weight;
+    }
+    PrefixState pf;
+
+    if (SORT) {
+        float dl[kBatchLayers];
+        int jl[kBatchLayers];
+        float lastDepth = -INFINITY;
+        int lastJ = -1;
+        int remaining = limit;
+        while (true) {
+            const bool go = remaining > 0;
+            if (!__syncthreads_or(go)) break;
+            const int bs = min(kBatchLayers, remaining);
+            const int found = select_sweep(P, c, go, bs, lastDepth, lastJ, dl, jl, s_geo, s_id);
+            if (go) {
+                const int n = min(found, remaining);
+                for (int i = 0; i < n; ++i) {
+                    const int id = P.ids[jl[i]];
+                    float m[9], w[3];
+                    load_geo(P.geo, id, m, w);
+                    const Bary b = apply_bary(m, c.px, c.py);
+                    const AttrRec a = load_attr<true>(P.attr, id);
+                    Contrib ct;
+                    backward_one_prefix(w, a, b, c.px, c.py, pg, fin, pf, ct);
+                    emit_contrib(ct, gpack);
+                }
+                if (n > 0) {
+                    lastDepth = dl[n - 1];
+                    lastJ = jl[n - 1];
+                    remaining -= n;
+                } else {
+                    remaining = 0;
+                }
+            }
+        }
+    } else {
+        // the forward's walk (render.cu:578-581): list order, covered entries only, until `limit` are done
+        int processed = 0;
+        bool done = limit <= 0;
+        for (int first = c.start; first < c.end; first += kChunk) {
+            const int n = min(kChunk, c.end - first);
+            __syncthreads();
+            stage_chunk(P, first, n, s_geo, s_id);
+            __syncthreads();
+            if (!__all_sync(0xffffffffu, done)) {
+                unsigned long long mask = warp_cull(s_geo, n, c.rect);
+                while (mask) {
+                    const int r = __ffsll((long long)mask) - 1;
+                    mask &= mask - 1;
+                    if (done) continue;
+                    const float* g = reinterpret_cast<const float*>(s_geo + 4 * r);
+                    const Bary b = apply_bary(g, c.px, c.py);
+                    if (!covered(b)) continue;
+                    const AttrRec a = load_attr<true>(P.attr, s_id[r]);
+                    Contrib ct;
+                    backward_one_prefix(g + 12, a, b, c.px, c.py, pg, fin, pf, ct);
+                    emit_contrib(ct, gpack);
+                    if (++processed >= limit) done = true;
+                }
+            }
+            if (__syncthreads_and(done)) break;
+        }
+    }
+}
+
 // Packed accumulator -> the three gradient tensors of the reference (render.cu:789-791).
 __global__ void __launch_bounds__(256) unpack_gradients_kernel(const float4* __restrict__ gpack, int V,
                                                                float4* __restrict__ gV, float* __restrict__ gC,
@@ -1218,6 +1341,48 @@ int tg_blend_backward(const float* tri_geo, const float* tri_attr, const int32_t
     return backward_impl(tri_geo, tri_attr, sorted_ids, offsets, V, W, H, tw, th, per_pixel_sort, max_layers, grad_image,
                          grad_depthmap, nullptr, false, 0.f, 0.f, nullptr, image, depthmap, final_weights, ends, selection,
                          grad_vertices, grad_colors, grad_opacities, accumulate, scratch, scratch_bytes, stream);
+}
+
+int tg_blend_backward_corrected(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids,
+                                const int32_t* offsets, int V, int W, int H, int tw, int th, int per_pixel_sort,
+                                int max_layers, const float* grad_image, const float* grad_depthmap, const float* image,
+                                const float* depthmap, const float* final_weights, const int32_t* ends,
+                                float* grad_vertices, float* grad_colors, float* grad_opacities, int accumulate,
+                                void* scratch, size_t scratch_bytes, tg_stream_t stream) {
+    if (int s = blend_args(W, H, tw, th, max_layers)) return s;
+    TG_REQUIRE(V >= 0, "V < 0");
+    TG_REQUIRE(offsets && image && depthmap && final_weights && ends && grad_image && grad_depthmap, "null pointer");
+    if (V == 0) return TG_OK;
+    TG_REQUIRE(accumulate == 0 || accumulate == 1, "accumulate must be 0 or 1");
+    TG_REQUIRE(scratch && grad_vertices && grad_colors && grad_opacities, "null gradient / scratch pointer");
+    TG_REQUIRE(((uintptr_t)image & 15) == 0 && ((uintptr_t)grad_image & 15) == 0 && ((uintptr_t)tri_geo & 15) == 0 &&
+                   ((uintptr_t)tri_attr & 15) == 0 && ((uintptr_t)grad_vertices & 15) == 0 && ((uintptr_t)scratch & 15) == 0,
+               "image / grad_image / tri_geo / tri_attr / grad_vertices / scratch must be 16-byte aligned");
+    if (scratch_bytes < tg_backward_scratch_bytes(V)) {
+        tg_host::set_error("backward scratch: need %zu bytes, got %zu", tg_backward_scratch_bytes(V), scratch_bytes);
+        return TG_ERR_WORKSPACE;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    float4* gpack = (float4*)scratch;
+    float* partials = (float*)((char*)scratch + (size_t)V * 32);
+    TG_CUDA(cudaMemsetAsync(gpack, 0, (size_t)V * 32 + sizeof(float) * tg::kLossPartials, s));
+    const tg::BlendParams P = make_params(tri_geo, tri_attr, sorted_ids, offsets, W, H, tw, th, 0.f, max_layers);
+    const int tiles = P.tiles_x * ((H + th - 1) / th);
+    const int threads = ((tw * th + 31) / 32) * 32;
+    const tg::BackwardIn in = {(const float4*)grad_image, grad_depthmap, (const float4*)image, depthmap, final_weights,
+                               ends, nullptr, 0.f, partials, nullptr};
+    if (threads <= 256) {
+        if (per_pixel_sort) tg::blend_backward_corrected_kernel<true, 256><<<tiles, threads, 0, s>>>(P, in, gpack);
+        else tg::blend_backward_corrected_kernel<false, 256><<<tiles, threads, 0, s>>>(P, in, gpack);
+    } else {
+        if (per_pixel_sort) tg::blend_backward_corrected_kernel<true, 1024><<<tiles, threads, 0, s>>>(P, in, gpack);
+        else tg::blend_backward_corrected_kernel<false, 1024><<<tiles, threads, 0, s>>>(P, in, gpack);
+    }
+    TG_LAUNCH_CHECK("blend_backward_corrected_kernel");
+    tg::unpack_gradients_kernel<<<(V + 255) / 256, 256, 0, s>>>(gpack, V, (float4*)grad_vertices, grad_colors,
+                                                              grad_opacities, accumulate, partials, 0.f, nullptr);
+    TG_LAUNCH_CHECK("unpack_gradients_kernel");
+    return TG_OK;
 }
 
 int tg_blend_backward_l2(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids, const int32_t* offsets,

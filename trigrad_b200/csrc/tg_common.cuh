@@ -106,6 +106,33 @@ __device__ __forceinline__ float interp_rn(const Bary& b, float a0, float a1, fl
     return div(nom, den);
 }
 
+// NDC extent of the pixel centres of a block of pixels (a warp's 8x4 block, a whole tile).
+struct PixelRect { float x0, x1, y0, y1; };
+
+// Can the triangle with matrix m cover any pixel centre inside R?  Each barycentric is evaluated at
+// the corner of R that maximises it, with the very operations of the per-pixel test; correctly
+// rounded FMAs are monotone, so a pixel inside R can never get a larger value than the corner.
+__device__ __forceinline__ bool rect_may_cover(const float* m, const PixelRect& R) {
+#pragma unroll
+    for (int k = 0; k < 3; k++) {
+        const float cx = (m[3 * k] >= 0.f) ? R.x1 : R.x0;
+        const float cy = (m[3 * k + 1] >= 0.f) ? R.y1 : R.y0;
+        const float v = fma_(m[3 * k], cx, fma_(m[3 * k + 1], cy, m[3 * k + 2]));
+        if (v < kEffZero) return false;
+    }
+    return true;
+}
+
+// Pixel-centre rectangle of tile (tx, ty); the last row / column of tiles may be cut by the image border.
+__device__ __forceinline__ PixelRect tile_pixel_rect(int tx, int ty, int W, int H, int tw, int th) {
+    PixelRect R;
+    R.x0 = pixel_coord(tx * tw, W);
+    R.x1 = pixel_coord(min((tx + 1) * tw, W) - 1, W);
+    R.y0 = pixel_coord(ty * th, H);
+    R.y1 = pixel_coord(min((ty + 1) * th, H) - 1, H);
+    return R;
+}
+
 __device__ __forceinline__ unsigned lane_id() { return threadIdx.x & 31u; }
 
 }  // namespace tg
