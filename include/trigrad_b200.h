@@ -232,6 +232,15 @@ int tg_unpack_gradients(const void* scratch, size_t scratch_bytes, int V, float 
                         float* grad_vertices, float* grad_colors, float* grad_opacities, int accumulate,
                         tg_stream_t stream);
 
+/* Packed input layout (see TG_INPUT_PACKED): rgba [V,4] = (colors, opacities), faces [T,4] = (indices, 0).
+ * No counterpart in the reference, whose layouts are fixed by its tensor arguments (src/trigrad/wrapper.py:115-158).
+ */
+int tg_pack_inputs(const float* colors, const float* opacities, const int32_t* indices, int V, int T, float* rgba,
+                   int32_t* faces, tg_stream_t stream);
+/* tg_unpack_gradients for the packed layout: grad_vertices [V,4] and grad_rgba [V,4] = (dr, dg, db, dopacity). */
+int tg_unpack_gradients_rgba(const void* scratch, size_t scratch_bytes, int V, float loss_scale, float* loss_out,
+                             float* grad_vertices, float* grad_rgba, int accumulate, tg_stream_t stream);
+
 /* ---- forward + backward of mean((image - target)^2) in one kernel --------------------------------
  * No counterpart in the reference: tg_blend_forward followed by tg_blend_backward_l2 for the default
  * mode (per-pixel sort, 1 <= max_layers <= 32, tiles of at most 256 pixels), fused so that the values
@@ -270,6 +279,13 @@ int tg_blend_step_l2(const float* tri_geo, const float* tri_attr, const int32_t*
  *                reference's backward indexes the list by position.  Ignored beyond 65536 tiles.
  */
 #define TG_FORWARD_CULL_TILES 1u
+/*                TG_INPUT_PACKED: `indices` is [T,4] int32 (fourth word ignored) and `colors` is [V,4] float32
+ *                (r, g, b, opacity), both 16-byte aligned; `opacities` is ignored (may be NULL).  One 16-byte load
+ *                per face and per vertex attribute instead of the reference's 12-byte strides
+ *                (src/trigrad/util.h:457-573: color3 and id3 are packed 3-word types).  Results are identical;
+ *                tg_pack_inputs converts, tg_unpack_gradients_rgba returns the gradients in the same layout.
+ */
+#define TG_INPUT_PACKED 2u
 size_t tg_forward_workspace_bytes(int T, int tiles, uint32_t list_capacity);
 int tg_render_forward(const float* vertices, const int32_t* indices, const float* colors, const float* opacities,
                       int T, int W, int H, int tile_w, int tile_h, float early_stopping_threshold,

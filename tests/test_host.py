@@ -126,3 +126,37 @@ def test_two_rank_view_sharding_and_allreduce_matches_single_rank(tmp_path):
     assert torch.allclose(g.flat, g0, rtol=1e-5, atol=1e-8)
     assert torch.allclose(loss, l0, rtol=1e-6)
     assert g.points.data_ptr() == g.flat.data_ptr()      # one buffer, typed views
+
+
+def test_obj_loader_reads_triangles_quads_and_relative_indices():
+    from trigrad_b200 import loads_obj
+    text = """# a unit square as one quad, then a triangle addressed with negative and slashed indices
+mtllib ignored.mtl
+v 0 0 0
+v 1 0 0
+v 1 1 0 1.0
+v 0 1 0
+vn 0 0 1
+vt 0.5 0.5
+f 1/1/1 2/1/1 3//1 4
+v 0.5 0.5 1
+g tip
+f -1 1 2/7
+"""
+    pts, faces = loads_obj(text)
+    assert pts.dtype == np.float32 and pts.shape == (5, 3)
+    assert faces.dtype == np.int32
+    assert faces.tolist() == [[0, 1, 2], [0, 2, 3], [4, 0, 1]]
+    assert pts[2].tolist() == [1.0, 1.0, 0.0] and pts[4].tolist() == [0.5, 0.5, 1.0]
+
+
+def test_obj_loader_rejects_bad_records(tmp_path):
+    from trigrad_b200 import load_obj, loads_obj
+    with pytest.raises(ValueError):
+        loads_obj("v 0 0 0\nf 1 2 3\n")            # indices beyond the vertices read so far
+    with pytest.raises(ValueError):
+        loads_obj("v 0 0\n")
+    p = tmp_path / "tri.obj"
+    p.write_text("v 0 0 0\nv 1 0 0\nv 0 1 0\nf 1 2 3\n")
+    pts, faces = load_obj(str(p))
+    assert pts.shape == (3, 3) and faces.tolist() == [[0, 1, 2]]

@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(HERE, "libtrigrad_b200.so")
 TG_OK, TG_ERR_BAD_ARG, TG_ERR_WORKSPACE, TG_ERR_CAPACITY, TG_ERR_DEVICE_FLAG, TG_ERR_CUDA = range(6)
 TG_ACCUMULATE_PACKED = 2   # accumulate mode of the backward entry points: the sums stay in the scratch
 TG_FORWARD_CULL_TILES = 1  # flag of the forward entry points: list a (triangle, tile) pair only if it can cover a pixel
+TG_INPUT_PACKED = 2        # flag of the forward entry points: faces [T,4] int32 and colours [V,4] (r, g, b, opacity)
 GEO_WORDS = 16
 ATTR_WORDS = 24
 
@@ -52,6 +53,8 @@ SIGNATURES = {
     "tg_render_forward": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                _u32, _vp, _vp, _sz, _vp, _vp, C.c_uint, _vp]),
     "tg_unpack_gradients": (_i, [_vp, _sz, _i, _f, _vp, _vp, _vp, _vp, _i, _vp]),
+    "tg_pack_inputs": (_i, [_vp, _vp, _vp, _i, _i, _vp, _vp, _vp]),
+    "tg_unpack_gradients_rgba": (_i, [_vp, _sz, _i, _f, _vp, _vp, _vp, _i, _vp]),
     "tg_project": (_i, [_vp, _i, _vp, _vp, _vp]),
     "tg_project_backward": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp]),
     "tg_project_clip": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp]),

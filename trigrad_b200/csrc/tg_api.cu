@@ -80,7 +80,8 @@ static int build_tile_lists(const float* vertices, const int32_t* indices, const
     TG_REQUIRE(list_capacity < 0x80000000u, "list capacity must stay below 2^31");
     const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
     const int tiles = tiles_x * tiles_y;
-    TG_REQUIRE((flags & ~(unsigned)TG_FORWARD_CULL_TILES) == 0, "unknown flag");
+    TG_REQUIRE((flags & ~(unsigned)(TG_FORWARD_CULL_TILES | TG_INPUT_PACKED)) == 0, "unknown flag");
+    const bool packed = (flags & TG_INPUT_PACKED) != 0;
     // beyond 65536 tiles the tile counts go through the device-wide scan, which the culling variant does not feed
     const bool cull = (flags & TG_FORWARD_CULL_TILES) != 0 && tiles <= tg::kTileScanByLastCta;
     const ForwardWorkspace ws(workspace, T, tiles, list_capacity);
@@ -103,7 +104,7 @@ static int build_tile_lists(const float* vertices, const int32_t* indices, const
     // per-triangle records, triangle offsets, per-tile counts and tile offsets
     int st = tg_host::preprocess_scan(vertices, indices, colors, opacities, T, W, H, tw, th, tri_geo, tri_attr,
                                       ws.tri_offsets, ws.scan_scratch, ws.status, ws.tile_cursor, offsets,
-                                      ws.tile_scan_scratch, cull, s);
+                                      ws.tile_scan_scratch, cull, packed, s);
     if (st) return st;
     timer.mark();                                                    // [2] start of "per_tile_lists"
     TG_CUDA(cudaMemcpyAsync(&info_host[0], ws.tri_offsets + T, 2 * sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
@@ -111,7 +112,7 @@ static int build_tile_lists(const float* vertices, const int32_t* indices, const
     // Entries are written while K travels to the host: the kernel drops those beyond the capacity, and
     // nothing that reads them is launched before K has been checked.
     st = tg_host::emit_entries(vertices, indices, T, W, H, tw, th, ws.tri_offsets, ws.scan_scratch, ws.tile_cursor,
-                               ws.entries, list_capacity, cull ? tri_geo : nullptr, s);
+                               ws.entries, list_capacity, cull ? tri_geo : nullptr, packed, s);
     if (st) return st;
     TG_CUDA(cudaEventSynchronize(k_ready));
     const uint32_t K = info_host[0];

@@ -18,8 +18,16 @@ __device__ __forceinline__ uint32_t preprocess_triangle(int t, const float4* __r
                                                         const float* __restrict__ opacities, int W, int H, int tw,
                                                         int th, int tiles_x, int tiles_y, int4* __restrict__ tri_rects,
                                                         float4* __restrict__ tri_geo, float4* __restrict__ tri_attr,
-                                                        Rect& r, float* m_out = nullptr) {
-    int ia = indices[3 * (size_t)t], ib = indices[3 * (size_t)t + 1], ic = indices[3 * (size_t)t + 2];
+                                                        Rect& r, float* m_out = nullptr, bool packed = false) {
+    // packed inputs: faces as [T,4] int32 and colours as [V,4] (r, g, b, opacity), one 16-byte load each instead
+    // of the reference's 12-byte strides (util.h:457-573); the branch is uniform over the grid
+    int ia, ib, ic;
+    if (packed) {
+        const int4 f = reinterpret_cast<const int4*>(indices)[t];
+        ia = f.x; ib = f.y; ic = f.z;
+    } else {
+        ia = indices[3 * (size_t)t]; ib = indices[3 * (size_t)t + 1]; ic = indices[3 * (size_t)t + 2];
+    }
     float4 a = vertices[ia], b = vertices[ib], c = vertices[ic];
 
     bool ok = tile_rect(a.x, a.y, b.x, b.y, c.x, c.y, W, H, tw, th, tiles_x, tiles_y, r);
@@ -61,12 +69,21 @@ __device__ __forceinline__ uint32_t preprocess_triangle(int t, const float4* __r
     g[3] = make_float4(a.w, b.w, c.w, zlow);
 
     float4* q = tri_attr + 6 * (size_t)t;
-    const float* ca = colors + 3 * (size_t)ia;
-    const float* cb = colors + 3 * (size_t)ib;
-    const float* cc = colors + 3 * (size_t)ic;
-    q[0] = make_float4(opacities[ia], opacities[ib], opacities[ic], ca[0]);
-    q[1] = make_float4(ca[1], ca[2], cb[0], cb[1]);
-    q[2] = make_float4(cb[2], cc[0], cc[1], cc[2]);
+    float4 ra, rb, rc;   // (r, g, b, opacity) of the three vertices
+    if (packed) {
+        const float4* rgba = reinterpret_cast<const float4*>(colors);
+        ra = rgba[ia]; rb = rgba[ib]; rc = rgba[ic];
+    } else {
+        const float* ca = colors + 3 * (size_t)ia;
+        const float* cb = colors + 3 * (size_t)ib;
+        const float* cc = colors + 3 * (size_t)ic;
+        ra = make_float4(ca[0], ca[1], ca[2], opacities[ia]);
+        rb = make_float4(cb[0], cb[1], cb[2], opacities[ib]);
+        rc = make_float4(cc[0], cc[1], cc[2], opacities[ic]);
+    }
+    q[0] = make_float4(ra.w, rb.w, rc.w, ra.x);
+    q[1] = make_float4(ra.y, ra.z, rb.x, rb.y);
+    q[2] = make_float4(rb.z, rc.x, rc.y, rc.z);
     q[3] = make_float4(div(1.f, a.w), div(1.f, b.w), div(1.f, c.w), __int_as_float(ia));
     q[4] = make_float4(__int_as_float(ib), __int_as_float(ic), a.x, a.y);
     q[5] = make_float4(b.x, b.y, c.x, c.y);
@@ -310,7 +327,7 @@ __global__ void __launch_bounds__(256, 6) preprocess_count_kernel(const float4* 
                                                                int tw, int th, int tiles_x, int tiles_y,
                                                                float4* __restrict__ tri_geo, float4* __restrict__ tri_attr,
                                                                uint32_t* __restrict__ tri_offsets /*[T], CTA-local*/,
-                                                               TileBinArgs bin) {
+                                                               TileBinArgs bin, int packed) {
     __shared__ uint32_t s_warp[8];
     __shared__ uint32_t s_buf[kTileScanRound];
     uint32_t* s_loc = s_buf;                 // [257] exclusive offsets of the CTA's triangles within the CTA
@@ -323,7 +340,7 @@ __global__ void __launch_bounds__(256, 6) preprocess_count_kernel(const float4* 
     Rect r = {0, 0, 0, 0};
     float m[9];
     const uint32_t count = (t < T) ? preprocess_triangle(t, vertices, indices, colors, opacities, W, H, tw, th, tiles_x,
-                                                         tiles_y, nullptr, tri_geo, tri_attr, r, CULL ? m : nullptr)
+                                                         tiles_y, nullptr, tri_geo, tri_attr, r, CULL ? m : nullptr, packed != 0)
                                    : 0u;
     if (CULL && count) {
 #pragma unroll
@@ -508,7 +525,7 @@ __global__ void __launch_bounds__(kEmitThreads) emit_keys_kernel(const float4* _
                                                                  uint32_t capacity, HistArgs hist,
                                                                  uint32_t* __restrict__ tile_cursor,
                                                                  const uint32_t* __restrict__ part_total,
-                                                                 const float4* __restrict__ tri_geo) {
+                                                                 const float4* __restrict__ tri_geo, int packed) {
     __shared__ EmitTri s_tri[kEmitThreads];
     __shared__ EmitMat s_mat[CULL ? kEmitThreads : 1];
     __shared__ uint32_t s_off[kEmitThreads + 1];
@@ -522,7 +539,13 @@ __global__ void __launch_bounds__(kEmitThreads) emit_keys_kernel(const float4* _
         for (int i = tid; i < hist.passes * kRadix; i += kEmitThreads) s_hist[i] = 0;
     if (tid < ntri) {
         const int t = t0 + tid;
-        const int ia = indices[3 * (size_t)t], ib = indices[3 * (size_t)t + 1], ic = indices[3 * (size_t)t + 2];
+        int ia, ib, ic;
+        if (packed) {
+            const int4 f = reinterpret_cast<const int4*>(indices)[t];
+            ia = f.x; ib = f.y; ic = f.z;
+        } else {
+            ia = indices[3 * (size_t)t]; ib = indices[3 * (size_t)t + 1]; ic = indices[3 * (size_t)t + 2];
+        }
         const float4 a = vertices[ia], b = vertices[ib], c = vertices[ic];
         EmitTri e;
         e.ax = a.x; e.ay = a.y; e.az = a.z; e.bx = b.x; e.by = b.y; e.bz = b.z; e.cx = c.x; e.cy = c.y; e.cz = c.z;
@@ -578,6 +601,16 @@ __global__ void __launch_bounds__(kEmitThreads) emit_keys_kernel(const float4* _
     }
 }
 
+// Inputs in the packed layout: colours and opacities as one [V,4] array, faces as [T,4] (fourth word 0).
+__global__ void __launch_bounds__(256) pack_inputs_kernel(const float* __restrict__ colors,
+                                                          const float* __restrict__ opacities,
+                                                          const int* __restrict__ indices, int V, int T,
+                                                          float4* __restrict__ rgba, int4* __restrict__ faces) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < V) rgba[i] = make_float4(colors[3 * (size_t)i], colors[3 * (size_t)i + 1], colors[3 * (size_t)i + 2], opacities[i]);
+    if (i < T) faces[i] = make_int4(indices[3 * (size_t)i], indices[3 * (size_t)i + 1], indices[3 * (size_t)i + 2], 0);
+}
+
 // ================================================================================================
 // Stage 5: tile ranges from the sorted keys.  Thread i looks at the boundary before entry i.
 __global__ void __launch_bounds__(256) tile_ranges_kernel(const uint64_t* __restrict__ keys, uint32_t n, int tiles,
@@ -627,7 +660,7 @@ size_t preprocess_scan_scratch_bytes(int T) { return 8 + 4 * ((size_t)(T > 0 ? (
 int preprocess_scan(const float* vertices, const int32_t* indices, const float* colors, const float* opacities, int T,
                     int W, int H, int tw, int th, float* tri_geo, float* tri_attr, uint32_t* tri_offsets, void* scratch,
                     uint32_t* status, uint32_t* tile_cursor, int32_t* offsets, void* tile_scan_scratch, bool cull,
-                    cudaStream_t stream) {
+                    bool packed, cudaStream_t stream) {
     if (int s = check_dims_internal(T, W, H, tw, th)) return s;
     TG_REQUIRE(tri_offsets && scratch && status && tile_cursor && offsets, "null pointer");
     const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
@@ -637,9 +670,11 @@ int preprocess_scan(const float* vertices, const int32_t* indices, const float* 
         TG_CUDA(cudaMemsetAsync(offsets, 0, sizeof(int32_t) * ((size_t)tiles + 1), stream));
         return TG_OK;
     }
-    TG_REQUIRE(vertices && indices && colors && opacities && tri_geo && tri_attr, "null pointer");
+    TG_REQUIRE(vertices && indices && colors && (packed || opacities) && tri_geo && tri_attr, "null pointer");
     TG_REQUIRE(((uintptr_t)vertices & 15) == 0 && ((uintptr_t)tri_geo & 15) == 0 && ((uintptr_t)tri_attr & 15) == 0,
                "vertices / tri_geo / tri_attr must be 16-byte aligned");
+    TG_REQUIRE(!packed || ((((uintptr_t)indices | (uintptr_t)colors) & 15) == 0),
+               "packed faces [T,4] and colours [V,4] must be 16-byte aligned");
     const bool by_last_cta = tiles <= tg::kTileScanByLastCta;
     TG_REQUIRE(by_last_cta || tile_scan_scratch, "null tile scan scratch");
     const tg::TileBinArgs bin = {tile_cursor, offsets, (uint32_t*)scratch, tiles, by_last_cta ? 1 : 0,
@@ -648,11 +683,11 @@ int preprocess_scan(const float* vertices, const int32_t* indices, const float* 
     if (cull)
         tg::preprocess_count_kernel<true><<<(T + 255) / 256, 256, 0, stream>>>(
             (const float4*)vertices, indices, colors, opacities, T, W, H, tw, th, tiles_x, tiles_y, (float4*)tri_geo,
-            (float4*)tri_attr, tri_offsets, bin);
+            (float4*)tri_attr, tri_offsets, bin, packed ? 1 : 0);
     else
         tg::preprocess_count_kernel<false><<<(T + 255) / 256, 256, 0, stream>>>(
             (const float4*)vertices, indices, colors, opacities, T, W, H, tw, th, tiles_x, tiles_y, (float4*)tri_geo,
-            (float4*)tri_attr, tri_offsets, bin);
+            (float4*)tri_attr, tri_offsets, bin, packed ? 1 : 0);
     TG_LAUNCH_CHECK("preprocess_count_kernel");
     if (!by_last_cta) {
         // counts -> offsets by the device-wide scan, then the cursors start at the offsets
@@ -676,7 +711,7 @@ int emit_keys(const float* vertices, const int32_t* indices, int T, int W, int H
     const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
     tg::emit_keys_kernel<false, false><<<(T + tg::kEmitThreads - 1) / tg::kEmitThreads, tg::kEmitThreads, 0, stream>>>(
         (const float4*)vertices, indices, T, W, H, tw, th, tiles_x, tiles_y, tri_offsets, keys, ids, capacity, hist,
-        nullptr, nullptr, nullptr);
+        nullptr, nullptr, nullptr, 0);
     TG_LAUNCH_CHECK("emit_keys_kernel");
     return TG_OK;
 }
@@ -685,7 +720,7 @@ int emit_keys(const float* vertices, const int32_t* indices, int T, int W, int H
 // `tri_offsets` and `scan_scratch` as preprocess_scan left them (CTA-local offsets, CTA totals).
 int emit_entries(const float* vertices, const int32_t* indices, int T, int W, int H, int tw, int th,
                  const uint32_t* tri_offsets, const void* scan_scratch, uint32_t* tile_cursor, uint64_t* entries,
-                 uint32_t capacity, const float* tri_geo_for_cull, cudaStream_t stream) {
+                 uint32_t capacity, const float* tri_geo_for_cull, bool packed, cudaStream_t stream) {
     if (int s = check_dims_internal(T, W, H, tw, th)) return s;
     if (T == 0 || capacity == 0) return TG_OK;
     TG_REQUIRE(vertices && indices && tri_offsets && scan_scratch && tile_cursor && entries, "null pointer");
@@ -695,11 +730,11 @@ int emit_entries(const float* vertices, const int32_t* indices, int T, int W, in
     if (tri_geo_for_cull)
         tg::emit_keys_kernel<true, true><<<grid, tg::kEmitThreads, 0, stream>>>(
             (const float4*)vertices, indices, T, W, H, tw, th, tiles_x, tiles_y, tri_offsets, entries, nullptr, capacity,
-            none, tile_cursor, (const uint32_t*)scan_scratch + 2, (const float4*)tri_geo_for_cull);
+            none, tile_cursor, (const uint32_t*)scan_scratch + 2, (const float4*)tri_geo_for_cull, packed ? 1 : 0);
     else
         tg::emit_keys_kernel<true, false><<<grid, tg::kEmitThreads, 0, stream>>>(
             (const float4*)vertices, indices, T, W, H, tw, th, tiles_x, tiles_y, tri_offsets, entries, nullptr, capacity,
-            none, tile_cursor, (const uint32_t*)scan_scratch + 2, nullptr);
+            none, tile_cursor, (const uint32_t*)scan_scratch + 2, nullptr, packed ? 1 : 0);
     TG_LAUNCH_CHECK("emit_entries_kernel");
     return TG_OK;
 }
@@ -833,6 +868,19 @@ int tg_scan_static(const uint32_t* in, uint32_t* out, int n, uint32_t* status, t
     tg::scan_kernel<<<parts, tg::kScanThreads, 0, s>>>(in, out, n, parts, (uint32_t*)scratch,
                                                       (uint64_t*)((char*)scratch + 256), status);
     TG_LAUNCH_CHECK("scan_kernel (static scratch)");
+    return TG_OK;
+}
+
+int tg_pack_inputs(const float* colors, const float* opacities, const int32_t* indices, int V, int T, float* rgba,
+                   int32_t* faces, tg_stream_t stream) {
+    TG_REQUIRE(V >= 0 && T >= 0, "negative size");
+    if (V == 0 && T == 0) return TG_OK;
+    TG_REQUIRE((V == 0 || (colors && opacities && rgba)) && (T == 0 || (indices && faces)), "null pointer");
+    TG_REQUIRE((((uintptr_t)rgba | (uintptr_t)faces) & 15) == 0, "rgba / faces must be 16-byte aligned");
+    const int n = V > T ? V : T;
+    tg::pack_inputs_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(colors, opacities, indices, V, T,
+                                                                              (float4*)rgba, (int4*)faces);
+    TG_LAUNCH_CHECK("pack_inputs_kernel");
     return TG_OK;
 }
 

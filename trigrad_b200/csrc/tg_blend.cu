@@ -1171,6 +1171,30 @@ __global__ void __launch_bounds__(256) unpack_gradients_kernel(const float4* __r
     gO[v] = o;
 }
 
+// The same for the packed input layout: colour and opacity gradients as one [V,4] array (dr, dg, db, dopacity).
+__global__ void __launch_bounds__(256) unpack_gradients_rgba_kernel(const float4* __restrict__ gpack, int V,
+                                                                    float4* __restrict__ gV, float4* __restrict__ gRGBA,
+                                                                    int accumulate, const float* __restrict__ l2_partials,
+                                                                    float l2_loss_scale, float* __restrict__ l2_loss_out) {
+    if (l2_loss_out && blockIdx.x == 0 && threadIdx.x < 32) {
+        float x = l2_partials[threadIdx.x] + l2_partials[threadIdx.x + 32];
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) x += __shfl_xor_sync(0xffffffffu, x, d);
+        if (threadIdx.x == 0) *l2_loss_out = (accumulate ? *l2_loss_out : 0.f) + x * l2_loss_scale;
+    }
+    const int v = blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= V) return;
+    const float4 a = gpack[2 * (size_t)v], b = gpack[2 * (size_t)v + 1];
+    float4 ov = make_float4(a.x, a.y, 0.f, a.z), oc = make_float4(b.x, b.y, b.z, a.w);
+    if (accumulate) {
+        const float4 pv = gV[v], pc = gRGBA[v];
+        ov.x += pv.x; ov.y += pv.y; ov.z = pv.z; ov.w += pv.w;
+        oc.x += pc.x; oc.y += pc.y; oc.z += pc.z; oc.w += pc.w;
+    }
+    gV[v] = ov;
+    gRGBA[v] = oc;
+}
+
 }  // namespace tg
 
 extern "C" {
@@ -1329,6 +1353,24 @@ int tg_unpack_gradients(const void* scratch, size_t scratch_bytes, int V, float 
         (const float4*)scratch, V, (float4*)grad_vertices, grad_colors, grad_opacities, accumulate, partials, loss_scale,
         loss_out);
     TG_LAUNCH_CHECK("unpack_gradients_kernel");
+    return TG_OK;
+}
+
+int tg_unpack_gradients_rgba(const void* scratch, size_t scratch_bytes, int V, float loss_scale, float* loss_out,
+                             float* grad_vertices, float* grad_rgba, int accumulate, tg_stream_t stream) {
+    TG_REQUIRE(V > 0, "V must be positive");
+    TG_REQUIRE(scratch && grad_vertices && grad_rgba, "null pointer");
+    TG_REQUIRE(accumulate == 0 || accumulate == 1, "accumulate must be 0 or 1");
+    TG_REQUIRE((((uintptr_t)grad_vertices | (uintptr_t)grad_rgba | (uintptr_t)scratch) & 15) == 0,
+               "grad_vertices / grad_rgba / scratch must be 16-byte aligned");
+    if (scratch_bytes < tg_backward_scratch_bytes(V)) {
+        tg_host::set_error("backward scratch: need %zu bytes, got %zu", tg_backward_scratch_bytes(V), scratch_bytes);
+        return TG_ERR_WORKSPACE;
+    }
+    const float* partials = (const float*)((const char*)scratch + (size_t)V * 32);
+    tg::unpack_gradients_rgba_kernel<<<(V + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+        (const float4*)scratch, V, (float4*)grad_vertices, (float4*)grad_rgba, accumulate, partials, loss_scale, loss_out);
+    TG_LAUNCH_CHECK("unpack_gradients_rgba_kernel");
     return TG_OK;
 }
 

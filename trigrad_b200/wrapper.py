@@ -109,13 +109,14 @@ def _ptr(t: torch.Tensor | None):
 
 def forward_native(vertices, indices, colors, opacities, width, height, tile_width, tile_height,
                    early_stopping_threshold, record_timing, per_pixel_sort, max_layers, save_selection=True,
-                   cull_tiles=False):
+                   cull_tiles=False, packed_inputs=False):
     """Run the whole forward path.  Returns the public outputs and the state saved for backward.
 
     ``save_selection=False`` (or planes larger than ``SELECTION_MAX_BYTES``) skips the per-pixel record of the
     blended fragment ids; the backward then searches the tile lists again.  ``cull_tiles`` lists a (triangle, tile)
     pair only if the triangle can cover a pixel centre of the tile (``TG_FORWARD_CULL_TILES``): same image, same
-    gradients, shorter lists than the reference's."""
+    gradients, shorter lists than the reference's.  ``packed_inputs``: ``indices`` is ``[T,4]`` int32 and ``colors`` is
+    ``[V,4]`` (r, g, b, opacity), ``opacities`` is None (``TG_INPUT_PACKED``)."""
     lib = N.lib()
     device = vertices.device
     T = indices.shape[0]
@@ -148,7 +149,9 @@ def forward_native(vertices, indices, colors, opacities, width, height, tile_wid
                 tile_height, float(early_stopping_threshold), int(bool(per_pixel_sort)), int(max_layers),
                 _ptr(image), _ptr(depthmap), _ptr(final_weights), _ptr(ends), _ptr(selection), _ptr(tri_geo), _ptr(tri_attr),
                 _ptr(sorted_ids), cap, _ptr(offsets), C.c_void_p(base), ws.numel() - (base - ws.data_ptr()),
-                C.c_void_p(info.data_ptr()), stage_ms, N.TG_FORWARD_CULL_TILES if cull_tiles else 0, C.c_void_p(stream))
+                C.c_void_p(info.data_ptr()), stage_ms,
+                (N.TG_FORWARD_CULL_TILES if cull_tiles else 0) | (N.TG_INPUT_PACKED if packed_inputs else 0),
+                C.c_void_p(stream))
             K = int(info[0])
             if status == N.TG_ERR_CAPACITY:
                 cap = int(K * 1.25) + 1024
