@@ -272,7 +272,7 @@ def test_live_reference_leg(make, sort):
                                     image_rel_l2=img_err, grad_rel_l2_vs_reference_build=errs,
                                     reference_build_vs_fp64=ref_noise, product_vs_fp64=own_noise)) + "\n")
     for name, err in errs.items():
-        bar = max(1e-4, 1.5 * ref_noise[name])
+        bar = max(1e-4, 2.0 * ref_noise[name])
         assert err <= bar, f"grad_{name} against the reference's own build: relative L2 error {err:.3e} (bar {bar:.3e})"
         assert own_noise[name] <= bar, f"grad_{name} against exact arithmetic: {own_noise[name]:.3e} (bar {bar:.3e})"
 

@@ -480,31 +480,20 @@ __device__ float tile_key(const TriXYZ& v, const Plane& pl, int tx, int ty, int 
         md0 = fminf(md0, plane_depth(pl, v.bx, v.by));
         return fminf(md0, plane_depth(pl, v.cx, v.cy));
     }
-    // A pass whose half-plane contains the whole bounding box returns its input unchanged (every vertex is kept, no
-    // edge crosses the boundary) and is skipped: most triangles only straddle one or two sides of a tile.  The test
-    // uses the very differences the pass would form, so the result is the same bit for bit.
-    const bool cut0 = !(sub(lox, xmin) >= 0.f), cut1 = !(sub(xmax, hix) >= 0.f);
-    const bool cut2 = !(sub(loy, ymin) >= 0.f), cut3 = !(sub(ymax, hiy) >= 0.f);
-    float2 pa[8], pb[8];
-    pa[0] = make_float2(v.ax, v.ay);
-    pa[1] = make_float2(v.bx, v.by);
-    pa[2] = make_float2(v.cx, v.cy);
-    int n = 3;
-    bool in_a = true;        // which of the two buffers holds the polygon (both are named statically in every call)
-#define TG_CLIP_STEP(AXIS, BOUND)                                                      \
-    {                                                                                  \
-        n = in_a ? clip_pass<AXIS>(pa, n, pb, BOUND) : clip_pass<AXIS>(pb, n, pa, BOUND); \
-        if (n <= 0) return 1e30f;                                                      \
-        in_a = !in_a;                                                                  \
-    }
-    if (cut0) TG_CLIP_STEP(0, xmin)
-    if (cut1) TG_CLIP_STEP(1, xmax)
-    if (cut2) TG_CLIP_STEP(2, ymin)
-    if (cut3) TG_CLIP_STEP(3, ymax)
-#undef TG_CLIP_STEP
+    float2 poly[8], buf[8];
+    poly[0] = make_float2(v.ax, v.ay);
+    poly[1] = make_float2(v.bx, v.by);
+    poly[2] = make_float2(v.cx, v.cy);
+    int n = clip_pass<0>(poly, 3, buf, xmin);
+    if (n <= 0) return 1e30f;
+    n = clip_pass<1>(buf, n, poly, xmax);
+    if (n <= 0) return 1e30f;
+    n = clip_pass<2>(poly, n, buf, ymin);
+    if (n <= 0) return 1e30f;
+    n = clip_pass<3>(buf, n, poly, ymax);
+    if (n <= 0) return 1e30f;
     float md = FLT_MAX;
-    if (in_a) { for (int i = 0; i < n; i++) md = fminf(md, plane_depth(pl, pa[i].x, pa[i].y)); }
-    else { for (int i = 0; i < n; i++) md = fminf(md, plane_depth(pl, pb[i].x, pb[i].y)); }
+    for (int i = 0; i < n; i++) md = fminf(md, plane_depth(pl, poly[i].x, poly[i].y));
     return md;
 }
 
