@@ -15,6 +15,7 @@ struct ForwardWorkspace {
     void* tile_scan_scratch;   // device-wide scan of the tile counts (only beyond kTileScanByLastCta tiles)
     uint32_t* long_list;       // work lists of the per-tile sort; only their six head words need clearing
     uint32_t* tile_cursor;     // [tiles]
+    uint32_t* tile_order;      // [tiles] launch order of the compositing kernel (valid when status[1] != 0)
     char* clear_end;
     size_t total;
 
@@ -33,6 +34,7 @@ struct ForwardWorkspace {
         tile_cursor = (uint32_t*)take(sizeof(uint32_t) * (size_t)tiles);
         long_list = (uint32_t*)take(tg_host::tile_sort_scratch_bytes(tiles));
         clear_end = (char*)long_list + 6 * sizeof(uint32_t);
+        tile_order = (uint32_t*)take(sizeof(uint32_t) * (size_t)tiles);
         total = off;
     }
 };
@@ -71,7 +73,7 @@ static int build_tile_lists(const float* vertices, const int32_t* indices, const
                             int T, int W, int H, int tw, int th, int max_layers, float* tri_geo, float* tri_attr,
                             int32_t* sorted_ids, uint32_t list_capacity, int32_t* offsets, void* workspace,
                             size_t workspace_bytes, uint32_t* info_host, unsigned flags, StageTimer& timer,
-                            uint32_t** device_status, cudaStream_t s) {
+                            uint32_t** device_status, const uint32_t** tile_order_out, cudaStream_t s) {
     TG_REQUIRE(T >= 0 && W > 0 && H > 0 && tw > 0 && th > 0, "sizes");
     TG_REQUIRE(tw * th <= 1024, "tile_width * tile_height must be <= 1024");
     TG_REQUIRE(max_layers >= 1, "max_layers must be >= 1");
@@ -86,6 +88,7 @@ static int build_tile_lists(const float* vertices, const int32_t* indices, const
     const bool cull = (flags & TG_FORWARD_CULL_TILES) != 0 && tiles <= tg::kTileScanByLastCta;
     const ForwardWorkspace ws(workspace, T, tiles, list_capacity);
     *device_status = ws.status;
+    *tile_order_out = ws.tile_order;
     if (workspace_bytes < ws.total) {
         tg_host::set_error("forward workspace: need %zu bytes, got %zu", ws.total, workspace_bytes);
         return TG_ERR_WORKSPACE;
@@ -104,7 +107,7 @@ static int build_tile_lists(const float* vertices, const int32_t* indices, const
     // per-triangle records, triangle offsets, per-tile counts and tile offsets
     int st = tg_host::preprocess_scan(vertices, indices, colors, opacities, T, W, H, tw, th, tri_geo, tri_attr,
                                       ws.tri_offsets, ws.scan_scratch, ws.status, ws.tile_cursor, offsets,
-                                      ws.tile_scan_scratch, cull, packed, s);
+                                      ws.tile_scan_scratch, cull, packed, ws.tile_order, ws.status + 1, s);
     if (st) return st;
     timer.mark();                                                    // [2] start of "per_tile_lists"
     TG_CUDA(cudaMemcpyAsync(&info_host[0], ws.tri_offsets + T, 2 * sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
@@ -164,12 +167,15 @@ int tg_render_forward(const float* vertices, const int32_t* indices, const float
     cudaStream_t s = (cudaStream_t)stream;
     StageTimer timer(stage_ms_host != nullptr, s);
     uint32_t* device_status = nullptr;
+    const uint32_t* tile_order = nullptr;
     int st = build_tile_lists(vertices, indices, colors, opacities, T, W, H, tw, th, max_layers, tri_geo, tri_attr,
-                              sorted_ids, list_capacity, offsets, workspace, workspace_bytes, info_host, flags, timer, &device_status, s);
+                              sorted_ids, list_capacity, offsets, workspace, workspace_bytes, info_host, flags, timer, &device_status, &tile_order, s);
     if (st) return st;
     timer.mark();                                                    // [4] start of "rasterization"
+    tg_host::set_tile_order(tile_order, device_status + 1);
     st = tg_blend_forward(tri_geo, tri_attr, sorted_ids, offsets, W, H, tw, th, thr, per_pixel_sort, max_layers, image,
                           depthmap, final_weights, ends, selection, stream);
+    tg_host::set_tile_order(nullptr, nullptr);
     if (st) return st;
     timer.mark();                                                    // [5] end
     // device error word: valid on the host once the stream has been synchronised
@@ -190,13 +196,16 @@ int tg_render_step_l2(const float* vertices, const int32_t* indices, const float
     cudaStream_t s = (cudaStream_t)stream;
     StageTimer timer(stage_ms_host != nullptr, s);
     uint32_t* device_status = nullptr;
+    const uint32_t* tile_order = nullptr;
     int st = build_tile_lists(vertices, indices, colors, opacities, T, W, H, tw, th, max_layers, tri_geo, tri_attr,
-                              sorted_ids, list_capacity, offsets, workspace, workspace_bytes, info_host, flags, timer, &device_status, s);
+                              sorted_ids, list_capacity, offsets, workspace, workspace_bytes, info_host, flags, timer, &device_status, &tile_order, s);
     if (st) return st;
     timer.mark();                                                    // [4] start of "rasterization" (here: forward + backward)
+    tg_host::set_tile_order(tile_order, device_status + 1);
     st = tg_blend_step_l2(tri_geo, tri_attr, sorted_ids, offsets, V, W, H, tw, th, thr, max_layers, target, grad_scale,
                           loss_scale, loss_out, image, depthmap, final_weights, ends, grad_vertices, grad_colors,
                           grad_opacities, accumulate, scratch, scratch_bytes, stream);
+    tg_host::set_tile_order(nullptr, nullptr);
     if (st) return st;
     timer.mark();                                                    // [5] end
     TG_CUDA(cudaMemcpyAsync(&info_host[2], device_status, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));

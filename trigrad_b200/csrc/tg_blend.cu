@@ -33,7 +33,16 @@ struct BlendParams {
     int W, H, tw, th, tiles_x;
     float thr;
     int max_layers;
+    // Optional launch order of the tiles (longest lists first, so that no heavy tile starts late): CTA b handles tile
+    // order[b] when *order_valid is non-zero, tile b otherwise.  Both null for the stage entry points.
+    const uint32_t* order;
+    const uint32_t* order_valid;
 };
+
+__device__ __forceinline__ int tile_of_block(const BlendParams& P) {
+    if (P.order != nullptr && *P.order_valid != 0u) return (int)P.order[blockIdx.x];
+    return (int)blockIdx.x;
+}
 
 struct PixelAcc {
     float alpha = 1.f, r = 0.f, g = 0.f, b = 0.f, depth = 0.f, weight = 0.f;
@@ -117,7 +126,7 @@ constexpr int kMaxTileCoords = 1026;
 
 __device__ __forceinline__ TileCtx tile_context(const BlendParams& P, float* s_coord) {
     TileCtx c;
-    c.tile = blockIdx.x;
+    c.tile = tile_of_block(P);
     const int tx = c.tile % P.tiles_x, ty = c.tile / P.tiles_x;
     for (int i = threadIdx.x; i < P.tw + P.th; i += blockDim.x)
         s_coord[i] = (i < P.tw) ? pixel_coord(tx * P.tw + i, P.W) : pixel_coord(ty * P.th + (i - P.tw), P.H);
@@ -248,9 +257,10 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 256 ? 5 : 1) blend_forward_kerne
     __shared__ float4 s_geo[kChunk * 4];
     __shared__ int s_id[kChunk];
     __shared__ float s_coord[kMaxTileCoords];
-    if (P.offsets[blockIdx.x] == P.offsets[blockIdx.x + 1]) {
+    const int this_tile = tile_of_block(P);
+    if (P.offsets[this_tile] == P.offsets[this_tile + 1]) {
         // a tile without entries: background, and no need for pixel-centre coordinates (any pixel order will do)
-        const int tx = blockIdx.x % P.tiles_x, ty = blockIdx.x / P.tiles_x;
+        const int tx = this_tile % P.tiles_x, ty = this_tile / P.tiles_x;
         const int ix = tx * P.tw + (int)threadIdx.x % P.tw, iy = ty * P.th + (int)threadIdx.x / P.tw;
         if ((int)threadIdx.x < P.tw * P.th && ix < P.W && iy < P.H) {
             const size_t index = (size_t)iy * P.W + ix;
@@ -1212,12 +1222,25 @@ static tg::BlendParams make_params(const float* tri_geo, const float* tri_attr, 
     P.geo = (const float4*)tri_geo; P.attr = (const float4*)tri_attr; P.ids = sorted_ids; P.offsets = offsets;
     P.W = W; P.H = H; P.tw = tw; P.th = th; P.tiles_x = (W + tw - 1) / tw;
     P.thr = thr; P.max_layers = max_layers;
+    P.order = nullptr; P.order_valid = nullptr;
     return P;
 }
 
 int tg_selection_planes(int per_pixel_sort, int max_layers) {
     return (per_pixel_sort && max_layers >= 1 && max_layers <= tg::kBatchLayers) ? max_layers : 0;
 }
+
+}  // extern "C"
+
+namespace tg_host {
+// Set by tg_render_forward / tg_render_step_l2 around their compositing call (same thread): the tile order the
+// binning kernel left in the workspace.  The stage entry points run with the identity order.
+static thread_local const uint32_t* g_tile_order = nullptr;
+static thread_local const uint32_t* g_tile_order_valid = nullptr;
+void set_tile_order(const uint32_t* order, const uint32_t* valid) { g_tile_order = order; g_tile_order_valid = valid; }
+}  // namespace tg_host
+
+extern "C" {
 
 int tg_blend_forward(const float* tri_geo, const float* tri_attr, const int32_t* sorted_ids, const int32_t* offsets,
                      int W, int H, int tw, int th, float thr, int per_pixel_sort, int max_layers, float* image,
@@ -1227,7 +1250,8 @@ int tg_blend_forward(const float* tri_geo, const float* tri_attr, const int32_t*
     TG_REQUIRE(((uintptr_t)image & 15) == 0 && ((uintptr_t)tri_geo & 15) == 0 && ((uintptr_t)tri_attr & 15) == 0,
                "image / tri_geo / tri_attr must be 16-byte aligned");
     if (tg_selection_planes(per_pixel_sort, max_layers) == 0) selection = nullptr;
-    const tg::BlendParams P = make_params(tri_geo, tri_attr, sorted_ids, offsets, W, H, tw, th, thr, max_layers);
+    tg::BlendParams P = make_params(tri_geo, tri_attr, sorted_ids, offsets, W, H, tw, th, thr, max_layers);
+    P.order = tg_host::g_tile_order; P.order_valid = tg_host::g_tile_order_valid;
     const int tiles = P.tiles_x * ((H + th - 1) / th);
     const int threads = ((tw * th + 31) / 32) * 32;
     cudaStream_t s = (cudaStream_t)stream;
@@ -1323,7 +1347,8 @@ int tg_blend_step_l2(const float* tri_geo, const float* tri_attr, const int32_t*
     float4* gpack = (float4*)scratch;
     float* partials = (float*)((char*)scratch + (size_t)V * 32);
     if (!packed) TG_CUDA(cudaMemsetAsync(gpack, 0, (size_t)V * 32 + sizeof(float) * tg::kLossPartials, s));
-    const tg::BlendParams P = make_params(tri_geo, tri_attr, sorted_ids, offsets, W, H, tw, th, thr, max_layers);
+    tg::BlendParams P = make_params(tri_geo, tri_attr, sorted_ids, offsets, W, H, tw, th, thr, max_layers);
+    P.order = tg_host::g_tile_order; P.order_valid = tg_host::g_tile_order_valid;
     const int tiles = P.tiles_x * ((H + th - 1) / th);
     const int threads = ((tw * th + 31) / 32) * 32;
     tg::blend_step_l2_kernel<256><<<tiles, threads, 0, s>>>(P, (float4*)image, depthmap, final_weights, ends,

@@ -93,10 +93,11 @@ size_t preprocess_scan_scratch_bytes(int T);
 int preprocess_scan(const float* vertices, const int32_t* indices, const float* colors, const float* opacities, int T,
                     int W, int H, int tw, int th, float* tri_geo, float* tri_attr, uint32_t* tri_offsets, void* scratch,
                     uint32_t* status, uint32_t* tile_cursor, int32_t* offsets, void* tile_scan_scratch, bool cull,
-                    bool packed, cudaStream_t stream);
+                    bool packed, uint32_t* tile_order, uint32_t* tile_order_valid, cudaStream_t stream);
 int emit_entries(const float* vertices, const int32_t* indices, int T, int W, int H, int tw, int th,
                  const uint32_t* tri_offsets, const void* scan_scratch, uint32_t* tile_cursor, uint64_t* entries,
                  uint32_t capacity, const float* tri_geo_for_cull, bool packed, cudaStream_t stream);
+void set_tile_order(const uint32_t* order, const uint32_t* valid);
 size_t tile_sort_scratch_bytes(int tiles);
 int sort_tile_lists(uint64_t* entries, const int32_t* offsets, int tiles, int32_t* sorted_ids, uint32_t* lists,
                     bool scratch_prepared, bool write_back, uint32_t longest, cudaStream_t stream);
