@@ -8,7 +8,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libtrigrad_b200.so")
+# TRIGRAD_B200_LIB names another build of the same ABI (comparing two builds of the kernels in one session)
+LIB_PATH = os.environ.get("TRIGRAD_B200_LIB") or os.path.join(HERE, "libtrigrad_b200.so")
 
 TG_OK, TG_ERR_BAD_ARG, TG_ERR_WORKSPACE, TG_ERR_CAPACITY, TG_ERR_DEVICE_FLAG, TG_ERR_CUDA = range(6)
 TG_ACCUMULATE_PACKED = 2   # accumulate mode of the backward entry points: the sums stay in the scratch

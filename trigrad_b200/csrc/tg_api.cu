@@ -1,7 +1,12 @@
 // Whole forward path behind one C entry point (stages 1-6 sequenced on the caller's stream).
+#include <atomic>
+#include <chrono>
+
 #include "tg_radix.cuh"
 
 namespace {
+
+constexpr uint32_t kNotArrived = 0xffffffffu;
 
 inline size_t align_up(size_t x, size_t a = 256) { return (x + a - 1) / a * a; }
 
@@ -15,7 +20,7 @@ struct ForwardWorkspace {
     void* tile_scan_scratch;   // device-wide scan of the tile counts (only beyond kTileScanByLastCta tiles)
     uint32_t* long_list;       // work lists of the per-tile sort; only their six head words need clearing
     uint32_t* tile_cursor;     // [tiles]
-    uint32_t* tile_order;      // [tiles] launch order of the compositing kernel (valid when status[1] != 0)
+    uint32_t* tile_order;      // [tiles] launch order of the compositing kernel, when the binning kernel wrote one
     char* clear_end;
     size_t total;
 
@@ -88,12 +93,12 @@ static int build_tile_lists(const float* vertices, const int32_t* indices, const
     const bool cull = (flags & TG_FORWARD_CULL_TILES) != 0 && tiles <= tg::kTileScanByLastCta;
     const ForwardWorkspace ws(workspace, T, tiles, list_capacity);
     *device_status = ws.status;
-    *tile_order_out = ws.tile_order;
+    *tile_order_out = nullptr;
     if (workspace_bytes < ws.total) {
         tg_host::set_error("forward workspace: need %zu bytes, got %zu", ws.total, workspace_bytes);
         return TG_ERR_WORKSPACE;
     }
-    info_host[0] = 0;
+    info_host[0] = kNotArrived;     // K < 2^31, so this value means "the copy of K has not landed yet"
     info_host[1] = 0;
     info_host[2] = 0;
     TG_REQUIRE(list_capacity == 0 || sorted_ids != nullptr, "null sorted_ids");
@@ -107,7 +112,7 @@ static int build_tile_lists(const float* vertices, const int32_t* indices, const
     // per-triangle records, triangle offsets, per-tile counts and tile offsets
     int st = tg_host::preprocess_scan(vertices, indices, colors, opacities, T, W, H, tw, th, tri_geo, tri_attr,
                                       ws.tri_offsets, ws.scan_scratch, ws.status, ws.tile_cursor, offsets,
-                                      ws.tile_scan_scratch, cull, packed, ws.tile_order, ws.status + 1, s);
+                                      ws.tile_scan_scratch, cull, packed, ws.tile_order, s);
     if (st) return st;
     timer.mark();                                                    // [2] start of "per_tile_lists"
     TG_CUDA(cudaMemcpyAsync(&info_host[0], ws.tri_offsets + T, 2 * sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
@@ -117,8 +122,32 @@ static int build_tile_lists(const float* vertices, const int32_t* indices, const
     st = tg_host::emit_entries(vertices, indices, T, W, H, tw, th, ws.tri_offsets, ws.scan_scratch, ws.tile_cursor,
                                ws.entries, list_capacity, cull ? tri_geo : nullptr, packed, s);
     if (st) return st;
-    TG_CUDA(cudaEventSynchronize(k_ready));
+    // K arrives by an 8-byte copy into (preferably pinned) host memory.  Watching the word itself is quicker than
+    // waking up from cudaEventSynchronize (the compositing kernels cannot be launched before K is known, so every
+    // microsecond here is an idle GPU once the entry writer has finished); after a bounded while, or for pageable
+    // memory where the copy has completed by now anyway, the event is waited for in the ordinary way, which also
+    // surfaces any error of the kernels before it.
+    {
+        const volatile uint32_t* watched = info_host;
+        const auto t0 = std::chrono::steady_clock::now();
+        for (uint32_t spins = 1; *watched == kNotArrived; ++spins) {
+#if defined(__x86_64__)
+            __builtin_ia32_pause();
+#endif
+            if ((spins & 0xfffu) == 0 && std::chrono::steady_clock::now() - t0 > std::chrono::milliseconds(200)) break;
+        }
+        std::atomic_thread_fence(std::memory_order_acquire);
+        if (info_host[0] == kNotArrived) TG_CUDA(cudaEventSynchronize(k_ready));
+    }
+    if (info_host[0] == kNotArrived) {
+        tg_host::set_error("the number of list entries never reached the host");
+        return TG_ERR_CUDA;
+    }
     const uint32_t K = info_host[0];
+    // the longest-list word carries "a launch order of the tiles was written" in its top bit
+    const bool have_order = (info_host[1] & tg::kOrderWrittenBit) != 0 && info_host[1] != UINT32_MAX;
+    if (info_host[1] != UINT32_MAX) info_host[1] &= ~tg::kOrderWrittenBit;
+    *tile_order_out = have_order ? ws.tile_order : nullptr;
     if (K > list_capacity) {
         tg_host::set_error("K = %u exceeds the list capacity %u", K, list_capacity);
         return TG_ERR_CAPACITY;
@@ -172,10 +201,10 @@ int tg_render_forward(const float* vertices, const int32_t* indices, const float
                               sorted_ids, list_capacity, offsets, workspace, workspace_bytes, info_host, flags, timer, &device_status, &tile_order, s);
     if (st) return st;
     timer.mark();                                                    // [4] start of "rasterization"
-    tg_host::set_tile_order(tile_order, device_status + 1);
+    tg_host::set_tile_order(tile_order);
     st = tg_blend_forward(tri_geo, tri_attr, sorted_ids, offsets, W, H, tw, th, thr, per_pixel_sort, max_layers, image,
                           depthmap, final_weights, ends, selection, stream);
-    tg_host::set_tile_order(nullptr, nullptr);
+    tg_host::set_tile_order(nullptr);
     if (st) return st;
     timer.mark();                                                    // [5] end
     // device error word: valid on the host once the stream has been synchronised
@@ -201,11 +230,11 @@ int tg_render_step_l2(const float* vertices, const int32_t* indices, const float
                               sorted_ids, list_capacity, offsets, workspace, workspace_bytes, info_host, flags, timer, &device_status, &tile_order, s);
     if (st) return st;
     timer.mark();                                                    // [4] start of "rasterization" (here: forward + backward)
-    tg_host::set_tile_order(tile_order, device_status + 1);
+    tg_host::set_tile_order(tile_order);
     st = tg_blend_step_l2(tri_geo, tri_attr, sorted_ids, offsets, V, W, H, tw, th, thr, max_layers, target, grad_scale,
                           loss_scale, loss_out, image, depthmap, final_weights, ends, grad_vertices, grad_colors,
                           grad_opacities, accumulate, scratch, scratch_bytes, stream);
-    tg_host::set_tile_order(nullptr, nullptr);
+    tg_host::set_tile_order(nullptr);
     if (st) return st;
     timer.mark();                                                    // [5] end
     TG_CUDA(cudaMemcpyAsync(&info_host[2], device_status, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));

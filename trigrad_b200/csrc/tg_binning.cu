@@ -241,8 +241,8 @@ struct TileBinArgs {
     uint32_t* longest;       // written when scan_here: the largest tile count
     uint32_t* part_total;    // [CTAs] entries of each CTA's triangles
     uint32_t* k_out;         // K = all entries
-    uint32_t* order;         // [tiles] or null: tiles by descending list-length class, written when scan_here
-    uint32_t* order_valid;   // set to 1 when `order` was written (only when the lists are uneven enough to matter)
+    uint32_t* order;         // [tiles] or null: tiles by descending list-length class, written when scan_here and
+                             // the lists are long and uneven enough to matter; *longest then carries kOrderWrittenBit
 };
 
 // Exclusive scan of cursor[0..tiles) by one CTA of 256 threads, in place, copy in offsets[0..tiles].
@@ -328,6 +328,7 @@ __device__ uint32_t tile_offsets_by_one_cta(uint32_t* cursor, int32_t* offsets, 
 // uneven and the tiles are few enough for one CTA (a 1920x1080 image: 8160 tiles, 5 us).
 constexpr uint32_t kOrderMinLongest = 256;
 constexpr int kOrderMaxTiles = 16384;
+constexpr uint32_t kOrderMinMean = 64;
 __device__ void tile_order_by_one_cta(const int32_t* offsets, int tiles, uint32_t* order, uint32_t* s_hist /*[33]*/) {
     const int tid = threadIdx.x;
     const unsigned lane = lane_id(), lt_mask = (1u << lane) - 1u;
@@ -373,6 +374,7 @@ __global__ void __launch_bounds__(256, 6) preprocess_count_kernel(const float4* 
     uint32_t* s_loc = s_buf;                 // [257] exclusive offsets of the CTA's triangles within the CTA
     int* s_rect = (int*)s_buf + 257;         // [768] x0, y0, rows of each triangle's tile rectangle
     __shared__ bool s_last;
+    __shared__ uint32_t s_k_upper;
     __shared__ float s_m[CULL ? 9 * 256 : 1];   // barycentric matrices of the CTA's triangles, component-major
     const int tid = threadIdx.x;
     const int p = blockIdx.x, num_parts = gridDim.x;
@@ -447,20 +449,26 @@ __global__ void __launch_bounds__(256, 6) preprocess_count_kernel(const float4* 
     __syncthreads();
     if (lane_id() == 0) s_warp[warp] = k;
     __syncthreads();
-    if (tid == 0 && !CULL) {
+    if (tid == 0) {
         k = 0;
 #pragma unroll
         for (int w = 0; w < 8; w++) k += s_warp[w];
-        *bin.k_out = k;
+        if (!CULL) *bin.k_out = k;
+        s_k_upper = k;                       // with culling an upper bound of K (sum of the rectangle sizes)
     }
+    __syncthreads();
     if (bin.scan_here) {
         const uint32_t biggest = tile_offsets_by_one_cta(bin.tile_cursor, bin.offsets, bin.tiles, bin.longest, s_buf, s_warp,
                                                          CULL ? bin.k_out : nullptr);
-        if (bin.order && biggest >= kOrderMinLongest && bin.tiles <= kOrderMaxTiles) {
+        // the launch order costs two more passes over the offsets: only for images of at most 16384 tiles whose
+        // lists are long on average (from the rectangle sizes) and uneven (the longest one at least 256 entries)
+        if (bin.order && bin.tiles <= kOrderMaxTiles && s_k_upper >= kOrderMinMean * (uint32_t)bin.tiles &&
+            biggest >= kOrderMinLongest) {
             __syncthreads();                      // the offsets written above are read back by other threads
             tile_order_by_one_cta(bin.offsets, bin.tiles, bin.order, s_buf);
-            __syncthreads();
-            if (tid == 0) { __threadfence(); *bin.order_valid = 1u; }
+            // the host reads the longest list length together with K: its top bit says "an order was written"
+            // (lengths stay below 2^31), so that the compositing kernel is given the order only when there is one
+            if (tid == 0) *bin.longest = biggest | kOrderWrittenBit;
         }
     }
 }
@@ -707,7 +715,7 @@ size_t preprocess_scan_scratch_bytes(int T) { return 8 + 4 * ((size_t)(T > 0 ? (
 int preprocess_scan(const float* vertices, const int32_t* indices, const float* colors, const float* opacities, int T,
                     int W, int H, int tw, int th, float* tri_geo, float* tri_attr, uint32_t* tri_offsets, void* scratch,
                     uint32_t* status, uint32_t* tile_cursor, int32_t* offsets, void* tile_scan_scratch, bool cull,
-                    bool packed, uint32_t* tile_order, uint32_t* tile_order_valid, cudaStream_t stream) {
+                    bool packed, uint32_t* tile_order, cudaStream_t stream) {
     if (int s = check_dims_internal(T, W, H, tw, th)) return s;
     TG_REQUIRE(tri_offsets && scratch && status && tile_cursor && offsets, "null pointer");
     const int tiles_x = (W + tw - 1) / tw, tiles_y = (H + th - 1) / th;
@@ -726,7 +734,7 @@ int preprocess_scan(const float* vertices, const int32_t* indices, const float* 
     TG_REQUIRE(by_last_cta || tile_scan_scratch, "null tile scan scratch");
     const tg::TileBinArgs bin = {tile_cursor, offsets, (uint32_t*)scratch, tiles, by_last_cta ? 1 : 0,
                                  tri_offsets + T + 1, (uint32_t*)scratch + 2, tri_offsets + T,
-                                 by_last_cta ? tile_order : nullptr, tile_order_valid};
+                                 by_last_cta ? tile_order : nullptr};
     TG_REQUIRE(!cull || by_last_cta, "tile culling is limited to 65536 tiles");
     if (cull)
         tg::preprocess_count_kernel<true><<<(T + 255) / 256, 256, 0, stream>>>(

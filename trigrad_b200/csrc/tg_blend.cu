@@ -34,14 +34,12 @@ struct BlendParams {
     float thr;
     int max_layers;
     // Optional launch order of the tiles (longest lists first, so that no heavy tile starts late): CTA b handles tile
-    // order[b] when *order_valid is non-zero, tile b otherwise.  Both null for the stage entry points.
+    // order[b], or tile b when there is none (the stage entry points; lists too short or too even to bother).
     const uint32_t* order;
-    const uint32_t* order_valid;
 };
 
 __device__ __forceinline__ int tile_of_block(const BlendParams& P) {
-    if (P.order != nullptr && *P.order_valid != 0u) return (int)P.order[blockIdx.x];
-    return (int)blockIdx.x;
+    return P.order != nullptr ? (int)P.order[blockIdx.x] : (int)blockIdx.x;
 }
 
 struct PixelAcc {
@@ -162,13 +160,51 @@ __device__ __forceinline__ TileCtx tile_context(const BlendParams& P, float* s_c
 }
 
 // Stage `n` records of the list starting at `first` into shared memory (ids + geometry).
+// Quad q of staged record r sits at s_geo[4 r + (q ^ ((r >> 1) & 3))]: with this swizzle the 32 lanes of a warp can
+// each read "their" record with 16-byte loads without shared-memory bank conflicts (a plain 64-byte stride puts
+// every second lane on the same banks), and a record read by all lanes at once is four broadcast loads.
+__device__ __forceinline__ int staged_quad(int r, int q) { return 4 * r + (q ^ ((r >> 1) & 3)); }
+
 __device__ __forceinline__ void stage_chunk(const BlendParams& P, int first, int n, float4* s_geo, int* s_id) {
     for (int i = threadIdx.x; i < n * 4; i += blockDim.x) {
         const int rec = i >> 2, q = i & 3;
         const int id = P.ids[first + rec];
         if (q == 0) s_id[rec] = id;
-        s_geo[i] = __ldg(P.geo + 4 * (size_t)id + q);
+        s_geo[staged_quad(rec, q)] = __ldg(P.geo + 4 * (size_t)id + q);
     }
+}
+
+// A staged geometry record in registers (only the parts a caller uses are actually loaded).
+struct StagedGeo {
+    float m[9];
+    float z[3];
+    float w[3];
+    float zlow;
+};
+// The same record read by ALL lanes at once (r uniform over the warp): word loads, each a one-cycle broadcast (a
+// 16-byte broadcast load occupies the shared-memory pipe four times as long), and only of the words really used.
+struct StagedRef {
+    const float* base;
+    int o[4];     // word offset of each quad inside the 16-word record
+    __device__ __forceinline__ StagedRef(const float4* s_geo, int r) : base(reinterpret_cast<const float*>(s_geo) + 16 * r) {
+        const int sw = (r >> 1) & 3;
+        o[0] = (0 ^ sw) << 2; o[1] = (1 ^ sw) << 2; o[2] = (2 ^ sw) << 2; o[3] = (3 ^ sw) << 2;
+    }
+    __device__ __forceinline__ float word(int e) const { return base[o[e >> 2] + (e & 3)]; }   // e: compile-time constant
+    __device__ __forceinline__ void matrix(float* m) const {
+#pragma unroll
+        for (int e = 0; e < 9; e++) m[e] = word(e);
+    }
+    __device__ __forceinline__ void weights(float* w) const { w[0] = word(12); w[1] = word(13); w[2] = word(14); }
+};
+
+__device__ __forceinline__ StagedGeo load_staged(const float4* s_geo, int r) {
+    const float4 a = s_geo[staged_quad(r, 0)], b = s_geo[staged_quad(r, 1)], c = s_geo[staged_quad(r, 2)],
+                 d = s_geo[staged_quad(r, 3)];
+    StagedGeo g;
+    g.m[0] = a.x; g.m[1] = a.y; g.m[2] = a.z; g.m[3] = a.w; g.m[4] = b.x; g.m[5] = b.y; g.m[6] = b.z; g.m[7] = b.w;
+    g.m[8] = c.x; g.z[0] = c.y; g.z[1] = c.z; g.z[2] = c.w; g.w[0] = d.x; g.w[1] = d.y; g.w[2] = d.z; g.zlow = d.w;
+    return g;
 }
 
 // Bit mask (64 records) of the staged records that may matter to this warp: the triangle may cover one
@@ -179,12 +215,12 @@ __device__ __forceinline__ unsigned long long warp_cull(const float4* s_geo, int
     const int lane = lane_id();
     bool k0 = false, k1 = false;
     if (lane < n) {
-        const float* g = reinterpret_cast<const float*>(s_geo + 4 * lane);
-        k0 = g[15] < depth_cut && rect_may_cover(g, R);
+        const StagedGeo g = load_staged(s_geo, lane);
+        k0 = g.zlow < depth_cut && rect_may_cover(g.m, R);
     }
     if (lane + 32 < n) {
-        const float* g = reinterpret_cast<const float*>(s_geo + 4 * (lane + 32));
-        k1 = g[15] < depth_cut && rect_may_cover(g, R);
+        const StagedGeo g = load_staged(s_geo, lane + 32);
+        k1 = g.zlow < depth_cut && rect_may_cover(g.m, R);
     }
     const unsigned m0 = __ballot_sync(0xffffffffu, k0), m1 = __ballot_sync(0xffffffffu, k1);
     return (unsigned long long)m0 | ((unsigned long long)m1 << 32);
@@ -213,10 +249,12 @@ __device__ __forceinline__ int select_sweep(const BlendParams& P, const TileCtx&
             const int r = __ffsll((long long)mask) - 1;
             mask &= mask - 1;
             if (!go) continue;
-            const float* g = reinterpret_cast<const float*>(s_geo + 4 * r);
-            const Bary b = apply_bary(g, c.px, c.py);
+            const StagedRef g(s_geo, r);
+            float m[9];
+            g.matrix(m);
+            const Bary b = apply_bary(m, c.px, c.py);
             if (!covered(b)) continue;
-            const float d = interp_rn(b, g[9], g[10], g[11], g[12], g[13], g[14]);
+            const float d = interp_rn(b, g.word(9), g.word(10), g.word(11), g.word(12), g.word(13), g.word(14));
             const int j = first + r;
             if (d < lastDepth) continue;
             if (d == lastDepth && j <= lastJ) continue;
@@ -321,11 +359,14 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 256 ? 5 : 1) blend_forward_kerne
                     mask &= mask - 1;
                     if (done) continue;
                     if (!(acc.alpha > P.thr && acc.blended < P.max_layers)) { done = true; continue; }
-                    const float* g = reinterpret_cast<const float*>(s_geo + 4 * r);
-                    const Bary b = apply_bary(g, c.px, c.py);
+                    const StagedRef g(s_geo, r);
+                    float m[9], w[3];
+                    g.matrix(m);
+                    const Bary b = apply_bary(m, c.px, c.py);
                     if (!covered(b)) continue;
+                    g.weights(w);
                     const AttrRec a = load_attr<false>(P.attr, s_id[r]);
-                    blend_one(b, g + 12, a, acc);
+                    blend_one(b, w, a, acc);
                 }
                 if (!(acc.alpha > P.thr && acc.blended < P.max_layers)) done = true;
             }
@@ -1004,12 +1045,15 @@ __global__ void __launch_bounds__(MAXT) blend_backward_kernel(BlendParams P, Bac
                 const int r = __ffsll((long long)mask) - 1;
                 mask &= mask - 1;
                 if (first + r >= limit) continue;
-                const float* g = reinterpret_cast<const float*>(s_geo + 4 * r);
-                const Bary b = apply_bary(g, c.px, c.py);
+                const StagedRef g(s_geo, r);
+                float m[9], w[3];
+                g.matrix(m);
+                const Bary b = apply_bary(m, c.px, c.py);
                 if (!covered(b)) continue;
+                g.weights(w);
                 const AttrRec a = load_attr<true>(P.attr, s_id[r]);
                 Contrib ct;
-                backward_one(g + 12, a, b, c.px, c.py, pg, st, ct);
+                backward_one(w, a, b, c.px, c.py, pg, st, ct);
                 emit_contrib(ct, gpack);
             }
         }
@@ -1138,12 +1182,15 @@ __global__ void __launch_bounds__(MAXT) blend_backward_corrected_kernel(BlendPar
                     const int r = __ffsll((long long)mask) - 1;
                     mask &= mask - 1;
                     if (done) continue;
-                    const float* g = reinterpret_cast<const float*>(s_geo + 4 * r);
-                    const Bary b = apply_bary(g, c.px, c.py);
+                    const StagedRef g(s_geo, r);
+                    float m[9], w[3];
+                    g.matrix(m);
+                    const Bary b = apply_bary(m, c.px, c.py);
                     if (!covered(b)) continue;
+                    g.weights(w);
                     const AttrRec a = load_attr<true>(P.attr, s_id[r]);
                     Contrib ct;
-                    backward_one_prefix(g + 12, a, b, c.px, c.py, pg, fin, pf, ct);
+                    backward_one_prefix(w, a, b, c.px, c.py, pg, fin, pf, ct);
                     emit_contrib(ct, gpack);
                     if (++processed >= limit) done = true;
                 }
@@ -1222,7 +1269,7 @@ static tg::BlendParams make_params(const float* tri_geo, const float* tri_attr, 
     P.geo = (const float4*)tri_geo; P.attr = (const float4*)tri_attr; P.ids = sorted_ids; P.offsets = offsets;
     P.W = W; P.H = H; P.tw = tw; P.th = th; P.tiles_x = (W + tw - 1) / tw;
     P.thr = thr; P.max_layers = max_layers;
-    P.order = nullptr; P.order_valid = nullptr;
+    P.order = nullptr;
     return P;
 }
 
@@ -1236,8 +1283,7 @@ namespace tg_host {
 // Set by tg_render_forward / tg_render_step_l2 around their compositing call (same thread): the tile order the
 // binning kernel left in the workspace.  The stage entry points run with the identity order.
 static thread_local const uint32_t* g_tile_order = nullptr;
-static thread_local const uint32_t* g_tile_order_valid = nullptr;
-void set_tile_order(const uint32_t* order, const uint32_t* valid) { g_tile_order = order; g_tile_order_valid = valid; }
+void set_tile_order(const uint32_t* order) { g_tile_order = order; }
 }  // namespace tg_host
 
 extern "C" {
@@ -1251,7 +1297,7 @@ int tg_blend_forward(const float* tri_geo, const float* tri_attr, const int32_t*
                "image / tri_geo / tri_attr must be 16-byte aligned");
     if (tg_selection_planes(per_pixel_sort, max_layers) == 0) selection = nullptr;
     tg::BlendParams P = make_params(tri_geo, tri_attr, sorted_ids, offsets, W, H, tw, th, thr, max_layers);
-    P.order = tg_host::g_tile_order; P.order_valid = tg_host::g_tile_order_valid;
+    P.order = tg_host::g_tile_order;
     const int tiles = P.tiles_x * ((H + th - 1) / th);
     const int threads = ((tw * th + 31) / 32) * 32;
     cudaStream_t s = (cudaStream_t)stream;
@@ -1348,7 +1394,7 @@ int tg_blend_step_l2(const float* tri_geo, const float* tri_attr, const int32_t*
     float* partials = (float*)((char*)scratch + (size_t)V * 32);
     if (!packed) TG_CUDA(cudaMemsetAsync(gpack, 0, (size_t)V * 32 + sizeof(float) * tg::kLossPartials, s));
     tg::BlendParams P = make_params(tri_geo, tri_attr, sorted_ids, offsets, W, H, tw, th, thr, max_layers);
-    P.order = tg_host::g_tile_order; P.order_valid = tg_host::g_tile_order_valid;
+    P.order = tg_host::g_tile_order;
     const int tiles = P.tiles_x * ((H + th - 1) / th);
     const int threads = ((tw * th + 31) / 32) * 32;
     tg::blend_step_l2_kernel<256><<<tiles, threads, 0, s>>>(P, (float4*)image, depthmap, final_weights, ends,

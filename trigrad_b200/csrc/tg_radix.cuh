@@ -19,6 +19,8 @@ constexpr size_t kCtrBytes = 64;
 constexpr int kHistDoneWord = 8;
 // Up to this many tiles the CTA that finishes the fused preprocess kernel last scans the tile counts itself.
 constexpr int kTileScanByLastCta = 65536;
+// Top bit of the longest-list word the binning kernel reports: a launch order of the tiles was written.
+constexpr uint32_t kOrderWrittenBit = 0x80000000u;
 
 // Exclusive scan of one value per thread over the first 256 threads of a CTA (all threads of the CTA
 // must call it; threads beyond 256 pass 0 and ignore the result).
@@ -93,11 +95,11 @@ size_t preprocess_scan_scratch_bytes(int T);
 int preprocess_scan(const float* vertices, const int32_t* indices, const float* colors, const float* opacities, int T,
                     int W, int H, int tw, int th, float* tri_geo, float* tri_attr, uint32_t* tri_offsets, void* scratch,
                     uint32_t* status, uint32_t* tile_cursor, int32_t* offsets, void* tile_scan_scratch, bool cull,
-                    bool packed, uint32_t* tile_order, uint32_t* tile_order_valid, cudaStream_t stream);
+                    bool packed, uint32_t* tile_order, cudaStream_t stream);
 int emit_entries(const float* vertices, const int32_t* indices, int T, int W, int H, int tw, int th,
                  const uint32_t* tri_offsets, const void* scan_scratch, uint32_t* tile_cursor, uint64_t* entries,
                  uint32_t capacity, const float* tri_geo_for_cull, bool packed, cudaStream_t stream);
-void set_tile_order(const uint32_t* order, const uint32_t* valid);
+void set_tile_order(const uint32_t* order);
 size_t tile_sort_scratch_bytes(int tiles);
 int sort_tile_lists(uint64_t* entries, const int32_t* offsets, int tiles, int32_t* sorted_ids, uint32_t* lists,
                     bool scratch_prepared, bool write_back, uint32_t longest, cudaStream_t stream);
