@@ -164,6 +164,7 @@ int tg_blend_forward(const float* tri_geo, const float* tri_attr, const int32_t*
 /* ---- stage 7: backward ------------------------------------------------------------------------
  * Replaces render_backward_kernel (src/trigrad/render.cu:621-695 with :455-538).
  * grad_vertices [V,4] (z column stays 0; 16-byte aligned), grad_colors [V,3], grad_opacities [V].
+ * grad_depthmap may be NULL (no gradient flows into the depth map: taken as zero, and 4 bytes per pixel less to read).
  * accumulate == 0: the three gradient buffers are overwritten; != 0: added to.
  * selection: what tg_blend_forward wrote, or NULL (the lists are then searched again).
  * scratch: tg_backward_scratch_bytes(V) bytes, 16-byte aligned (packed per-vertex accumulator).

@@ -511,3 +511,30 @@ def test_world_space_view_step_with_packed_accumulators_on_two_streams():
             assert Hh.rel_l2(a.cpu().numpy(), b.cpu().numpy()) <= 1e-5
         for p in packs:
             assert not bool(p.scratch.any())
+
+
+@pytest.mark.parametrize("use", ["image", "depth"])
+def test_loss_that_uses_only_one_output(use):
+    """Autograd hands the unused output's gradient over as None (no zero tensor is made): image-only and depth-only
+    losses against the oracle with the other upstream gradient zero."""
+    sc = S.config1_icosphere(width=128, height=128)
+    rng = np.random.default_rng(3)
+    gi = rng.normal(size=(sc.height, sc.width, 4)).astype(np.float32)
+    gd = rng.normal(size=(sc.height, sc.width)).astype(np.float32)
+    v, i, c, o = Hh.scene_tensors(sc)
+    v.requires_grad_(), c.requires_grad_(), o.requires_grad_()
+    image, depth = trigrad_b200.render(v, i, c, o, sc.width, sc.height)
+    if use == "image":
+        (image * Hh.cuda(gi)).sum().backward()
+        gd[:] = 0
+    else:
+        d0 = torch.where(torch.isfinite(depth), depth, torch.zeros_like(depth))
+        (d0 * Hh.cuda(gd)).sum().backward()
+        gi[:] = 0
+    of = O.forward(sc.vertices, sc.indices, sc.colors, sc.opacities, sc.width, sc.height)
+    og = O.backward(sc.vertices, sc.indices, sc.colors, sc.opacities, sc.width, sc.height, of, gi, gd)
+    for a, b in zip((v.grad, c.grad, o.grad), og):
+        if float(np.abs(b).max()) == 0.0:
+            assert float(a.abs().max()) == 0.0
+        else:
+            assert Hh.rel_l2(a.cpu().numpy(), b) <= 1e-4

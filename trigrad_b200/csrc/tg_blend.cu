@@ -544,7 +544,7 @@ __device__ __forceinline__ int load_pixel_state(const TileCtx& c, const BlendPar
     } else {
         const float4 gi = in.gimage[index];
         pg.gr = gi.x; pg.gg = gi.y; pg.gb = gi.z; pg.ga = gi.w;
-        pg.gd = in.gdepth[index];
+        pg.gd = in.gdepth ? in.gdepth[index] : 0.f;      // no depth-map gradient given: zero
     }
     pg.final_alpha = img.w;
     pg.final_weight = in.final_w[index];
@@ -1326,7 +1326,7 @@ static int backward_impl(const float* tri_geo, const float* tri_attr, const int3
     if (int s = blend_args(W, H, tw, th, max_layers)) return s;
     TG_REQUIRE(V >= 0, "V < 0");
     TG_REQUIRE(offsets && image && depthmap && final_weights && ends, "null pointer");
-    TG_REQUIRE(l2_target || (grad_image && grad_depthmap), "null upstream gradient");
+    TG_REQUIRE(l2_target || grad_image, "null upstream gradient");
     if (V == 0) return TG_OK;
     const bool packed = accumulate == TG_ACCUMULATE_PACKED;   // gradients stay in the scratch, which keeps accumulating
     TG_REQUIRE(scratch && (packed || (grad_vertices && grad_colors && grad_opacities)), "null gradient / scratch pointer");
@@ -1450,7 +1450,7 @@ int tg_blend_backward(const float* tri_geo, const float* tri_attr, const int32_t
                       const float* grad_depthmap, const float* image, const float* depthmap, const float* final_weights,
                       const int32_t* ends, const int32_t* selection, float* grad_vertices, float* grad_colors,
                       float* grad_opacities, int accumulate, void* scratch, size_t scratch_bytes, tg_stream_t stream) {
-    TG_REQUIRE(grad_image && grad_depthmap, "null upstream gradient");
+    TG_REQUIRE(grad_image, "null upstream gradient");
     return backward_impl(tri_geo, tri_attr, sorted_ids, offsets, V, W, H, tw, th, per_pixel_sort, max_layers, grad_image,
                          grad_depthmap, nullptr, false, 0.f, 0.f, nullptr, image, depthmap, final_weights, ends, selection,
                          grad_vertices, grad_colors, grad_opacities, accumulate, scratch, scratch_bytes, stream);
@@ -1464,7 +1464,7 @@ int tg_blend_backward_corrected(const float* tri_geo, const float* tri_attr, con
                                 void* scratch, size_t scratch_bytes, tg_stream_t stream) {
     if (int s = blend_args(W, H, tw, th, max_layers)) return s;
     TG_REQUIRE(V >= 0, "V < 0");
-    TG_REQUIRE(offsets && image && depthmap && final_weights && ends && grad_image && grad_depthmap, "null pointer");
+    TG_REQUIRE(offsets && image && depthmap && final_weights && ends && grad_image, "null pointer");
     if (V == 0) return TG_OK;
     TG_REQUIRE(accumulate == 0 || accumulate == 1, "accumulate must be 0 or 1");
     TG_REQUIRE(scratch && grad_vertices && grad_colors && grad_opacities, "null gradient / scratch pointer");

@@ -180,8 +180,10 @@ def backward_native(grad_image, grad_depthmap, saved, V, width, height, tile_wid
         st.check_error_word(st.last_slot)
         nscratch = lib.tg_backward_scratch_bytes(V)
         scratch = torch.empty(nscratch, dtype=torch.uint8, device=device)
+        if grad_image is None:       # only the depth map was used downstream
+            grad_image = torch.zeros_like(image)
         grad_image = grad_image.contiguous()
-        grad_depthmap = grad_depthmap.contiguous()
+        grad_depthmap = None if grad_depthmap is None else grad_depthmap.contiguous()     # None: taken as zero by the kernel
         accumulate = out is not None
         if out is None:
             f32 = dict(dtype=torch.float32, device=device)
@@ -321,6 +323,9 @@ class Renderer(Function):
             max_layers = n + 1
         ctx.width, ctx.height = width, height
         ctx.tile_width, ctx.tile_height = tile_width, tile_height
+        # an output that was not used downstream arrives in backward as None instead of a tensor of zeros that
+        # autograd would have to fill and the kernel to read (the depth map, in the usual image-only loss)
+        ctx.set_materialize_grads(False)
         ctx.per_pixel_sort, ctx.max_layers = per_pixel_sort, max_layers
         if n < 1:
             ctx.skipped = True
@@ -345,9 +350,13 @@ class Renderer(Function):
 
     @staticmethod
     def backward(ctx, grad_image: torch.Tensor, grad_depthmap: torch.Tensor, grad_timings=None):
-        if ctx.skipped:
-            vertices, colors, opacities = ctx.saved_tensors
-            gV, gC, gO = torch.zeros_like(vertices), torch.zeros_like(colors), torch.zeros_like(opacities)
+        if ctx.skipped or (grad_image is None and grad_depthmap is None):
+            if ctx.skipped:
+                vertices, colors, opacities = ctx.saved_tensors
+                gV, gC, gO = torch.zeros_like(vertices), torch.zeros_like(colors), torch.zeros_like(opacities)
+            else:
+                dev, V = ctx.saved_tensors[4].device, ctx.num_vertices
+                gV, gC, gO = (torch.zeros((V, 4), device=dev), torch.zeros((V, 3), device=dev), torch.zeros((V,), device=dev))
         else:
             saved = tuple(ctx.saved_tensors) + (() if ctx.has_selection else (None,))
             gV, gC, gO = backward_native(grad_image, grad_depthmap, saved, ctx.num_vertices, ctx.width,
