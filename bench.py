@@ -243,8 +243,17 @@ class ViewBatch:
     atomic additions.  Either way the summed gradients and the loss end up in ``self.grads`` (one contiguous fp32
     buffer, the object of the all-reduce)."""
 
-    def __init__(self, torch, Vw, scene, dev, n_streams, one_kernel=False):
+    def __init__(self, torch, Vw, scene, dev, n_streams, one_kernel=False, host_threads=1):
         self.torch, self.Vw, self.scene, self.dev, self.one_kernel = torch, Vw, scene, dev, one_kernel
+        # Every view makes the issuing host thread wait once (for the number of list entries, before the compositing
+        # kernels can be launched).  With several host threads, each feeding its own streams, one thread's wait no
+        # longer holds back the launches of the other streams (ctypes calls and the wait release the GIL).
+        self.host_threads = max(1, host_threads)
+        self.pool = None
+        if self.host_threads > 1:
+            from concurrent.futures import ThreadPoolExecutor
+
+            self.pool = ThreadPoolExecutor(max_workers=self.host_threads)
         self.camera_ring = "mesh" in scene.meta
         self.W, self.H = scene.width, scene.height
         self.V = scene.num_vertices
@@ -282,16 +291,27 @@ class ViewBatch:
         start.record(main)
         for st in self.side_streams:
             st.wait_event(start)
-        for b, (v, t, ready) in enumerate(items):
-            si = b % self.n_streams
-            stream = main if si == 0 else self.side_streams[si - 1]
-            with torch.cuda.stream(stream):
-                if ready is not None:
-                    stream.wait_event(ready)
-                    if isinstance(v, torch.Tensor):
-                        v.record_stream(stream)
-                    t.record_stream(stream)
-                self.render_view(v, t, si)
+        def issue(si_set):
+            torch.cuda.set_device(self.dev)          # the current device is a per-thread setting
+            for b, (v, t, ready) in enumerate(items):
+                si = b % self.n_streams
+                if si not in si_set:
+                    continue
+                stream = main if si == 0 else self.side_streams[si - 1]
+                with torch.cuda.stream(stream):
+                    if ready is not None:
+                        stream.wait_event(ready)
+                        if isinstance(v, torch.Tensor):
+                            v.record_stream(stream)
+                        t.record_stream(stream)
+                    self.render_view(v, t, si)
+
+        if self.pool is None:
+            issue(set(range(self.n_streams)))
+        else:
+            sets = [set(range(k, self.n_streams, self.host_threads)) for k in range(self.host_threads)]
+            for f in [self.pool.submit(issue, ss) for ss in sets if ss]:
+                f.result()
         for st in self.side_streams:
             done = torch.cuda.Event()
             done.record(st)
@@ -381,7 +401,8 @@ def cfg4_sharded_block(torch, dist, Vw, dev, rank: int, world: int, n_streams: i
     scene, wname = make_scene("cfg4")
     pvs = scene.meta["pvs"]
     mine = list(Vw.shard_views(len(pvs), rank, world))
-    batch = ViewBatch(torch, Vw, scene, dev, min(n_streams, max(1, len(mine))))
+    n_s = min(n_streams, max(1, len(mine)))
+    batch = ViewBatch(torch, Vw, scene, dev, n_s, host_threads=n_s)
     W, H = scene.width, scene.height
     rng = np.random.default_rng(100 + rank)
     # a handful of distinct targets reused round-robin (64 full-size fp32 targets would be 2 GB of nothing new)
@@ -486,6 +507,9 @@ def main() -> None:
     ap.add_argument("--pairs", type=float, default=float(1 << 25), help="--workload sort: number of pairs")
     ap.add_argument("--streams", type=int, default=4,
                     help="CUDA streams the views of a step are spread over (independent views overlap on the GPU)")
+    ap.add_argument("--host-threads", type=int, default=0,
+                    help="host threads that issue the views of a step, each feeding its own subset of the streams "
+                         "(0 = one per stream)")
     ap.add_argument("--views-per-gpu", type=int, default=8,
                     help="views of the mesh rendered per GPU per step (a batch of views; gradients are summed)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -536,7 +560,8 @@ def main() -> None:
     verts_np = S_project(scene, views_np[0]) if camera_ring else views_np[0]
 
     n_streams = max(1, min(args.streams, B))
-    batch = ViewBatch(torch, Vw, scene, dev, n_streams, one_kernel=args.one_kernel)
+    host_threads = args.host_threads if args.host_threads > 0 else n_streams
+    batch = ViewBatch(torch, Vw, scene, dev, n_streams, one_kernel=args.one_kernel, host_threads=host_threads)
     grads = batch.grads
     pos_comp = batch.pos_comp
     dv = list(views_np) if camera_ring else [torch.from_numpy(x).to(dev) for x in views_np]
@@ -662,7 +687,7 @@ def main() -> None:
         "data": "synthetic",
         "config": {"workload": wname, "triangles": T, "vertices": V, "width": W, "height": H,
                    "tile": [scene.tile_width, scene.tile_height], "per_pixel_sort": True, "max_layers": 32,
-                   "views_per_gpu_per_step": B, "streams": n_streams, "one_kernel_step": bool(args.one_kernel), "K_pairs": stages["_K"], "l2": "256 MB buffer rewritten between timed steps",
+                   "views_per_gpu_per_step": B, "streams": n_streams, "host_threads": batch.host_threads, "one_kernel_step": bool(args.one_kernel), "K_pairs": stages["_K"], "l2": "256 MB buffer rewritten between timed steps",
                    "e2e_target_dtype": "u8 rgba (value / 255)",
                    "exchange": "none" if world == 1 else f"one NCCL all_reduce of {pos_comp + 4}V fp32 gradients per step"},
         "triangles_per_s": T * B * world / (ms_per_step * 1e-3),
