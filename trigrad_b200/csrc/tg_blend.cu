@@ -160,10 +160,11 @@ __device__ __forceinline__ TileCtx tile_context(const BlendParams& P, float* s_c
 }
 
 // Stage `n` records of the list starting at `first` into shared memory (ids + geometry).
-// Quad q of staged record r sits at s_geo[4 r + (q ^ ((r >> 1) & 3))]: with this swizzle the 32 lanes of a warp can
-// each read "their" record with 16-byte loads without shared-memory bank conflicts (a plain 64-byte stride puts
-// every second lane on the same banks), and a record read by all lanes at once is four broadcast loads.
-__device__ __forceinline__ int staged_quad(int r, int q) { return 4 * r + (q ^ ((r >> 1) & 3)); }
+// Staged records are 80 bytes apart (64 bytes of record, 16 of padding): with that stride the 32 lanes of a warp can
+// each read "their" record with 16-byte loads without shared-memory bank conflicts (a 64-byte stride puts every
+// second lane on the same banks), and the words of a record keep constant offsets from its base.
+constexpr int kStagedQuads = 5;
+__device__ __forceinline__ int staged_quad(int r, int q) { return kStagedQuads * r + q; }
 
 __device__ __forceinline__ void stage_chunk(const BlendParams& P, int first, int n, float4* s_geo, int* s_id) {
     for (int i = threadIdx.x; i < n * 4; i += blockDim.x) {
@@ -181,23 +182,6 @@ struct StagedGeo {
     float w[3];
     float zlow;
 };
-// The same record read by ALL lanes at once (r uniform over the warp): word loads, each a one-cycle broadcast (a
-// 16-byte broadcast load occupies the shared-memory pipe four times as long), and only of the words really used.
-struct StagedRef {
-    const float* base;
-    int o[4];     // word offset of each quad inside the 16-word record
-    __device__ __forceinline__ StagedRef(const float4* s_geo, int r) : base(reinterpret_cast<const float*>(s_geo) + 16 * r) {
-        const int sw = (r >> 1) & 3;
-        o[0] = (0 ^ sw) << 2; o[1] = (1 ^ sw) << 2; o[2] = (2 ^ sw) << 2; o[3] = (3 ^ sw) << 2;
-    }
-    __device__ __forceinline__ float word(int e) const { return base[o[e >> 2] + (e & 3)]; }   // e: compile-time constant
-    __device__ __forceinline__ void matrix(float* m) const {
-#pragma unroll
-        for (int e = 0; e < 9; e++) m[e] = word(e);
-    }
-    __device__ __forceinline__ void weights(float* w) const { w[0] = word(12); w[1] = word(13); w[2] = word(14); }
-};
-
 __device__ __forceinline__ StagedGeo load_staged(const float4* s_geo, int r) {
     const float4 a = s_geo[staged_quad(r, 0)], b = s_geo[staged_quad(r, 1)], c = s_geo[staged_quad(r, 2)],
                  d = s_geo[staged_quad(r, 3)];
@@ -249,12 +233,10 @@ __device__ __forceinline__ int select_sweep(const BlendParams& P, const TileCtx&
             const int r = __ffsll((long long)mask) - 1;
             mask &= mask - 1;
             if (!go) continue;
-            const StagedRef g(s_geo, r);
-            float m[9];
-            g.matrix(m);
-            const Bary b = apply_bary(m, c.px, c.py);
+            const float* g = reinterpret_cast<const float*>(s_geo + kStagedQuads * r);    // broadcast word loads
+            const Bary b = apply_bary(g, c.px, c.py);
             if (!covered(b)) continue;
-            const float d = interp_rn(b, g.word(9), g.word(10), g.word(11), g.word(12), g.word(13), g.word(14));
+            const float d = interp_rn(b, g[9], g[10], g[11], g[12], g[13], g[14]);
             const int j = first + r;
             if (d < lastDepth) continue;
             if (d == lastDepth && j <= lastJ) continue;
@@ -292,7 +274,7 @@ template <bool SORT, int MAXT>
 __global__ void __launch_bounds__(MAXT, MAXT <= 256 ? 5 : 1) blend_forward_kernel(BlendParams P, float4* __restrict__ image,
                                                              float* __restrict__ depthmap, float* __restrict__ final_w,
                                                              int* __restrict__ ends, int* __restrict__ sel) {
-    __shared__ float4 s_geo[kChunk * 4];
+    __shared__ float4 s_geo[kChunk * kStagedQuads];
     __shared__ int s_id[kChunk];
     __shared__ float s_coord[kMaxTileCoords];
     const int this_tile = tile_of_block(P);
@@ -359,14 +341,11 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 256 ? 5 : 1) blend_forward_kerne
                     mask &= mask - 1;
                     if (done) continue;
                     if (!(acc.alpha > P.thr && acc.blended < P.max_layers)) { done = true; continue; }
-                    const StagedRef g(s_geo, r);
-                    float m[9], w[3];
-                    g.matrix(m);
-                    const Bary b = apply_bary(m, c.px, c.py);
+                    const float* g = reinterpret_cast<const float*>(s_geo + kStagedQuads * r);
+                    const Bary b = apply_bary(g, c.px, c.py);
                     if (!covered(b)) continue;
-                    g.weights(w);
                     const AttrRec a = load_attr<false>(P.attr, s_id[r]);
-                    blend_one(b, w, a, acc);
+                    blend_one(b, g + 12, a, acc);
                 }
                 if (!(acc.alpha > P.thr && acc.blended < P.max_layers)) done = true;
             }
@@ -896,7 +875,7 @@ __global__ void __launch_bounds__(MAXT, 4) blend_step_l2_kernel(BlendParams P, f
                                                                 float grad_scale, float* __restrict__ l2_partials,
                                                                 float4* __restrict__ gpack) {
     static_assert(MAXT == 256, "the per-warp queues are sized for 8 warps");
-    __shared__ float4 s_geo[kChunk * 4];
+    __shared__ float4 s_geo[kChunk * kStagedQuads];
     __shared__ int s_id[kChunk];
     __shared__ float s_coord[kMaxTileCoords];
     __shared__ float s_queue[MAXT / 32][kQueueFields][kQueueSlots];
@@ -986,7 +965,7 @@ __global__ void __launch_bounds__(MAXT, 4) blend_step_l2_kernel(BlendParams P, f
 // General path (any max_layers, both modes): searches the list again as the reference does.
 template <bool SORT, int MAXT>
 __global__ void __launch_bounds__(MAXT) blend_backward_kernel(BlendParams P, BackwardIn in, float4* __restrict__ gpack) {
-    __shared__ float4 s_geo[kChunk * 4];
+    __shared__ float4 s_geo[kChunk * kStagedQuads];
     __shared__ int s_id[kChunk];
     __shared__ float s_coord[kMaxTileCoords];
     const TileCtx c = tile_context(P, s_coord);
@@ -1045,15 +1024,12 @@ __global__ void __launch_bounds__(MAXT) blend_backward_kernel(BlendParams P, Bac
                 const int r = __ffsll((long long)mask) - 1;
                 mask &= mask - 1;
                 if (first + r >= limit) continue;
-                const StagedRef g(s_geo, r);
-                float m[9], w[3];
-                g.matrix(m);
-                const Bary b = apply_bary(m, c.px, c.py);
+                const float* g = reinterpret_cast<const float*>(s_geo + kStagedQuads * r);
+                const Bary b = apply_bary(g, c.px, c.py);
                 if (!covered(b)) continue;
-                g.weights(w);
                 const AttrRec a = load_attr<true>(P.attr, s_id[r]);
                 Contrib ct;
-                backward_one(w, a, b, c.px, c.py, pg, st, ct);
+                backward_one(g + 12, a, b, c.px, c.py, pg, st, ct);
                 emit_contrib(ct, gpack);
             }
         }
@@ -1120,7 +1096,7 @@ __device__ __forceinline__ void backward_one_prefix(const float* w, const AttrRe
 template <bool SORT, int MAXT>
 __global__ void __launch_bounds__(MAXT) blend_backward_corrected_kernel(BlendParams P, BackwardIn in,
                                                                         float4* __restrict__ gpack) {
-    __shared__ float4 s_geo[kChunk * 4];
+    __shared__ float4 s_geo[kChunk * kStagedQuads];
     __shared__ int s_id[kChunk];
     __shared__ float s_coord[kMaxTileCoords];
     const TileCtx c = tile_context(P, s_coord);
@@ -1182,15 +1158,12 @@ __global__ void __launch_bounds__(MAXT) blend_backward_corrected_kernel(BlendPar
                     const int r = __ffsll((long long)mask) - 1;
                     mask &= mask - 1;
                     if (done) continue;
-                    const StagedRef g(s_geo, r);
-                    float m[9], w[3];
-                    g.matrix(m);
-                    const Bary b = apply_bary(m, c.px, c.py);
+                    const float* g = reinterpret_cast<const float*>(s_geo + kStagedQuads * r);
+                    const Bary b = apply_bary(g, c.px, c.py);
                     if (!covered(b)) continue;
-                    g.weights(w);
                     const AttrRec a = load_attr<true>(P.attr, s_id[r]);
                     Contrib ct;
-                    backward_one_prefix(w, a, b, c.px, c.py, pg, fin, pf, ct);
+                    backward_one_prefix(g + 12, a, b, c.px, c.py, pg, fin, pf, ct);
                     emit_contrib(ct, gpack);
                     if (++processed >= limit) done = true;
                 }
