@@ -261,8 +261,9 @@ int tg_blend_step_l2(const float* tri_geo, const float* tri_attr, const int32_t*
  *   sorted_ids   [list_capacity] int32   out, first K entries valid
  *   offsets      [tiles+1] int32         out
  *   info_host    uint32[4] in (preferably pinned) host memory.  [0] receives K and [1] the length
- *                of the longest tile list; the call synchronises the stream once to read them (the
- *                reference does the same, src/trigrad/render.cu:290).  [2] receives the device error
+ *                of the longest tile list; the call waits on the host until they have arrived (it watches
+ *                the first word, so pinned memory makes this quick; the reference synchronises at the same
+ *                point, src/trigrad/render.cu:290).  [2] receives the device error
  *                word (0 = fine) by an asynchronous copy: it is valid after the caller next
  *                synchronises the stream.  [3] is not used.
  *   stage_ms_host  NULL or float[5]: milliseconds of {init, per_tile_lists, sorting,

@@ -360,8 +360,14 @@ __device__ void tile_order_by_one_cta(const int32_t* offsets, int tiles, uint32_
 // CULL: a (triangle, tile) pair of the bounding rectangle is counted only if the triangle can cover the centre of
 // some pixel of the tile (rect_may_cover on the tile's pixel-centre rectangle): the exact test the reference
 // leaves open (render.cu:110).  K is then the sum of the tile counts, not of the rectangle sizes.
-template <bool CULL>
-__global__ void __launch_bounds__(256, 6) preprocess_count_kernel(const float4* __restrict__ vertices,
+// MINB: CTAs per SM the register budget is set for.  Six (40 registers) keeps a mesh of up to 888 x 256 triangles
+// resident in a single wave; larger meshes run several waves anyway and gain from more registers per thread
+// (more of a triangle's gathers in flight at once).
+#ifndef TG_PREPROCESS_MINB_LARGE
+#define TG_PREPROCESS_MINB_LARGE 5
+#endif
+template <bool CULL, int MINB>
+__global__ void __launch_bounds__(256, MINB) preprocess_count_kernel(const float4* __restrict__ vertices,
                                                                const int* __restrict__ indices,
                                                                const float* __restrict__ colors,
                                                                const float* __restrict__ opacities, int T, int W, int H,
@@ -570,7 +576,7 @@ constexpr int kEmitThreads = 256;
 // DIRECT: the tile offsets are known already; every entry takes the next free slot of its tile
 // (`tile_cursor`, arrival order) and is stored there as (ordered depth << 32 | triangle), ready for the
 // per-tile sort.  `keys` is that array, `ids` is unused.
-// CULL (with DIRECT): pairs that preprocess_count_kernel<true> did not count are skipped by the same test.
+// CULL (with DIRECT): pairs that the culling preprocess_count_kernel did not count are skipped by the same test.
 template <bool DIRECT, bool CULL>
 __global__ void __launch_bounds__(kEmitThreads) emit_keys_kernel(const float4* __restrict__ vertices,
                                                                  const int* __restrict__ indices, int T, int W, int H,
@@ -637,9 +643,12 @@ __global__ void __launch_bounds__(kEmitThreads) emit_keys_kernel(const float4* _
         if (CULL && !rect_may_cover(s_mat[lo].m, tile_pixel_rect(tx, ty, W, H, tw, th))) continue;
         const TriXYZ v = {tr.ax, tr.ay, tr.az, tr.bx, tr.by, tr.bz, tr.cx, tr.cy, tr.cz};
         const Plane pl = {tr.A, tr.B, tr.C};
+        // DIRECT: the slot does not depend on the key, so its atomic (a round trip to L2) is issued first and
+        // travels while the polygon is clipped
+        uint32_t pos = 0;
+        if (DIRECT) pos = atomicAdd(&tile_cursor[ty * tiles_x + tx], 1u);
         const float depth = tile_key(v, pl, tx, ty, W, H, tw, th);
         if (DIRECT) {
-            const uint32_t pos = atomicAdd(&tile_cursor[ty * tiles_x + tx], 1u);
             if (pos < capacity) keys[pos] = ((uint64_t)float_to_ordered(depth) << 32) | (uint32_t)(t0 + lo);
             continue;
         }
@@ -736,14 +745,18 @@ int preprocess_scan(const float* vertices, const int32_t* indices, const float* 
                                  tri_offsets + T + 1, (uint32_t*)scratch + 2, tri_offsets + T,
                                  by_last_cta ? tile_order : nullptr};
     TG_REQUIRE(!cull || by_last_cta, "tile culling is limited to 65536 tiles");
-    if (cull)
-        tg::preprocess_count_kernel<true><<<(T + 255) / 256, 256, 0, stream>>>(
-            (const float4*)vertices, indices, colors, opacities, T, W, H, tw, th, tiles_x, tiles_y, (float4*)tri_geo,
-            (float4*)tri_attr, tri_offsets, bin, packed ? 1 : 0);
-    else
-        tg::preprocess_count_kernel<false><<<(T + 255) / 256, 256, 0, stream>>>(
-            (const float4*)vertices, indices, colors, opacities, T, W, H, tw, th, tiles_x, tiles_y, (float4*)tri_geo,
-            (float4*)tri_attr, tri_offsets, bin, packed ? 1 : 0);
+    const int grid = (T + 255) / 256;
+    const bool one_wave = grid <= 148 * 6;      // all CTAs resident at once at six per SM
+#define TG_LAUNCH_PREPROCESS(CULLV, MINBV)                                                                             \
+    tg::preprocess_count_kernel<CULLV, MINBV><<<grid, 256, 0, stream>>>(                                               \
+        (const float4*)vertices, indices, colors, opacities, T, W, H, tw, th, tiles_x, tiles_y, (float4*)tri_geo,      \
+        (float4*)tri_attr, tri_offsets, bin, packed ? 1 : 0)
+    if (cull) {
+        if (one_wave) TG_LAUNCH_PREPROCESS(true, 6); else TG_LAUNCH_PREPROCESS(true, TG_PREPROCESS_MINB_LARGE);
+    } else {
+        if (one_wave) TG_LAUNCH_PREPROCESS(false, 6); else TG_LAUNCH_PREPROCESS(false, TG_PREPROCESS_MINB_LARGE);
+    }
+#undef TG_LAUNCH_PREPROCESS
     TG_LAUNCH_CHECK("preprocess_count_kernel");
     if (!by_last_cta) {
         // counts -> offsets by the device-wide scan, then the cursors start at the offsets

@@ -23,7 +23,7 @@
 
 namespace tg {
 
-constexpr int kChunk = 64;   // records staged per step: 64 x 64 B = 4 KB
+constexpr int kChunk = 64;   // records staged per step (64 bytes each, 80 bytes apart in shared memory)
 
 struct BlendParams {
     const float4* geo;
