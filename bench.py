@@ -615,7 +615,8 @@ def main() -> None:
     # ---- end to end from host buffers through the public API -----------------------------------------
     # Every step copies all of its inputs from pinned host memory (shared mesh attributes once, per-view
     # vertices and target for each view) and copies the loss and the summed gradients back.  The copies of
-    # view b+1 run on a second stream while view b renders.  Targets travel as 8-bit RGBA (what an image on
+    # view b+1 run on a second stream while view b renders; the loop is measured both with and without overlap
+    # between consecutive steps (see e2e_loop).  Targets travel as 8-bit RGBA (what an image on
     # the host is; the loss reads value / 255): a quarter of the bytes of a float32 target.  The pinned buffers
     # are allocated from the NUMA node the GPU hangs off.
     old_affinity = bind_host_to_gpu_numa_node(local_rank)
@@ -623,50 +624,104 @@ def main() -> None:
     hp = torch.from_numpy(scene.meta["mesh"].points).pin_memory() if camera_ring else None
     hv = [] if camera_ring else [torch.from_numpy(x).pin_memory() for x in views_np]   # camera matrices stay on the host
     ht = [torch.from_numpy(np.round(x * 255).astype(np.uint8)).pin_memory() for x in targets_np]
-    out_g = torch.empty_like(grads.flat, device="cpu").pin_memory()      # gradients and, last element, the loss
+    out_g = [torch.empty_like(grads.flat, device="cpu").pin_memory() for _ in range(2)]   # gradients and, last, the loss
     if old_affinity is not None:
         os.sched_setaffinity(0, old_affinity)
     h2d = sum(t.numel() * t.element_size() for t in [hi, hc, ho] + hv + ht + ([hp] if camera_ring else []))
-    d2h = out_g.numel() * 4
+    d2h = out_g[0].numel() * 4
     copy_stream = torch.cuda.Stream(device=dev)
+    d2h_stream = torch.cuda.Stream(device=dev)
     main_stream = torch.cuda.current_stream(dev)
+    snapshot = [torch.empty_like(grads.flat) for _ in range(2)]
 
-    def e2e_step():
+    def stage_inputs():
+        """Queue one step's host->device copies on the copy stream: the shared mesh attributes, then per view its
+        vertices (or nothing: camera matrices are passed by value) and its target, each view with an event."""
         staged = []
         with torch.cuda.stream(copy_stream):
+            shared = [hi.to(dev, non_blocking=True), hc.to(dev, non_blocking=True), ho.to(dev, non_blocking=True)]
             if camera_ring:
-                batch.points = hp.to(dev, non_blocking=True)
-            batch.i = hi.to(dev, non_blocking=True)
-            batch.c = hc.to(dev, non_blocking=True)
-            batch.o = ho.to(dev, non_blocking=True)
+                shared.append(hp.to(dev, non_blocking=True))
             for b in range(B):
                 vb = views_np[b] if camera_ring else hv[b].to(dev, non_blocking=True)
                 tb = ht[b].to(dev, non_blocking=True)
                 ev = torch.cuda.Event()
                 ev.record(copy_stream)
                 staged.append((vb, tb, ev))
-        batch.run(staged)        # each view waits for its own copies (queued after the shared ones)
-        for t in (batch.i, batch.c, batch.o) + ((batch.points,) if camera_ring else ()):
-            t.record_stream(main_stream)
-            for st in batch.side_streams:
-                t.record_stream(st)
+        return shared, staged
+
+    def e2e_loop(n: int, pipelined: bool) -> float:
+        """n steps from host buffers; seconds per step by the host clock, everything delivered at the end.
+
+        Not pipelined: a step's copies start once the step before has delivered its result to the host.
+        Pipelined (two sets of buffers, the loop a trainer with a prefetching loader runs): the copies of step k+1
+        are queued before step k is launched, and step k's result is copied to the host on a stream of its own while
+        step k+1 renders; the host reads it one step late.  Either way every step copies all of its inputs and
+        returns all of its gradients inside the timed region."""
+        barrier()
+        t0 = time.perf_counter()
+        delivered = [None, None]
+        pending = stage_inputs() if pipelined else None
+        for k in range(n):
+            shared, staged = pending if pipelined else stage_inputs()
+            pending = stage_inputs() if pipelined and k + 1 < n else None
+            batch.i, batch.c, batch.o = shared[:3]
+            if camera_ring:
+                batch.points = shared[3]
+            batch.run(staged)        # each view waits for its own copies (queued after the shared ones)
+            for t in shared:
+                t.record_stream(main_stream)
+                for st in batch.side_streams:
+                    t.record_stream(st)
+            if world > 1:
+                Vw.allreduce_gradients(grads)
+            if not pipelined:
+                out_g[0].copy_(grads.flat, non_blocking=True)
+                main_stream.synchronize()
+                continue
+            slot = k % 2
+            if delivered[slot] is not None:
+                delivered[slot].synchronize()           # the host has read step k-2 before its buffers are reused
+            snapshot[slot].copy_(grads.flat)
+            ready = torch.cuda.Event()
+            ready.record(main_stream)
+            d2h_stream.wait_event(ready)
+            with torch.cuda.stream(d2h_stream):
+                out_g[slot].copy_(snapshot[slot], non_blocking=True)
+                delivered[slot] = torch.cuda.Event()
+                delivered[slot].record(d2h_stream)
+            if delivered[1 - slot] is not None:
+                delivered[1 - slot].synchronize()       # result of the step before, read while this one renders
+        for ev in delivered:
+            if ev is not None:
+                ev.synchronize()
+        barrier()
+        dt = torch.tensor([(time.perf_counter() - t0) / n], dtype=torch.float64, device=dev)
         if world > 1:
-            Vw.allreduce_gradients(grads)
-        out_g.copy_(grads.flat, non_blocking=True)
-        main_stream.synchronize()
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        return float(dt.item())
+
+    def copies_alone_gbs() -> float:
+        """Host->device rate of one step's input copies with nothing else running (what bounds the pipelined loop
+        when the step's rendering takes less time than its copies)."""
+        best = float("inf")
+        for _ in range(4):
+            barrier()
+            t0 = time.perf_counter()
+            kept = stage_inputs()
+            copy_stream.synchronize()
+            best = min(best, time.perf_counter() - t0)
+            del kept
+        return h2d / best / 1e9
 
     e2e_steps = max(3, min(args.steps, 20))
-    for _ in range(2):
-        e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
-    barrier()
-    e2e_dt = torch.tensor([(time.perf_counter() - t0) / e2e_steps], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(e2e_dt, op=dist.ReduceOp.MAX)
-    e2e_value = W * H * B * world / float(e2e_dt.item()) / 1e6
+    h2d_gbs = copies_alone_gbs()
+    e2e_loop(2, False)
+    e2e_serial_s = e2e_loop(e2e_steps, False)
+    e2e_loop(3, True)
+    e2e_s = e2e_loop(e2e_steps, True)
+    e2e_value = W * H * B * world / e2e_s / 1e6
+    e2e_serial_value = W * H * B * world / e2e_serial_s / 1e6
 
     # ---- per-kernel timing for the roofline (stage entry points, CUDA events, L2 flushed) ------------
     stages = measure_stages(torch, St, scene, verts_np, flush, reps=max(5, min(20, args.steps)))
@@ -694,7 +749,11 @@ def main() -> None:
         "ms_per_view": ms_per_step / B,
         "wall_s_timed_region": t_wall,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": float(e2e_dt.item()) * 1e3},
+                "ms_per_step": e2e_s * 1e3, "h2d_gbs_copies_alone": h2d_gbs,
+                "pipeline": "two buffer sets: step k+1's inputs are copied while step k renders, step k's gradients "
+                            "are read back while step k+1 renders; every step's copies are inside the timed region",
+                "unpipelined": {"value": e2e_serial_value, "ms_per_step": e2e_serial_s * 1e3,
+                                "note": "a step's copies start after the step before has delivered its result"}},
         "gpu_launches": int(n_launch),
         "clocks": clk.summary(),
         "roofline": roofline,
