@@ -228,28 +228,38 @@ __device__ __forceinline__ int select_sweep(const BlendParams& P, const TileCtx&
         float cut = go ? ((found == bs) ? dl[bs - 1] : INFINITY) : -INFINITY;
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) cut = fmaxf(cut, __shfl_xor_sync(0xffffffffu, cut, d));
-        unsigned long long mask = warp_cull(s_geo, n, c.rect, cut);
-        while (mask) {
-            const int r = __ffsll((long long)mask) - 1;
-            mask &= mask - 1;
-            if (!go) continue;
-            const float* g = reinterpret_cast<const float*>(s_geo + kStagedQuads * r);    // broadcast word loads
-            const Bary b = apply_bary(g, c.px, c.py);
-            if (!covered(b)) continue;
-            const float d = interp_rn(b, g[9], g[10], g[11], g[12], g[13], g[14]);
-            const int j = first + r;
-            if (d < lastDepth) continue;
-            if (d == lastDepth && j <= lastJ) continue;
-            if (found == bs && d >= dl[bs - 1]) continue;
-            int pos = (found < bs) ? found : (bs - 1);
-            while (pos > 0 && d < dl[pos - 1]) {
-                dl[pos] = dl[pos - 1];
-                jl[pos] = jl[pos - 1];
-                pos--;
+        const unsigned long long mask = warp_cull(s_geo, n, c.rect, cut);
+        // the two 32-bit halves of the mask one after the other: bit scans on 32-bit words are cheaper than on the
+        // 64-bit one, and this loop runs once per surviving record and warp
+#pragma unroll 1
+        for (int half = 0; half < 2; half++) {
+            unsigned bits = half ? (unsigned)(mask >> 32) : (unsigned)mask;
+            while (bits) {
+                const int r = __ffs((int)bits) - 1 + 32 * half;
+                bits &= bits - 1;
+                if (!go) continue;
+                // all lanes read the same record: broadcast 16-byte loads
+                const float4* rec = s_geo + kStagedQuads * r;
+                const float4 q0 = rec[0], q1 = rec[1], q2 = rec[2];
+                const float m[9] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w, q2.x};
+                const Bary b = apply_bary(m, c.px, c.py);
+                if (!covered(b)) continue;
+                const float4 q3 = rec[3];
+                const float d = interp_rn(b, q2.y, q2.z, q2.w, q3.x, q3.y, q3.z);
+                const int j = first + r;
+                if (d < lastDepth) continue;
+                if (d == lastDepth && j <= lastJ) continue;
+                if (found == bs && d >= dl[bs - 1]) continue;
+                int pos = (found < bs) ? found : (bs - 1);
+                while (pos > 0 && d < dl[pos - 1]) {
+                    dl[pos] = dl[pos - 1];
+                    jl[pos] = jl[pos - 1];
+                    pos--;
+                }
+                dl[pos] = d;
+                jl[pos] = j;
+                if (found < bs) found++;
             }
-            dl[pos] = d;
-            jl[pos] = j;
-            if (found < bs) found++;
         }
     }
     return found;
@@ -335,17 +345,21 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 256 ? 5 : 1) blend_forward_kerne
             __syncthreads();
             // a warp whose lanes have all stopped skips the chunk
             if (!__all_sync(0xffffffffu, done)) {
-                unsigned long long mask = warp_cull(s_geo, n, c.rect);
-                while (mask) {
-                    const int r = __ffsll((long long)mask) - 1;
-                    mask &= mask - 1;
-                    if (done) continue;
-                    if (!(acc.alpha > P.thr && acc.blended < P.max_layers)) { done = true; continue; }
-                    const float* g = reinterpret_cast<const float*>(s_geo + kStagedQuads * r);
-                    const Bary b = apply_bary(g, c.px, c.py);
-                    if (!covered(b)) continue;
-                    const AttrRec a = load_attr<false>(P.attr, s_id[r]);
-                    blend_one(b, g + 12, a, acc);
+                const unsigned long long mask = warp_cull(s_geo, n, c.rect);
+#pragma unroll 1
+                for (int half = 0; half < 2; half++) {      // 32-bit bit scans, as in select_sweep
+                    unsigned bits = half ? (unsigned)(mask >> 32) : (unsigned)mask;
+                    while (bits) {
+                        const int r = __ffs((int)bits) - 1 + 32 * half;
+                        bits &= bits - 1;
+                        if (done) continue;
+                        if (!(acc.alpha > P.thr && acc.blended < P.max_layers)) { done = true; continue; }
+                        const float* g = reinterpret_cast<const float*>(s_geo + kStagedQuads * r);
+                        const Bary b = apply_bary(g, c.px, c.py);
+                        if (!covered(b)) continue;
+                        const AttrRec a = load_attr<false>(P.attr, s_id[r]);
+                        blend_one(b, g + 12, a, acc);
+                    }
                 }
                 if (!(acc.alpha > P.thr && acc.blended < P.max_layers)) done = true;
             }
