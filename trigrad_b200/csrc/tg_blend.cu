@@ -237,13 +237,14 @@ __device__ __forceinline__ int select_sweep(const BlendParams& P, const TileCtx&
             while (bits) {
                 const int r = __ffs((int)bits) - 1 + 32 * half;
                 bits &= bits - 1;
-                if (!go) continue;
                 // all lanes read the same record: broadcast 16-byte loads
                 const float4* rec = s_geo + kStagedQuads * r;
                 const float4 q0 = rec[0], q1 = rec[1], q2 = rec[2];
                 const float m[9] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w, q2.x};
                 const Bary b = apply_bary(m, c.px, c.py);
-                if (!covered(b)) continue;
+                // one minimum instead of three comparisons: fminf skips NaN operands, so the result is below
+                // kEffZero exactly when one of the three is (and NaN, i.e. "covered", when all three are NaN)
+                if (!go || fminf(fminf(b.x, b.y), b.z) < kEffZero) continue;
                 const float4 q3 = rec[3];
                 const float d = interp_rn(b, q2.y, q2.z, q2.w, q3.x, q3.y, q3.z);
                 const int j = first + r;
