@@ -141,8 +141,9 @@ __device__ __forceinline__ TileCtx tile_context(const BlendParams& P, float* s_c
     c.ix = tx * P.tw + lx;
     c.iy = ty * P.th + ly;
     c.active = (int)threadIdx.x < P.tw * P.th && c.ix < P.W && c.iy < P.H;
-    c.start = P.offsets[c.tile];
-    c.end = P.offsets[c.tile + 1];
+    // (a caller that walks no tile list - the queued backward, whose blocks need not be the forward's tiles - passes none)
+    c.start = P.offsets ? P.offsets[c.tile] : 0;
+    c.end = P.offsets ? P.offsets[c.tile + 1] : 0;
     __syncthreads();
     c.px = s_coord[min(lx, P.tw - 1)];
     c.py = s_coord[P.tw + min(ly, P.th - 1)];
@@ -813,11 +814,11 @@ __device__ __noinline__ void backward_rounds_direct(const BlendParams& P, float 
 }
 
 template <int MAXT>
-__global__ void __launch_bounds__(MAXT, 4) blend_backward_queued_kernel(BlendParams P, BackwardIn in,
+__global__ void __launch_bounds__(MAXT, 1024 / MAXT) blend_backward_queued_kernel(BlendParams P, BackwardIn in,
                                                                         const int* __restrict__ sel,
                                                                         float4* __restrict__ gpack) {
-    static_assert(MAXT == 256, "the per-warp queues are sized for 8 warps");
-    __shared__ float s_coord[kMaxTileCoords];
+    static_assert(MAXT % 32 == 0 && MAXT <= 256, "one queue per warp, at most 8 warps");
+    __shared__ float s_coord[MAXT + 2];      // tile_w + tile_h <= tile_w * tile_h + 1 <= MAXT + 1
     __shared__ float s_queue[MAXT / 32][kQueueFields][kQueueSlots];
     const TileCtx c = tile_context(P, s_coord);
     PixelGrad pg;
@@ -1340,7 +1341,18 @@ static int backward_impl(const float* tri_geo, const float* tri_attr, const int3
                                ends, target_u8 ? nullptr : (const float4*)l2_target, l2_grad_scale, partials,
                                target_u8 ? (const uchar4*)l2_target : nullptr};
     if (threads <= 256) {
-        if (saved) tg::blend_backward_queued_kernel<256><<<tiles, threads, 0, s>>>(P, in, selection, gpack);
+        if (saved) {
+            // The queued kernel walks the per-pixel selection, not the tile lists, so its blocks need not be the
+            // forward's tiles: 16x8 pixels (four warps) finish more evenly than whole tiles do, and a block's
+            // registers come free only when its slowest warp is done (config 3: 179 -> 173 µs; 64 threads the
+            // same, 32 threads slower again).
+            tg::BlendParams Q = P;
+            Q.tw = 16; Q.th = 8;
+            Q.tiles_x = (W + Q.tw - 1) / Q.tw;
+            Q.offsets = nullptr; Q.ids = nullptr; Q.order = nullptr;
+            const int blocks = Q.tiles_x * ((H + Q.th - 1) / Q.th);
+            tg::blend_backward_queued_kernel<128><<<blocks, 128, 0, s>>>(Q, in, selection, gpack);
+        }
         else if (per_pixel_sort) tg::blend_backward_kernel<true, 256><<<tiles, threads, 0, s>>>(P, in, gpack);
         else tg::blend_backward_kernel<false, 256><<<tiles, threads, 0, s>>>(P, in, gpack);
     } else {
