@@ -217,6 +217,7 @@ __device__ __forceinline__ unsigned long long warp_cull(const float4* s_geo, int
 __device__ __forceinline__ int select_sweep(const BlendParams& P, const TileCtx& c, bool go, int bs, float lastDepth,
                                             int lastJ, float* dl, int* jl, float4* s_geo, int* s_id) {
     int found = 0;
+    float dfar = -INFINITY;     // dl[found - 1]; -inf while the batch is empty, so the first fragment is appended
     const bool warp_go = __any_sync(0xffffffffu, go);
     for (int first = c.start; first < c.end; first += kChunk) {
         const int n = min(kChunk, c.end - first);
@@ -226,7 +227,7 @@ __device__ __forceinline__ int select_sweep(const BlendParams& P, const TileCtx&
         if (!warp_go) continue;
         // Once every collecting lane of the warp holds a full batch, a record whose depth lower bound is
         // not below the farthest kept depth of any lane cannot enter any lane's batch (ties lose).
-        float cut = go ? ((found == bs) ? dl[bs - 1] : INFINITY) : -INFINITY;
+        float cut = go ? ((found == bs) ? dfar : INFINITY) : -INFINITY;
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) cut = fmaxf(cut, __shfl_xor_sync(0xffffffffu, cut, d));
         const unsigned long long mask = warp_cull(s_geo, n, c.rect, cut);
@@ -251,7 +252,16 @@ __device__ __forceinline__ int select_sweep(const BlendParams& P, const TileCtx&
                 const int j = first + r;
                 if (d < lastDepth) continue;
                 if (d == lastDepth && j <= lastJ) continue;
-                if (found == bs && d >= dl[bs - 1]) continue;
+                // the farthest kept depth stays in a register: lists come roughly front to back, so most
+                // fragments go to the end of the batch (ties keep list order) or, once it is full, nowhere
+                if (d >= dfar) {
+                    if (found == bs) continue;
+                    dl[found] = d;
+                    jl[found] = j;
+                    dfar = d;
+                    found++;
+                    continue;
+                }
                 int pos = (found < bs) ? found : (bs - 1);
                 while (pos > 0 && d < dl[pos - 1]) {
                     dl[pos] = dl[pos - 1];
@@ -261,6 +271,7 @@ __device__ __forceinline__ int select_sweep(const BlendParams& P, const TileCtx&
                 dl[pos] = d;
                 jl[pos] = j;
                 if (found < bs) found++;
+                dfar = dl[found - 1];
             }
         }
     }
