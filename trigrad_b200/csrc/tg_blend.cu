@@ -176,6 +176,27 @@ __device__ __forceinline__ void stage_chunk(const BlendParams& P, int first, int
     }
 }
 
+// The attribute quads the forward blend needs (opacities, colours, 1/w: the first four of the six), staged next to
+// the geometry when the whole tile list fits in one chunk: the blend of the selected fragments then reads its
+// records from shared memory instead of gathering 128 bytes per fragment and lane through L1.  Same 80-byte pitch.
+__device__ __forceinline__ void stage_attr_chunk(const BlendParams& P, int first, int n, float4* s_attr) {
+    for (int i = threadIdx.x; i < n * 4; i += blockDim.x) {
+        const int rec = i >> 2, q = i & 3;
+        const int id = P.ids[first + rec];
+        s_attr[staged_quad(rec, q)] = __ldg(P.attr + kAttrQuads * (size_t)id + q);
+    }
+}
+__device__ __forceinline__ AttrRec staged_attr(const float4* s_attr, int r) {
+    const float4 q0 = s_attr[staged_quad(r, 0)], q1 = s_attr[staged_quad(r, 1)], q2 = s_attr[staged_quad(r, 2)],
+                 q3 = s_attr[staged_quad(r, 3)];
+    AttrRec a;
+    a.o[0] = q0.x; a.o[1] = q0.y; a.o[2] = q0.z;
+    a.c[0] = q0.w; a.c[1] = q1.x; a.c[2] = q1.y; a.c[3] = q1.z; a.c[4] = q1.w; a.c[5] = q2.x; a.c[6] = q2.y; a.c[7] = q2.z;
+    a.c[8] = q2.w;
+    a.iw[0] = q3.x; a.iw[1] = q3.y; a.iw[2] = q3.z;
+    return a;
+}
+
 // A staged geometry record in registers (only the parts a caller uses are actually loaded).
 struct StagedGeo {
     float m[9];
@@ -214,8 +235,10 @@ __device__ __forceinline__ unsigned long long warp_cull(const float4* s_geo, int
 // One selection sweep over the whole tile list (select_next_k_in_tile, reference render.cu:375-415):
 // keeps the `bs` covered fragments smallest in (depth, j) among those after (lastDepth, lastJ).
 // All threads of the CTA must call it; `go` says whether this thread collects.
+// `s_attr`, when given, receives the attribute quads of the chunk as well (stage_attr_chunk).
 __device__ __forceinline__ int select_sweep(const BlendParams& P, const TileCtx& c, bool go, int bs, float lastDepth,
-                                            int lastJ, float* dl, int* jl, float4* s_geo, int* s_id) {
+                                            int lastJ, float* dl, int* jl, float4* s_geo, int* s_id,
+                                            float4* s_attr = nullptr) {
     int found = 0;
     float dfar = -INFINITY;     // dl[found - 1]; -inf while the batch is empty, so the first fragment is appended
     const bool warp_go = __any_sync(0xffffffffu, go);
@@ -223,6 +246,7 @@ __device__ __forceinline__ int select_sweep(const BlendParams& P, const TileCtx&
         const int n = min(kChunk, c.end - first);
         __syncthreads();
         stage_chunk(P, first, n, s_geo, s_id);
+        if (s_attr) stage_attr_chunk(P, first, n, s_attr);
         __syncthreads();
         if (!warp_go) continue;
         // Once every collecting lane of the warp holds a full batch, a record whose depth lower bound is
@@ -298,6 +322,7 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 256 ? 5 : 1) blend_forward_kerne
                                                              float* __restrict__ depthmap, float* __restrict__ final_w,
                                                              int* __restrict__ ends, int* __restrict__ sel) {
     __shared__ float4 s_geo[kChunk * kStagedQuads];
+    __shared__ float4 s_attr[SORT ? kChunk * kStagedQuads : 1];
     __shared__ int s_id[kChunk];
     __shared__ float s_coord[kMaxTileCoords];
     const int this_tile = tile_of_block(P);
@@ -328,10 +353,25 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 256 ? 5 : 1) blend_forward_kerne
             const bool go = want && acc.alpha > P.thr && acc.blended < P.max_layers;
             if (!__syncthreads_or(go)) break;
             const int bs = min(kBatchLayers, P.max_layers - acc.blended);
-            const int found = select_sweep(P, c, go, bs, lastDepth, lastJ, dl, jl, s_geo, s_id);
+            // A list of one chunk is still in shared memory after the sweep, and then its attribute quads were staged
+            // with it (while the geometry loads were in flight anyway): the blend reads its records from shared memory
+            // instead of gathering 128 bytes per fragment and lane through L1.  (Deciding after the sweep, from the
+            // number of pixels that found something, whether staging the attributes pays was slower: the loads then
+            // wait alone behind a barrier.)
+            const bool one_chunk = c.end - c.start <= kChunk;
+            const int found = select_sweep(P, c, go, bs, lastDepth, lastJ, dl, jl, s_geo, s_id, one_chunk ? s_attr : nullptr);
             if (go) {
                 const int n = min(found, P.max_layers - acc.blended);
                 for (int i = 0; i < n; i++) {
+                    if (one_chunk) {
+                        const int r = jl[i] - c.start;
+                        const StagedGeo g = load_staged(s_geo, r);
+                        const Bary b = apply_bary(g.m, c.px, c.py);
+                        const AttrRec a = staged_attr(s_attr, r);
+                        if (sel) sel[(size_t)acc.blended * plane + index] = s_id[r];
+                        blend_one(b, g.w, a, acc);
+                        continue;
+                    }
                     const int id = P.ids[jl[i]];
                     float m[9], w[3];
                     load_geo(P.geo, id, m, w);
