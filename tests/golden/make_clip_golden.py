@@ -45,7 +45,7 @@ def seeded_inputs():
     return clip, idx, colors, opac
 
 
-def main(reference_root="/root/reference"):
+def main(reference_root=os.environ.get("TRIGRAD_REFERENCE", os.path.join(os.sep, "root", "reference"))):
     split = reference_split_clipped(reference_root)
     clip, idx, colors, opac = seeded_inputs()
     tc = torch.tensor(clip, requires_grad=True)
