@@ -129,11 +129,15 @@ __device__ __forceinline__ TileCtx tile_context(const BlendParams& P, float* s_c
     for (int i = threadIdx.x; i < P.tw + P.th; i += blockDim.x)
         s_coord[i] = (i < P.tw) ? pixel_coord(tx * P.tw + i, P.W) : pixel_coord(ty * P.th + (i - P.tw), P.H);
     int lx, ly;
-    if ((P.tw & 7) == 0 && (P.th & 3) == 0) {
+    const bool blocks = (P.tw & 7) == 0 && (P.th & 3) == 0;
+    int bx0 = 0, by0 = 0;
+    if (blocks) {
         // a warp owns an 8x4 block of the tile: compact footprint, fewer records survive its cull
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, bpr = P.tw >> 3;
-        lx = (warp % bpr) * 8 + (lane & 7);
-        ly = (warp / bpr) * 4 + (lane >> 3);
+        bx0 = (warp % bpr) * 8;
+        by0 = (warp / bpr) * 4;
+        lx = bx0 + (lane & 7);
+        ly = by0 + (lane >> 3);
     } else {
         lx = threadIdx.x % P.tw;
         ly = threadIdx.x / P.tw;
@@ -147,6 +151,16 @@ __device__ __forceinline__ TileCtx tile_context(const BlendParams& P, float* s_c
     __syncthreads();
     c.px = s_coord[min(lx, P.tw - 1)];
     c.py = s_coord[P.tw + min(ly, P.th - 1)];
+    if (blocks) {
+        // the coordinates grow with the index, so the extent of the block's pixels inside the image is given by
+        // its first and last valid column and row
+        const int nx = min(8, P.W - tx * P.tw - bx0), ny = min(4, P.H - ty * P.th - by0);
+        if (nx > 0 && ny > 0 && (int)threadIdx.x < P.tw * P.th)
+            c.rect = {s_coord[bx0], s_coord[bx0 + nx - 1], s_coord[P.tw + by0], s_coord[P.tw + by0 + ny - 1]};
+        else
+            c.rect = {INFINITY, -INFINITY, INFINITY, -INFINITY};
+        return c;
+    }
     float x0 = c.active ? c.px : INFINITY, x1 = c.active ? c.px : -INFINITY;
     float y0 = c.active ? c.py : INFINITY, y1 = c.active ? c.py : -INFINITY;
 #pragma unroll
