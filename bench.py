@@ -402,7 +402,8 @@ def cfg4_sharded_block(torch, dist, Vw, dev, rank: int, world: int, n_streams: i
     pvs = scene.meta["pvs"]
     mine = list(Vw.shard_views(len(pvs), rank, world))
     n_s = min(n_streams, max(1, len(mine)))
-    batch = ViewBatch(torch, Vw, scene, dev, n_s, host_threads=n_s)
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    batch = ViewBatch(torch, Vw, scene, dev, n_s, host_threads=max(1, min(n_s, cores // max(1, world))))
     W, H = scene.width, scene.height
     rng = np.random.default_rng(100 + rank)
     # a handful of distinct targets reused round-robin (64 full-size fp32 targets would be 2 GB of nothing new)
@@ -560,7 +561,9 @@ def main() -> None:
     verts_np = S_project(scene, views_np[0]) if camera_ring else views_np[0]
 
     n_streams = max(1, min(args.streams, B))
-    host_threads = args.host_threads if args.host_threads > 0 else n_streams
+    # one issuing thread per stream, but no more threads than this rank's share of the host cores
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    host_threads = args.host_threads if args.host_threads > 0 else max(1, min(n_streams, cores // max(1, world)))
     batch = ViewBatch(torch, Vw, scene, dev, n_streams, one_kernel=args.one_kernel, host_threads=host_threads)
     grads = batch.grads
     pos_comp = batch.pos_comp

@@ -2,6 +2,8 @@
 #include <atomic>
 #include <chrono>
 
+#include <sched.h>
+
 #include "tg_radix.cuh"
 
 namespace {
@@ -134,6 +136,9 @@ static int build_tile_lists(const float* vertices, const int32_t* indices, const
 #if defined(__x86_64__)
             __builtin_ia32_pause();
 #endif
+            // after a short pure spin the core is offered to other runnable threads between looks (several ranks or
+            // issuing threads per core: a waiter must not hold up the thread whose launches it is waiting behind)
+            if (spins > 2048) sched_yield();
             if ((spins & 0xfffu) == 0 && std::chrono::steady_clock::now() - t0 > std::chrono::milliseconds(200)) break;
         }
         std::atomic_thread_fence(std::memory_order_acquire);
