@@ -590,7 +590,7 @@ __global__ void __launch_bounds__(kEmitThreads) emit_keys_kernel(const float4* _
     __shared__ EmitTri s_tri[kEmitThreads];
     __shared__ EmitMat s_mat[CULL ? kEmitThreads : 1];
     __shared__ uint32_t s_off[kEmitThreads + 1];
-    __shared__ uint32_t s_hist[kMaxPasses * kRadix];
+    __shared__ uint32_t s_hist[DIRECT ? 1 : kMaxPasses * kRadix];     // digit counts of the radix route only
     __shared__ uint32_t s_warp_tot[kSortWarps];
     __shared__ bool s_last;
     const int tid = threadIdx.x;
