@@ -206,7 +206,7 @@ int tg_render_forward(const float* vertices, const int32_t* indices, const float
                               sorted_ids, list_capacity, offsets, workspace, workspace_bytes, info_host, flags, timer, &device_status, &tile_order, s);
     if (st) return st;
     timer.mark();                                                    // [4] start of "rasterization"
-    tg_host::set_tile_order(tile_order);
+    tg_host::set_tile_order(tile_order, info_host[1]);      // with the longest list: long lists are streamed
     st = tg_blend_forward(tri_geo, tri_attr, sorted_ids, offsets, W, H, tw, th, thr, per_pixel_sort, max_layers, image,
                           depthmap, final_weights, ends, selection, stream);
     tg_host::set_tile_order(nullptr);

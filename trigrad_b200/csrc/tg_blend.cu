@@ -246,29 +246,74 @@ __device__ __forceinline__ unsigned long long warp_cull(const float4* s_geo, int
     return (unsigned long long)m0 | ((unsigned long long)m1 << 32);
 }
 
+// 16-byte asynchronous copy global -> shared (completion awaited with cp_async_wait_all by the issuing thread, then
+// made visible to the CTA by a barrier).
+__device__ __forceinline__ void cp_async16(float4* smem_dst, const float4* gmem_src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)),
+                 "l"(gmem_src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 // One selection sweep over the whole tile list (select_next_k_in_tile, reference render.cu:375-415):
 // keeps the `bs` covered fragments smallest in (depth, j) among those after (lastDepth, lastJ).
 // All threads of the CTA must call it; `go` says whether this thread collects.
 // `s_attr`, when given, receives the attribute quads of the chunk as well (stage_attr_chunk).
+// `s_geo2` / `s_id2`, when given, are a second pair of staging buffers: a list of more than one chunk is then streamed
+// (CTAs of 256 threads: one quad per thread and chunk) - the records of chunk k + 1 travel by asynchronous copies
+// while chunk k is processed, their ids having been fetched one iteration earlier still, and one barrier per chunk
+// replaces the two of the load-then-process loop.
+// (STREAM is a template parameter so that callers which never stream carry none of its state.)
+template <bool STREAM = false>
 __device__ __forceinline__ int select_sweep(const BlendParams& P, const TileCtx& c, bool go, int bs, float lastDepth,
                                             int lastJ, float* dl, int* jl, float4* s_geo, int* s_id,
-                                            float4* s_attr = nullptr) {
+                                            float4* s_attr = nullptr, float4* s_geo2 = nullptr, int* s_id2 = nullptr) {
     int found = 0;
     float dfar = -INFINITY;     // dl[found - 1]; -inf while the batch is empty, so the first fragment is appended
     const bool warp_go = __any_sync(0xffffffffu, go);
-    for (int first = c.start; first < c.end; first += kChunk) {
+    const bool streamed = STREAM && s_geo2 != nullptr && c.end - c.start > kChunk && blockDim.x == 4 * kChunk;
+    const int my_rec = threadIdx.x >> 2, my_q = threadIdx.x & 3;
+    int id_ahead = -1;          // streamed: id of this thread's record in the chunk after the one being copied
+    if (streamed) {
+        __syncthreads();        // whoever read the buffers before (an earlier sweep) is done
+        const int id = P.ids[c.start + my_rec];                       // chunk 0 is full: the list is longer
+        if (my_q == 0) s_id[my_rec] = id;
+        cp_async16(s_geo + staged_quad(my_rec, my_q), P.geo + 4 * (size_t)id + my_q);
+        cp_async_commit();
+        if (my_rec < c.end - c.start - kChunk) id_ahead = P.ids[c.start + kChunk + my_rec];
+    }
+    int chunk = 0;
+    for (int first = c.start; first < c.end; first += kChunk, chunk++) {
         const int n = min(kChunk, c.end - first);
-        __syncthreads();
-        stage_chunk(P, first, n, s_geo, s_id);
-        if (s_attr) stage_attr_chunk(P, first, n, s_attr);
-        __syncthreads();
+        const float4* geo_now = s_geo;          // the staged records of this chunk
+        if (streamed) {
+            float4* other_geo = s_geo2;         // buffers the next chunk is copied into
+            int* other_id = s_id2;
+            if (chunk & 1) { geo_now = s_geo2; other_geo = s_geo; other_id = s_id; }
+            cp_async_wait_all();
+            __syncthreads();    // this chunk has landed for everyone, and everyone has left the chunk before
+            if (first + kChunk < c.end) {
+                if (id_ahead >= 0) {
+                    if (my_q == 0) other_id[my_rec] = id_ahead;
+                    cp_async16(other_geo + staged_quad(my_rec, my_q), P.geo + 4 * (size_t)id_ahead + my_q);
+                }
+                cp_async_commit();
+                const int first2 = first + 2 * kChunk;
+                id_ahead = (first2 < c.end && my_rec < c.end - first2) ? P.ids[first2 + my_rec] : -1;
+            }
+        } else {
+            __syncthreads();
+            stage_chunk(P, first, n, s_geo, s_id);
+            if (s_attr) stage_attr_chunk(P, first, n, s_attr);
+            __syncthreads();
+        }
         if (!warp_go) continue;
         // Once every collecting lane of the warp holds a full batch, a record whose depth lower bound is
         // not below the farthest kept depth of any lane cannot enter any lane's batch (ties lose).
         float cut = go ? ((found == bs) ? dfar : INFINITY) : -INFINITY;
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) cut = fmaxf(cut, __shfl_xor_sync(0xffffffffu, cut, d));
-        const unsigned long long mask = warp_cull(s_geo, n, c.rect, cut);
+        const unsigned long long mask = warp_cull(geo_now, n, c.rect, cut);
         // the two 32-bit halves of the mask one after the other: bit scans on 32-bit words are cheaper than on the
         // 64-bit one, and this loop runs once per surviving record and warp
 #pragma unroll 1
@@ -278,7 +323,7 @@ __device__ __forceinline__ int select_sweep(const BlendParams& P, const TileCtx&
                 const int r = __ffs((int)bits) - 1 + 32 * half;
                 bits &= bits - 1;
                 // all lanes read the same record: broadcast 16-byte loads
-                const float4* rec = s_geo + kStagedQuads * r;
+                const float4* rec = geo_now + kStagedQuads * r;
                 const float4 q0 = rec[0], q1 = rec[1], q2 = rec[2];
                 const float m[9] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w, q2.x};
                 const Bary b = apply_bary(m, c.px, c.py);
@@ -331,13 +376,16 @@ __device__ __forceinline__ void store_pixel(const TileCtx& c, const BlendParams&
 
 // sel: optional [planes][H*W] int32; plane k of a pixel receives the triangle id of its k-th blended
 // fragment (k < ends).  Only written when it is not null (per-pixel mode, max_layers <= 32).
-template <bool SORT, int MAXT>
+// STREAM: lists of more than one chunk are streamed through two staging buffers (select_sweep); instantiated
+// separately because the state it carries costs the one-chunk tiles a few spilled registers.
+template <bool SORT, int MAXT, bool STREAM = false>
 __global__ void __launch_bounds__(MAXT, MAXT <= 256 ? 5 : 1) blend_forward_kernel(BlendParams P, float4* __restrict__ image,
                                                              float* __restrict__ depthmap, float* __restrict__ final_w,
                                                              int* __restrict__ ends, int* __restrict__ sel) {
     __shared__ float4 s_geo[kChunk * kStagedQuads];
-    __shared__ float4 s_attr[SORT ? kChunk * kStagedQuads : 1];
+    __shared__ float4 s_attr[SORT ? kChunk * kStagedQuads : 1];   // one-chunk lists: attributes; longer ones: 2nd buffer
     __shared__ int s_id[kChunk];
+    __shared__ int s_id2[STREAM ? kChunk : 1];
     __shared__ float s_coord[kMaxTileCoords];
     const int this_tile = tile_of_block(P);
     if (P.offsets[this_tile] == P.offsets[this_tile + 1]) {
@@ -373,7 +421,8 @@ __global__ void __launch_bounds__(MAXT, MAXT <= 256 ? 5 : 1) blend_forward_kerne
             // number of pixels that found something, whether staging the attributes pays was slower: the loads then
             // wait alone behind a barrier.)
             const bool one_chunk = c.end - c.start <= kChunk;
-            const int found = select_sweep(P, c, go, bs, lastDepth, lastJ, dl, jl, s_geo, s_id, one_chunk ? s_attr : nullptr);
+            const int found = select_sweep<STREAM>(P, c, go, bs, lastDepth, lastJ, dl, jl, s_geo, s_id,
+                                                   one_chunk ? s_attr : nullptr, one_chunk ? nullptr : s_attr, s_id2);
             if (go) {
                 const int n = min(found, P.max_layers - acc.blended);
                 for (int i = 0; i < n; i++) {
@@ -1337,7 +1386,11 @@ namespace tg_host {
 // Set by tg_render_forward / tg_render_step_l2 around their compositing call (same thread): the tile order the
 // binning kernel left in the workspace.  The stage entry points run with the identity order.
 static thread_local const uint32_t* g_tile_order = nullptr;
-void set_tile_order(const uint32_t* order) { g_tile_order = order; }
+static thread_local uint32_t g_longest_list = 0;
+void set_tile_order(const uint32_t* order, uint32_t longest_list) {
+    g_tile_order = order;
+    g_longest_list = longest_list;
+}
 }  // namespace tg_host
 
 extern "C" {
@@ -1357,7 +1410,10 @@ int tg_blend_forward(const float* tri_geo, const float* tri_attr, const int32_t*
     cudaStream_t s = (cudaStream_t)stream;
     float4* img = (float4*)image;
     if (threads <= 256) {
-        if (per_pixel_sort) tg::blend_forward_kernel<true, 256><<<tiles, threads, 0, s>>>(P, img, depthmap, final_weights, ends, selection);
+        // lists well beyond one staged chunk (the binning kernel of the same call reported the longest): stream them
+        if (per_pixel_sort && threads == 256 && tg_host::g_longest_list > 2u * tg::kChunk)
+            tg::blend_forward_kernel<true, 256, true><<<tiles, threads, 0, s>>>(P, img, depthmap, final_weights, ends, selection);
+        else if (per_pixel_sort) tg::blend_forward_kernel<true, 256><<<tiles, threads, 0, s>>>(P, img, depthmap, final_weights, ends, selection);
         else tg::blend_forward_kernel<false, 256><<<tiles, threads, 0, s>>>(P, img, depthmap, final_weights, ends, nullptr);
     } else {
         if (per_pixel_sort) tg::blend_forward_kernel<true, 1024><<<tiles, threads, 0, s>>>(P, img, depthmap, final_weights, ends, selection);

@@ -99,7 +99,7 @@ int preprocess_scan(const float* vertices, const int32_t* indices, const float* 
 int emit_entries(const float* vertices, const int32_t* indices, int T, int W, int H, int tw, int th,
                  const uint32_t* tri_offsets, const void* scan_scratch, uint32_t* tile_cursor, uint64_t* entries,
                  uint32_t capacity, const float* tri_geo_for_cull, bool packed, cudaStream_t stream);
-void set_tile_order(const uint32_t* order);
+void set_tile_order(const uint32_t* order, uint32_t longest_list = 0);
 size_t tile_sort_scratch_bytes(int tiles);
 int sort_tile_lists(uint64_t* entries, const int32_t* offsets, int tiles, int32_t* sorted_ids, uint32_t* lists,
                     bool scratch_prepared, bool write_back, uint32_t longest, cudaStream_t stream);
